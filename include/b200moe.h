@@ -1,0 +1,179 @@
+/*
+ * b200moe -- C ABI of the sm_100a routed-MoE expert path.
+ *
+ * Every entry point takes raw device pointers, explicit sizes / pitches and a
+ * cudaStream_t (passed as void*), enqueues its kernels on that stream and returns at
+ * once: 0 on success or one of the negative B200MOE_ERR_* codes below.  Nothing here
+ * allocates, synchronises or throws.  Kernels that can wait on something (the GEMMs) or
+ * validate device-side data also take `status`, a device int32[4] block that the
+ * caller zeroes once and reads after a synchronisation of its own:
+ *   status[0] 0 = fine, 1 = a bounded wait ran out, 2 = malformed offsets / ids
+ *   status[1] block index, status[2] where, status[3] detail.
+ *
+ * "Reference" citations name the function of als244/mlops that the entry point
+ * replaces, by path inside that project.
+ *
+ * Pitches named ld* are in ELEMENTS of the tensor they belong to unless the comment
+ * says bytes.  All E4M3 tensors hold torch.float8_e4m3fn bytes.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_OK 0
+#define B200MOE_ERR_ARG (-1)       /* null pointer, negative size, unsupported combination */
+#define B200MOE_ERR_ALIGN (-2)     /* pointer / pitch alignment requirement not met */
+#define B200MOE_ERR_TENSORMAP (-3) /* the driver refused a TMA tensor map for an operand */
+#define B200MOE_ERR_LAUNCH (-4)    /* a kernel launch failed */
+#define B200MOE_ERR_DRIVER (-5)    /* cuTensorMapEncodeTiled not available */
+#define B200MOE_ERR_LIMIT (-6)     /* a size exceeds a documented maximum */
+
+/* Routing modes of b200moe_route_topk. */
+#define B200MOE_ROUTE_TOPK_THEN_SOFTMAX 0
+#define B200MOE_ROUTE_SOFTMAX_THEN_TOPK 1
+#define B200MOE_ROUTE_SIGMOID_NOAUX_TC 2
+
+/* Activation scale granularity of b200moe_quantize_rows. */
+#define B200MOE_SCALE_BLOCK128 0 /* one fp32 scale per row and 128-column block */
+#define B200MOE_SCALE_ROW 1      /* one fp32 scale per row */
+
+/*
+ * Top-k routing from fp32 logits [tokens, experts] (row pitch ld).  Writes
+ * weights fp32 [tokens, top_k] and ids int32 [tokens, top_k], picks in descending
+ * selection value, ties to the lowest expert id.  `bias` (fp32 [experts], may be NULL),
+ * n_group, topk_group and routed_scaling are read in mode SIGMOID_NOAUX_TC only.
+ * Limits: experts <= 1024, top_k <= 32, n_group <= 32 when group selection is active.
+ * Reference: src/mlops/kernels/moe_router.py:235-344 (`route`).
+ */
+int b200moe_route_topk(const float* logits, long long ld, int tokens, int experts, int top_k, int mode,
+                       const float* bias, int n_group, int topk_group, float routed_scaling,
+                       float* weights, int32_t* ids, void* stream);
+
+/*
+ * Stable sort of the flat ids [assignments] by expert:
+ *   order [assignments] int32, offsets [experts + 1] int32, slots [assignments] int32,
+ *   counts64 [experts] int64 (may be NULL).
+ * `workspace` must hold b200moe_sort_assignments_workspace_bytes(...) bytes.
+ * Limits: experts <= 1024, assignments < 2^31.
+ * Reference: src/mlops/kernels/moe_dispatch.py:106-119 (`sort_assignments`).
+ */
+long long b200moe_sort_assignments_workspace_bytes(long long assignments, int experts);
+int b200moe_sort_assignments(const int32_t* ids, long long assignments, int experts, int32_t* order,
+                             int32_t* offsets, int32_t* slots, long long* counts64, void* workspace,
+                             int32_t* status, void* stream);
+
+/*
+ * E4M3 quantisation of bf16 rows, optionally gathered: output row r reads input row
+ * gather[r] / gather_div (gather may be NULL: row r).  q is [rows, width] bytes with
+ * byte pitch ldq; scale of (row r, block b) is written to
+ * scales[r * scale_row_stride + b * scale_block_stride] (block b = columns 128b..128b+127;
+ * mode B200MOE_SCALE_ROW writes only b = 0).  width % 8 == 0.
+ * Reference: src/mlops/kernels/quack_moe/quantize_rows.py:140-207 (`quantize_rows_fp8`,
+ * per-row); the 1x128 mode applies the same equations per block.
+ */
+int b200moe_quantize_rows(const void* x, long long ldx, const int32_t* gather, int gather_div,
+                          long long rows, int width, void* q, long long ldq, float* scales,
+                          long long scale_row_stride, long long scale_block_stride, int mode,
+                          void* stream);
+
+/*
+ * SwiGLU of h13 = [gate | up] (bf16 [rows, 2*width]) computed in fp32 and rounded once
+ * to E4M3 with 1x128 scales (act_q, scales) and/or bf16 (act_bf16); either output may be
+ * NULL.  `limited` != 0 caps the gate at `limit` and clips up to [-limit, limit].
+ * Reference: src/mlops/kernels/quack_moe/swiglu_rows.py:246-256 (`swiglu_quantize_rows_fp8`),
+ * clamp semantics src/mlops/kernels/moe_reference.py:12-17.
+ */
+int b200moe_swiglu_quantize(const void* h13, long long ldh, long long rows, int width, void* act_q,
+                            long long ldq, float* scales, long long scale_row_stride,
+                            long long scale_block_stride, void* act_bf16, long long lda, float limit,
+                            int limited, void* stream);
+
+/*
+ * Routed SwiGLU backward.  r = dy_row @ W2 before the route weight (bf16 [rows, width]),
+ * score(row) = route_weights[order[row]].  Outputs (each may be NULL):
+ *   dscore fp32 [rows] = <r, act>; grad_h13 = dSwiGLU(score * r) as E4M3 + 1x128 scales
+ *   ([rows, 2*width], needs width % 128 == 0) and/or bf16; act_scaled = score * act (bf16).
+ * Reference: src/mlops/kernels/quack_moe/swiglu_rows.py:292-316
+ * (`routed_swiglu_rows_backward`).
+ */
+int b200moe_dswiglu_routed(const void* h13, long long ldh, const void* r, long long ldr,
+                           const float* route_weights, const int32_t* order, long long rows, int width,
+                           float* dscore, void* grad_h13_q, long long ldq, float* grad_h13_scales,
+                           long long scale_row_stride, long long scale_block_stride,
+                           void* grad_h13_bf16, long long ldg, void* act_scaled, long long lda,
+                           float limit, int limited, void* stream);
+
+/*
+ * Weight quantisation: w [experts, out, in] (bf16, or fp32 when src_is_fp32) ->
+ * q E4M3 same shape, scale fp32 [experts, ceil(out/128), ceil(in/128)].
+ * Reference: src/mlops/kernels/block_fp8.py:63-93 (`quantize_blocks`).
+ */
+int b200moe_quantize_blocks(const void* w, int src_is_fp32, int experts, int out, int in, void* q,
+                            float* scale, void* stream);
+
+/*
+ * Grouped block-FP8 GEMM, bf16 output.  Rows offsets[g]..offsets[g+1] of A belong to
+ * group g:  d[row, :] = (A_q . a_scale)[row, :] @ (B_q . b_scale)[g]^T.
+ *   a        E4M3 [rows_total, K], byte pitch lda (multiple of 16)
+ *   a_scale  fp32, scale of (row, K block kb) at a_scale[row*as_row_stride + kb*as_kb_stride]
+ *            (as_kb_stride = 0 gives one scale per row)
+ *   b        E4M3, contiguous; b_mn_major == 0: [groups, N, K] with scales
+ *            [groups, ceil(N/128), ceil(K/128)] (the forward products);
+ *            b_mn_major != 0: [groups, K, N] with scales [groups, ceil(K/128), ceil(N/128)]
+ *            (the stored weight read along its rows: input gradients, no transposed copy)
+ *   d        bf16 [rows_total, N], pitch ldd
+ *   block_n  128 or 256: tile width
+ * Every 128-wide K block is accumulated on the tensor cores from zero and promoted in
+ * fp32 by a_scale * b_scale.  N % 8 == 0, K % 16 == 0 (N % 16 for b_mn_major),
+ * groups <= 1024.
+ * Reference: src/mlops/kernels/block_fp8.py:249-341 (`grouped_block_gemm`) and
+ * src/mlops/kernels/quack_moe/block_fp8_gemm.py:1424-1484 (`block_fp8_gemm`,
+ * `block_fp8_transposed_gemm`).
+ */
+int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale, long long as_row_stride,
+                             long long as_kb_stride, const void* b, const float* b_scale, void* d,
+                             long long ldd, const int32_t* offsets, int groups, long long rows_total,
+                             int N, int K, int b_mn_major, int block_n, int32_t* status, void* stream);
+
+/*
+ * Grouped weight gradient: out[g] (M x N) = G[rows of g, 0:M]^T @ X[rows of g, 0:N],
+ * bf16 operands (pitches ldg, ldx), fp32 sums, out [groups, M, N] contiguous in bf16 or
+ * fp32 (out_is_fp32).  Groups without rows get zeros.  M % 8 == 0, N % 8 == 0.
+ * Reference: src/mlops/kernels/moe_grouped_gemm.py:300-342 (`grouped_mm_wgrad`).
+ */
+int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const void* x, long long ldx,
+                               const int32_t* offsets, int groups, long long rows_total, int M, int N,
+                               void* out, int out_is_fp32, int32_t* status, void* stream);
+
+/*
+ * out[t] = residual[t] + sum_k weights[t,k] * src[slots[t,k]] (fp32 sums, k ascending, one
+ * rounding).  weights NULL = 1, residual NULL = 0.  All row tensors bf16.
+ * Reference: src/mlops/kernels/moe_dispatch.py:136-196 (`combine`, `dispatch_backward`).
+ */
+int b200moe_combine(const void* src, long long lds, long long src_rows, const int32_t* slots,
+                    const float* weights, const void* residual, long long ldr, void* out, long long ldo,
+                    long long tokens, int width, int top_k, void* stream);
+
+/*
+ * dst[r] = src[gather[r] / gather_div], bf16 rows.
+ * Reference: src/mlops/kernels/moe_dispatch.py:122-124 (`dispatch`).
+ */
+int b200moe_gather_rows(const void* src, long long lds, const int32_t* gather, int gather_div,
+                        long long rows, int width, void* dst, long long ldd, void* stream);
+
+/*
+ * out[i] = values[slots[i]] for i < n (fp32): a per-sorted-row scalar in assignment order.
+ * Reference: src/mlops/providers/moe_common.py:325-329 (route-weight gradient gather).
+ */
+int b200moe_gather_scalar(const float* values, const int32_t* slots, long long n, float* out,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

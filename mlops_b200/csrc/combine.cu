@@ -1,0 +1,115 @@
+// Un-permute / combine: out[t] = residual[t] + sum_k w[t,k] * src[slots[t,k]] in fp32,
+// slots visited in the fixed order k = 0..K-1 and the sum rounded once, so the result
+// is bitwise repeatable (reference: src/mlops/kernels/moe_dispatch.py:21-72, used by
+// `combine` :168 and, without weights and residual, by `dispatch_backward` :136).
+#include "common.cuh"
+#include "host_util.h"
+
+namespace b200 {
+
+constexpr int kCombineThreads = 128;
+
+__global__ void __launch_bounds__(kCombineThreads)
+combine_kernel(const __nv_bfloat16* __restrict__ src, long long lds, long long src_rows,
+               const int* __restrict__ slots, const float* __restrict__ weights,
+               const __nv_bfloat16* __restrict__ residual, long long ldr, __nv_bfloat16* __restrict__ out,
+               long long ldo, int D, int K) {
+  const long long t = blockIdx.x;
+  const int* st = slots + t * K;
+  const float* wt = weights != nullptr ? weights + t * K : nullptr;
+  for (int c = threadIdx.x * 8; c < D; c += kCombineThreads * 8) {
+    float acc[8];
+    if (residual != nullptr) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(residual + t * ldr + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        acc[2 * i] = f.x;
+        acc[2 * i + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    }
+    for (int k = 0; k < K; ++k) {
+      long long slot = st[k];
+      slot = slot < 0 ? 0 : (slot >= src_rows ? src_rows - 1 : slot);
+      const float w = wt != nullptr ? wt[k] : 1.0f;
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + slot * lds + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        acc[2 * i] = fmaf(f.x, w, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(f.y, w, acc[2 * i + 1]);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + t * ldo + c) = o;
+  }
+}
+
+// dst[r] = src[gather[r] / gather_div] (bf16 rows), the expert-ordered copy of token rows.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, const int* __restrict__ gather,
+                   int gather_div, long long rows, int D, __nv_bfloat16* __restrict__ dst, long long ldd) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const long long s = gather[r] / gather_div;
+  for (int c = lane * 8; c < D; c += 256)
+    *reinterpret_cast<uint4*>(dst + r * ldd + c) = *reinterpret_cast<const uint4*>(src + s * lds + c);
+}
+
+// out[t, k] = values[slots[t, k]]: a per-sorted-row scalar brought back to assignment order.
+__global__ void gather_scalar_kernel(const float* __restrict__ values, const int* __restrict__ slots,
+                                     long long n, float* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = values[slots[i]];
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200moe_combine(const void* src, long long lds, long long src_rows, const int32_t* slots,
+                               const float* weights, const void* residual, long long ldr, void* out,
+                               long long ldo, long long tokens, int width, int top_k, void* stream) {
+  if (!src || !slots || !out || tokens < 0 || width <= 0 || top_k <= 0 || src_rows <= 0)
+    return B200MOE_ERR_ARG;
+  if ((width % 8) || (lds % 8) || (ldo % 8) || (residual && (ldr % 8))) return B200MOE_ERR_ALIGN;
+  if (((uintptr_t)src & 15) || ((uintptr_t)out & 15) || ((uintptr_t)residual & 15)) return B200MOE_ERR_ALIGN;
+  if (tokens > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  if (tokens == 0) return B200MOE_OK;
+  combine_kernel<<<(unsigned)tokens, kCombineThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(src), lds, src_rows, slots, weights,
+      reinterpret_cast<const __nv_bfloat16*>(residual), ldr, reinterpret_cast<__nv_bfloat16*>(out), ldo, width,
+      top_k);
+  return launch_status();
+}
+
+extern "C" int b200moe_gather_rows(const void* src, long long lds, const int32_t* gather, int gather_div,
+                                   long long rows, int width, void* dst, long long ldd, void* stream) {
+  if (!src || !gather || !dst || rows < 0 || width <= 0 || gather_div <= 0) return B200MOE_ERR_ARG;
+  if ((width % 8) || (lds % 8) || (ldd % 8) || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15))
+    return B200MOE_ERR_ALIGN;
+  if (rows == 0) return B200MOE_OK;
+  gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(src), lds, gather, gather_div, rows, width,
+      reinterpret_cast<__nv_bfloat16*>(dst), ldd);
+  return launch_status();
+}
+
+extern "C" int b200moe_gather_scalar(const float* values, const int32_t* slots, long long n, float* out,
+                                     void* stream) {
+  if (!values || !slots || !out || n < 0) return B200MOE_ERR_ARG;
+  if (n == 0) return B200MOE_OK;
+  gather_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      values, slots, n, out);
+  return launch_status();
+}

@@ -1,0 +1,418 @@
+// Grouped block-FP8 GEMM for sm_100a.
+//
+//   D[rows of group g, :] = sum over 128-wide K blocks kb of
+//        a_scale[row, kb] * b_scale[g, n/128, kb] * (A_q[row, kb] . B_q[g, n, kb])
+//
+// A_q and B_q are E4M3; every 128-K block is multiplied on the tcgen05 tensor cores
+// from a zeroed TMEM accumulator, drained by the epilogue warps and promoted into
+// fp32 registers with the block's two scales, so FP8 accumulation never spans more
+// than one scale block (the rule the reference's block GEMMs follow:
+// src/mlops/kernels/block_fp8.py:217-223, kernels/quack_moe/block_fp8_gemm.py:1087-1136).
+//
+// One persistent CTA per SM, 12 warps:
+//   warp 0      TMA producer (A tile 128x128 bytes, B tile BLOCK_N x 128 bytes per stage)
+//   warp 1      UMMA issuer (one elected thread), 4 x (128 x BLOCK_N x 32) per K block
+//   warp 2      TMEM allocation / release
+//   warp 3      builds the tile table (group -> first M tile) in shared memory
+//   warps 4-11  epilogue: tcgen05.ld of a K block's partial, scale, accumulate; at the
+//               end of the K loop convert to bf16 and store the rows that belong to the
+//               group (rows past the group's end were multiplied but are not written).
+// Two TMEM accumulator buffers let the tensor cores run K block k+1 while block k is
+// being promoted.  No load is multicast; every wait is bounded.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace b200 {
+
+constexpr int kMaxGroups = 1024;
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 128;  // bytes == elements for E4M3
+constexpr int kGemmThreads = 384;
+
+struct GemmFp8Params {
+  const float* a_scale;
+  long long as_row_stride, as_kb_stride;
+  const float* b_scale;
+  long long bs_group_stride, bs_n_stride, bs_k_stride;
+  __nv_bfloat16* d;
+  long long ldd;
+  const int* offsets;
+  int groups, N, K, rows_total;
+  int* status;
+};
+
+template <int BLOCK_N>
+struct GemmCfg {
+  static constexpr int kStages = BLOCK_N == 128 ? 6 : 4;
+  static constexpr int kABytes = kBlockM * kBlockK;
+  static constexpr int kBBytes = BLOCK_N * kBlockK;
+  static constexpr int kTmemCols = 2 * BLOCK_N;
+  static constexpr int kTileBytes = kStages * (kABytes + kBBytes);
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSchedBytes = 2 * (kMaxGroups + 1) * 4;
+  static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes;
+};
+
+struct TileCoord {
+  int group, m0, rows_valid;
+};
+
+// m_tile_start[g] = number of M tiles in groups < g; offs[g] = first row of group g.
+__device__ __forceinline__ TileCoord locate_m_tile(int mt, const int* m_tile_start, const int* offs,
+                                                   int groups) {
+  int lo = 0, hi = groups - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (m_tile_start[mid] <= mt) lo = mid; else hi = mid - 1;
+  }
+  // groups with zero tiles share a start with their successor; the search above lands on
+  // the last group whose start <= mt, which is the one that owns the tile.
+  TileCoord c;
+  c.group = lo;
+  c.m0 = offs[lo] + (mt - m_tile_start[lo]) * kBlockM;
+  c.rows_valid = min(kBlockM, offs[lo + 1] - c.m0);
+  return c;
+}
+
+template <int BLOCK_N, bool B_MN_MAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b, const GemmFp8Params p) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  constexpr int kStages = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kStages * Cfg::kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTileBytes);
+  uint64_t* full = bars;                    // [kStages]
+  uint64_t* empty = bars + kStages;         // [kStages]
+  uint64_t* tfull = bars + 2 * kStages;     // [2]
+  uint64_t* tempty = bars + 2 * kStages + 2;  // [2]
+  uint64_t* drain = bars + 2 * kStages + 4;   // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  int* total_m_tiles_s = abort_flag + 1;
+  int* m_tile_start = reinterpret_cast<int*>(smem + Cfg::kTileBytes + Cfg::kBarBytes);  // [groups+1]
+  int* offs = m_tile_start + (kMaxGroups + 1);                                          // [groups+1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int groups = p.groups;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int num_n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 8);
+    mbar_init(&tempty[1], 8);
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 3) {
+    // Tile table: exclusive scan of ceil(M_g / 128) over the groups.
+    int running = 0;
+    bool bad = false;
+    for (int base = 0; base < groups; base += 32) {
+      const int g = base + lane;
+      int lo = 0, hi = 0;
+      if (g < groups) {
+        lo = p.offsets[g];
+        hi = p.offsets[g + 1];
+        if (lo < 0 || hi < lo || hi > p.rows_total) bad = true;
+      }
+      int tiles = (g < groups && !bad) ? (hi - lo + kBlockM - 1) / kBlockM : 0;
+      int incl = tiles;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (g < groups) {
+        m_tile_start[g] = running + incl - tiles;
+        offs[g] = lo;
+        if (g == groups - 1) offs[groups] = hi;
+      }
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) {
+      m_tile_start[groups] = running;
+      *total_m_tiles_s = bad ? 0 : running;
+      if (bad) report_error(p.status, ERR_BAD_OFFSETS, 0, 0);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = (*total_m_tiles_s) * num_n_tiles;
+
+  // The wide tile keeps 128 fp32 sums per epilogue thread: registers move from the
+  // producer warpgroup (warps 0-3) to the two epilogue warpgroups.  Each role adjusts
+  // its own limit at the top of its branch so the branches never merge in between.
+#define B200_REG_DEC() do { if constexpr (BLOCK_N == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); } while (0)
+#define B200_REG_INC() do { if constexpr (BLOCK_N == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); } while (0)
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    B200_REG_DEC();
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int mt = t / num_n_tiles;
+        const int n0 = (t - mt * num_n_tiles) * BLOCK_N;
+        const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[s], Cfg::kABytes + Cfg::kBBytes);
+          tma_load_2d(sA + s * Cfg::kABytes, &tmap_a, &full[s], kb * kBlockK, c.m0);
+          if (!B_MN_MAJOR) {
+            tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], kb * kBlockK, n0, c.group);
+          } else {
+#pragma unroll
+            for (int panel = 0; panel < BLOCK_N / 128; ++panel)
+              tma_load_3d(sB + s * Cfg::kBBytes + panel * (128 * kBlockK), &tmap_b, &full[s],
+                          n0 + panel * 128, kb * kBlockK, c.group);
+          }
+        }
+      }
+      if (!ok) {
+        // Unwinding: give the copies that were issued a bounded chance to land before
+        // this CTA's shared memory is released.
+        const uint32_t issued = it;
+        for (int s = 0; s < kStages; ++s) {
+          if (issued <= (uint32_t)s) continue;
+          const uint32_t last = ((issued - 1 - s) / kStages) * kStages + s;
+          const uint32_t ph = (last / kStages) & 1;
+          const long long start = clock64();
+          while (!mbar_try(&full[s], ph) && clock64() - start < 20000000LL) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ UMMA issuer -------------------------------
+    B200_REG_DEC();
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(0, 0, 0, B_MN_MAJOR ? 1 : 0, kBlockM, BLOCK_N);
+      uint32_t it = 0, ab = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it, ++ab) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          const int buf = ab & 1;
+          const uint32_t aph = (ab >> 1) & 1;
+          if (!mbar_wait(&tempty[buf], aph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sA + s * Cfg::kABytes);
+          const uint32_t b_addr = smem_u32(sB + s * Cfg::kBBytes);
+          const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
+          const uint64_t bdesc = B_MN_MAJOR ? make_smem_desc(b_addr, 128 * kBlockK, 1024)
+                                            : make_smem_desc(b_addr, 16, 1024);
+          const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+#pragma unroll
+          for (int k = 0; k < kBlockK / 32; ++k) {
+            // K-major: 32 bytes further along the 128-byte swizzled row.
+            // MN-major: 32 K-rows of 128 bytes further.
+            const uint64_t a_k = adesc + (uint64_t)((k * 32) >> 4);
+            const uint64_t b_k = bdesc + (uint64_t)(B_MN_MAJOR ? ((k * 32 * 128) >> 4) : ((k * 32) >> 4));
+            umma_f8(d_tmem, a_k, b_k, idesc, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          umma_commit(&tfull[buf]);
+        }
+      }
+      if (!ok) {
+        umma_commit(drain);
+        const long long start = clock64();
+        while (!mbar_try(drain, 0) && clock64() - start < 20000000LL) {}
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------- epilogue --------------------------------
+    B200_REG_INC();
+    constexpr int kCols = BLOCK_N / 2;  // columns owned by one thread
+    const int q = warp & 3;             // TMEM lane quarter this warp may read
+    const int half = (warp - 4) >> 2;   // which half of the tile's columns
+    const int row_in_tile = q * 32 + lane;
+    float acc[kCols];
+    uint32_t ab = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int mt = t / num_n_tiles;
+      const int n0 = (t - mt * num_n_tiles) * BLOCK_N;
+      const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
+      const int grow = c.m0 + row_in_tile;
+      const int srow = min(grow, p.rows_total - 1);
+      const float* as_ptr = p.a_scale + (long long)srow * p.as_row_stride;
+      const int col0 = n0 + half * kCols;
+      const float* bs_ptr = p.b_scale + (long long)c.group * p.bs_group_stride +
+                            (long long)min(col0 / 128, (p.N - 1) / 128) * p.bs_n_stride;
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+      float s_next = as_ptr[0] * bs_ptr[0];
+      for (int kb = 0; kb < num_kb; ++kb, ++ab) {
+        const float s = s_next;
+        if (kb + 1 < num_kb)
+          s_next = as_ptr[(long long)(kb + 1) * p.as_kb_stride] * bs_ptr[(long long)(kb + 1) * p.bs_k_stride];
+        const int buf = ab & 1;
+        const uint32_t aph = (ab >> 1) & 1;
+        if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N + half * kCols;
+#pragma unroll
+        for (int cc = 0; cc < kCols / 32; ++cc) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + cc * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(s, __uint_as_float(r[j]), acc[cc * 32 + j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
+      }
+      if (!ok) break;
+      if (row_in_tile < c.rows_valid) {
+        __nv_bfloat16* drow = p.d + (long long)grow * p.ldd + col0;
+#pragma unroll
+        for (int j = 0; j < kCols; j += 8) {
+          if (col0 + j + 8 <= p.N) {
+            uint4 v;
+            v.x = pack_bf16x2(acc[j + 0], acc[j + 1]);
+            v.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
+            v.z = pack_bf16x2(acc[j + 4], acc[j + 5]);
+            v.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
+            *reinterpret_cast<uint4*>(drow + j) = v;
+          }
+        }
+      }
+    }
+  }
+
+  else {
+    B200_REG_DEC();
+  }
+#undef B200_REG_DEC
+#undef B200_REG_INC
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BLOCK_N, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp8Params& p,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  auto kern = grouped_gemm_fp8_kernel<BLOCK_N, B_MN>;
+  // Function attributes are per device; setting one is a cheap host-side call.
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+    return B200MOE_ERR_LAUNCH;
+  const long long m_tiles_bound = (p.rows_total + kBlockM - 1) / kBlockM + p.groups;
+  const long long n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+  long long grid = m_tiles_bound * n_tiles;
+  const int sms = sm_count();
+  if (grid > sms) grid = sms;
+  if (grid < 1) grid = 1;
+  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  return launch_status();
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
+                                        long long as_row_stride, long long as_kb_stride, const void* b,
+                                        const float* b_scale, void* d, long long ldd,
+                                        const int32_t* offsets, int groups, long long rows_total, int N,
+                                        int K, int b_mn_major, int block_n, int32_t* status,
+                                        void* stream) {
+  if (!a || !a_scale || !b || !b_scale || !d || !offsets || !status) return B200MOE_ERR_ARG;
+  if (groups <= 0 || N <= 0 || K <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
+  if (groups > kMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  if (block_n != 128 && block_n != 256) return B200MOE_ERR_ARG;
+  if ((N % 8) || (K % 16) || (lda % 16) || (ldd % 8)) return B200MOE_ERR_ALIGN;
+  if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)d & 15)) return B200MOE_ERR_ALIGN;
+  if (b_mn_major && (N % 16)) return B200MOE_ERR_ALIGN;
+  if (rows_total == 0) return B200MOE_OK;
+
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_total};
+    uint64_t strides[1] = {(uint64_t)lda};
+    uint32_t box[2] = {128, 128};
+    int r = encode_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+  }
+  const int kblocks = (K + 127) / 128;
+  const int nblocks = (N + 127) / 128;
+  GemmFp8Params p;
+  p.a_scale = a_scale;
+  p.as_row_stride = as_row_stride;
+  p.as_kb_stride = as_kb_stride;
+  p.b_scale = b_scale;
+  p.d = reinterpret_cast<__nv_bfloat16*>(d);
+  p.ldd = ldd;
+  p.offsets = offsets;
+  p.groups = groups;
+  p.N = N;
+  p.K = K;
+  p.rows_total = (int)rows_total;
+  p.status = status;
+  if (!b_mn_major) {
+    // B is [groups, N, K], K contiguous; scales [groups, ceil(N/128), ceil(K/128)].
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)groups};
+    uint64_t strides[2] = {(uint64_t)K, (uint64_t)K * (uint64_t)N};
+    uint32_t box[3] = {128, (uint32_t)block_n, 1};
+    int r = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+    p.bs_group_stride = (long long)nblocks * kblocks;
+    p.bs_n_stride = kblocks;
+    p.bs_k_stride = 1;
+  } else {
+    // B is [groups, K, N], N contiguous (the stored weight read for an input gradient);
+    // scales [groups, ceil(K/128), ceil(N/128)].
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)groups};
+    uint64_t strides[2] = {(uint64_t)N, (uint64_t)K * (uint64_t)N};
+    uint32_t box[3] = {128, 128, 1};
+    int r = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+    p.bs_group_stride = (long long)nblocks * kblocks;
+    p.bs_n_stride = 1;
+    p.bs_k_stride = nblocks;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (block_n == 128) {
+    return b_mn_major ? launch_gemm<128, true>(ta, tb, p, s) : launch_gemm<128, false>(ta, tb, p, s);
+  }
+  return b_mn_major ? launch_gemm<256, true>(ta, tb, p, s) : launch_gemm<256, false>(ta, tb, p, s);
+}

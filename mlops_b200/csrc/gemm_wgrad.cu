@@ -1,0 +1,331 @@
+// Grouped weight-gradient GEMM for sm_100a (bf16 operands, fp32 accumulation in TMEM).
+//
+//   dW[g] (M x N) = G[rows of g, 0:M]^T @ X[rows of g, 0:N]
+//
+// Both operands are token-major matrices, so the contraction (token) axis is the slow
+// axis of both: the tiles are loaded by TMA as K-rows of 128 bytes and handed to
+// tcgen05.mma as MN-major operands.  The K extent of a group is arbitrary; the rows of
+// the last K block that lie past the group's end are zeroed in the A tile before the
+// MMAs are issued, so the neighbouring group's rows contribute nothing.  Sums are fp32
+// for the whole K loop (one TMEM accumulator per tile, two buffers so the epilogue of a
+// tile overlaps the MMAs of the next) and are written at the requested dtype; a group
+// without rows gets exact zeros (reference: src/mlops/kernels/moe_grouped_gemm.py:120-174,
+// 300-342 -- fp32 sums, selectable output dtype, zero for empty experts).
+#include "common.cuh"
+#include "host_util.h"
+
+namespace b200 {
+
+constexpr int kWgMaxGroups = 1024;
+constexpr int kWgBlockM = 128;
+constexpr int kWgBlockN = 256;
+constexpr int kWgBlockK = 64;
+constexpr int kWgStages = 4;
+constexpr int kWgThreads = 384;
+constexpr int kWgPanelBytes = kWgBlockK * 128;            // 64 K-rows x 64 bf16
+constexpr int kWgABytes = (kWgBlockM / 64) * kWgPanelBytes;  // 16 KB
+constexpr int kWgBBytes = (kWgBlockN / 64) * kWgPanelBytes;  // 32 KB
+constexpr int kWgTileBytes = kWgStages * (kWgABytes + kWgBBytes);
+constexpr int kWgSmemBytes = 1024 + kWgTileBytes + 256;
+constexpr int kWgTmemCols = 2 * kWgBlockN;
+
+struct WgradParams {
+  void* out;  // [groups, M, N]
+  const int* offsets;
+  int groups, M, N, rows_total;
+  int* status;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store8(OutT* dst, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(dst) = o;
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kWgThreads, 1)
+grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_x,
+                     const WgradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kWgStages * kWgABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWgTileBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kWgStages;
+  uint64_t* tfull = bars + 2 * kWgStages;
+  uint64_t* tempty = bars + 2 * kWgStages + 2;
+  uint64_t* drain = bars + 2 * kWgStages + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kWgStages + 5);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + kWgBlockM - 1) / kWgBlockM;
+  const int n_tiles = (p.N + kWgBlockN - 1) / kWgBlockN;
+  const int tiles_per_group = m_tiles * n_tiles;
+  const long long total_tiles = (long long)tiles_per_group * p.groups;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kWgStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 8);
+    mbar_init(&tempty[1], 8);
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_g);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, kWgTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Every role walks the same tile sequence and derives the same K range from `offsets`.
+  // A malformed range (negative, decreasing, past the end) is treated as empty.
+  auto group_range = [&](int g, int& lo, int& hi) {
+    lo = p.offsets[g];
+    hi = p.offsets[g + 1];
+    if (lo < 0 || hi < lo || hi > p.rows_total) {
+      report_error(p.status, ERR_BAD_OFFSETS, 20, g);
+      lo = hi = 0;
+    }
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int g = (int)(t / tiles_per_group);
+        const int rem = (int)(t - (long long)g * tiles_per_group);
+        const int m0 = (rem / n_tiles) * kWgBlockM;
+        const int n0 = (rem % n_tiles) * kWgBlockN;
+        int lo, hi;
+        group_range(g, lo, hi);
+        const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kWgStages;
+          const uint32_t ph = (it / kWgStages) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[s], kWgABytes + kWgBBytes);
+          const int krow = lo + kb * kWgBlockK;
+#pragma unroll
+          for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl)
+            tma_load_2d(sA + s * kWgABytes + pnl * kWgPanelBytes, &tmap_g, &full[s], m0 + pnl * 64, krow);
+#pragma unroll
+          for (int pnl = 0; pnl < kWgBlockN / 64; ++pnl)
+            tma_load_2d(sB + s * kWgBBytes + pnl * kWgPanelBytes, &tmap_x, &full[s], n0 + pnl * 64, krow);
+        }
+      }
+      if (!ok) {
+        const uint32_t issued = it;
+        for (int s = 0; s < kWgStages; ++s) {
+          if (issued <= (uint32_t)s) continue;
+          const uint32_t last = ((issued - 1 - s) / kWgStages) * kWgStages + s;
+          const uint32_t ph = (last / kWgStages) & 1;
+          const long long start = clock64();
+          while (!mbar_try(&full[s], ph) && clock64() - start < 20000000LL) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // All 32 lanes stay in the loop: they zero the K tail together; lane 0 issues.
+    constexpr uint32_t idesc = make_idesc(1, 1, 1, 1, kWgBlockM, kWgBlockN);
+    uint32_t it = 0, tb = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int g = (int)(t / tiles_per_group);
+      int lo, hi;
+      group_range(g, lo, hi);
+      const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+      if (num_kb == 0) continue;
+      const int buf = tb & 1;
+      const uint32_t aph = (tb >> 1) & 1;
+      ++tb;
+      if (!mbar_wait(&tempty[buf], aph ^ 1, abort_flag, p.status, 23)) { ok = false; break; }
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % kWgStages;
+        const uint32_t ph = (it / kWgStages) & 1;
+        if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22)) { ok = false; break; }
+        const int valid = hi - lo - kb * kWgBlockK;
+        if (valid < kWgBlockK) {
+          // rows [valid, 64) of both A panels: 128 bytes each, 16 bytes per lane-step
+          const int nbytes = (kWgBlockK - valid) * 128;
+          for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl) {
+            uint8_t* base = sA + s * kWgABytes + pnl * kWgPanelBytes + valid * 128;
+            for (int o = lane * 16; o < nbytes; o += 32 * 16)
+              *reinterpret_cast<uint4*>(base + o) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(sA + s * kWgABytes);
+          const uint32_t b_addr = smem_u32(sB + s * kWgBBytes);
+          const uint64_t adesc = make_smem_desc(a_addr, kWgPanelBytes, 1024);
+          const uint64_t bdesc = make_smem_desc(b_addr, kWgPanelBytes, 1024);
+          const uint32_t d_tmem = tmem_base + buf * kWgBlockN;
+#pragma unroll
+          for (int k = 0; k < kWgBlockK / 16; ++k) {
+            const uint64_t step = (uint64_t)((k * 16 * 128) >> 4);
+            umma_f16(d_tmem, adesc + step, bdesc + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (kb == num_kb - 1) umma_commit(&tfull[buf]);
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok && lane == 0) {
+      umma_commit(drain);
+      const long long start = clock64();
+      while (!mbar_try(drain, 0) && clock64() - start < 20000000LL) {}
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;
+    const int half = (warp - 4) >> 2;
+    constexpr int kCols = kWgBlockN / 2;
+    uint32_t tb = 0;
+    bool ok = true;
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int g = (int)(t / tiles_per_group);
+      const int rem = (int)(t - (long long)g * tiles_per_group);
+      const int m0 = (rem / n_tiles) * kWgBlockM;
+      const int n0 = (rem % n_tiles) * kWgBlockN;
+      int lo, hi;
+      group_range(g, lo, hi);
+      const bool has_rows = hi > lo;
+      const int m = m0 + q * 32 + lane;
+      const int col0 = n0 + half * kCols;
+      OutT* orow = out + ((long long)g * p.M + m) * p.N + col0;
+      int buf = 0;
+      if (has_rows) {
+        buf = tb & 1;
+        const uint32_t aph = (tb >> 1) & 1;
+        ++tb;
+        if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 24)) { ok = false; break; }
+        tc_fence_after_sync();
+      }
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kWgBlockN + half * kCols;
+#pragma unroll
+      for (int cc = 0; cc < kCols / 32; ++cc) {
+        uint32_t r[32];
+        if (has_rows) {
+          tmem_ld_32x32(taddr + cc * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + cc * 32 + j + 8 <= p.N) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
+              store8<OutT>(orow + cc * 32 + j, v);
+            }
+          }
+        }
+      }
+      if (has_rows) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kWgTmemCols);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const void* x, long long ldx,
+                                          const int32_t* offsets, int groups, long long rows_total, int M,
+                                          int N, void* out, int out_is_fp32, int32_t* status,
+                                          void* stream) {
+  if (!g || !x || !offsets || !out || !status) return B200MOE_ERR_ARG;
+  if (groups <= 0 || M <= 0 || N <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
+  if (groups > kWgMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  if ((M % 8) || (N % 8) || (ldg % 8) || (ldx % 8)) return B200MOE_ERR_ALIGN;
+  if (((uintptr_t)g & 15) || ((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return B200MOE_ERR_ALIGN;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const size_t esz = out_is_fp32 ? 4 : 2;
+  if (rows_total == 0) {
+    return cudaMemsetAsync(out, 0, (size_t)groups * M * N * esz, s) == cudaSuccess ? B200MOE_OK
+                                                                                   : B200MOE_ERR_LAUNCH;
+  }
+  CUtensorMap tg, tx;
+  {
+    uint64_t dims[2] = {(uint64_t)M, (uint64_t)rows_total};
+    uint64_t strides[1] = {(uint64_t)ldg * 2};
+    uint32_t box[2] = {64, (uint32_t)kWgBlockK};
+    int r = encode_tensor_map(&tg, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)rows_total};
+    uint64_t strides[1] = {(uint64_t)ldx * 2};
+    uint32_t box[2] = {64, (uint32_t)kWgBlockK};
+    int r = encode_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+  }
+  WgradParams p;
+  p.out = out;
+  p.offsets = offsets;
+  p.groups = groups;
+  p.M = M;
+  p.N = N;
+  p.rows_total = (int)rows_total;
+  p.status = status;
+  const long long tiles = (long long)groups * ((M + kWgBlockM - 1) / kWgBlockM) * ((N + kWgBlockN - 1) / kWgBlockN);
+  long long grid = tiles < sm_count() ? tiles : sm_count();
+  if (out_is_fp32) {
+    auto kern = grouped_wgrad_kernel<float>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmemBytes) != cudaSuccess)
+      return B200MOE_ERR_LAUNCH;
+    kern<<<(unsigned)grid, kWgThreads, kWgSmemBytes, s>>>(tg, tx, p);
+  } else {
+    auto kern = grouped_wgrad_kernel<__nv_bfloat16>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmemBytes) != cudaSuccess)
+      return B200MOE_ERR_LAUNCH;
+    kern<<<(unsigned)grid, kWgThreads, kWgSmemBytes, s>>>(tg, tx, p);
+  }
+  return launch_status();
+}

@@ -1,0 +1,333 @@
+"""Tensor-level wrappers over the C ABI: each function unpacks torch CUDA tensors into
+pointers / pitches, allocates the outputs with torch's caching allocator and enqueues the
+kernel on the current CUDA stream. No function synchronises, reads device memory on the
+host, or has a non-CUDA path: a CPU tensor is an error.
+
+Names follow the reference's raw kernel functions (`route`, `sort_assignments`,
+`quantize_rows_fp8`, `grouped_block_gemm`, `combine`, ...) so call sites read like
+`src/mlops/providers/moe_common.py` of the reference.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ._lib import NativeError, check, lib
+
+ROUTING_MODES = {"topk_then_softmax": 0, "softmax_then_topk": 1, "sigmoid_noaux_tc": 2}
+FP8 = torch.float8_e4m3fn
+
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors) -> torch.device:
+    device = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise NativeError("mlops_b200 kernels take CUDA tensors only (no CPU path)")
+        if device is None:
+            device = t.device
+        elif t.device != device:
+            raise NativeError("tensors live on different devices")
+    return device
+
+
+def _ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def status_block(device) -> torch.Tensor:
+    """The per-device int32[4] block the kernels report bounded-wait and validation
+    failures into. Created (zeroed) on first use."""
+    index = torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    block = _STATUS.get(index)
+    if block is None:
+        block = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
+        _STATUS[index] = block
+    return block
+
+
+def check_status(device=None) -> None:
+    """Synchronising check of the status block; raises when a kernel reported a failure.
+    Not called on the forward/backward path (it reads device memory)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    block = _STATUS.get(index)
+    if block is None:
+        return
+    code, where_block, where, detail = block.tolist()
+    if code != 0:
+        block.zero_()
+        names = {1: "bounded wait ran out", 2: "malformed offsets or ids", 3: "too many groups"}
+        raise NativeError(
+            f"device status: {names.get(code, code)} (block {where_block}, where {where}, detail {detail})"
+        )
+
+
+# ----------------------------------------------------------------------------- routing
+def route_topk(logits, top_k, mode, *, bias=None, n_group=1, topk_group=1, routed_scaling=1.0):
+    """(weights fp32 [T,K], ids int32 [T,K]) of fp32 logits [T,E]."""
+    _need_cuda(logits, bias)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise NativeError("logits must be fp32 [tokens, experts] with unit inner stride")
+    tokens, experts = logits.shape
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((tokens, top_k), dtype=torch.int32, device=logits.device)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    check(
+        lib.b200moe_route_topk(
+            logits.data_ptr(), logits.stride(0), tokens, experts, int(top_k), ROUTING_MODES[mode],
+            _ptr(bias), int(n_group), int(topk_group), float(routed_scaling),
+            weights.data_ptr(), ids.data_ptr(), _stream(),
+        ),
+        "route_topk",
+    )
+    return weights, ids
+
+
+def sort_assignments(route_ids, experts):
+    """(order int32 [R], offsets int32 [E+1], slots int32 [T,K], counts int64 [E])."""
+    _need_cuda(route_ids)
+    flat = route_ids.reshape(-1)
+    if flat.dtype != torch.int32 or not flat.is_contiguous():
+        flat = flat.to(torch.int32).contiguous()
+    n = flat.numel()
+    device = flat.device
+    order = torch.empty(n, dtype=torch.int32, device=device)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=device)
+    slots = torch.empty(n, dtype=torch.int32, device=device)
+    counts = torch.empty(experts, dtype=torch.int64, device=device)
+    nbytes = lib.b200moe_sort_assignments_workspace_bytes(n, experts)
+    workspace = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=device)
+    check(
+        lib.b200moe_sort_assignments(
+            flat.data_ptr(), n, experts, order.data_ptr(), offsets.data_ptr(), slots.data_ptr(),
+            counts.data_ptr(), workspace.data_ptr(), status_block(device).data_ptr(), _stream(),
+        ),
+        "sort_assignments",
+    )
+    return order, offsets, slots.view(route_ids.shape), counts
+
+
+# ------------------------------------------------------------------------ quantisation
+def _scale_buffer(rows, blocks, device):
+    """Scales are stored block-major ([blocks, rows]) so that the GEMM epilogue's 32
+    lanes read 32 consecutive floats; the returned view is [rows, blocks]."""
+    return torch.empty((blocks, max(rows, 1)), dtype=torch.float32, device=device)[:, :rows].t()
+
+
+def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128"):
+    """E4M3 rows and fp32 scales of bf16 `x [T, D]`; output row r reads input row
+    `gather[r] // gather_div`. Returns (q [R, D] float8_e4m3fn, scales [R, blocks])."""
+    _need_cuda(x, gather)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise NativeError("x must be bf16 [rows, width] with unit inner stride")
+    rows = x.shape[0] if gather is None else gather.numel()
+    width = x.shape[1]
+    q = torch.empty((rows, width), dtype=FP8, device=x.device)
+    blocks = (width + 127) // 128 if mode == "1x128" else 1
+    scales = _scale_buffer(rows, blocks, x.device)
+    check(
+        lib.b200moe_quantize_rows(
+            x.data_ptr(), x.stride(0), _ptr(gather), int(gather_div), rows, width, q.data_ptr(),
+            q.stride(0), scales.data_ptr(), scales.stride(0), scales.stride(1),
+            0 if mode == "1x128" else 1, _stream(),
+        ),
+        "quantize_rows",
+    )
+    return q, scales
+
+
+def swiglu_quantize(h13, *, limit=None, quantized=True, rounded=False):
+    """SwiGLU of h13 = [gate | up]. Returns (act_q, scales, act_bf16); entries not asked
+    for are None."""
+    _need_cuda(h13)
+    rows, two_f = h13.shape
+    width = two_f // 2
+    device = h13.device
+    act_q = scales = act = None
+    if quantized:
+        act_q = torch.empty((rows, width), dtype=FP8, device=device)
+        scales = _scale_buffer(rows, (width + 127) // 128, device)
+    if rounded:
+        act = torch.empty((rows, width), dtype=torch.bfloat16, device=device)
+    check(
+        lib.b200moe_swiglu_quantize(
+            h13.data_ptr(), h13.stride(0), rows, width, _ptr(act_q), width, _ptr(scales),
+            0 if scales is None else scales.stride(0), 0 if scales is None else scales.stride(1),
+            _ptr(act), width, 0.0 if limit is None else float(limit), 0 if limit is None else 1,
+            _stream(),
+        ),
+        "swiglu_quantize",
+    )
+    return act_q, scales, act
+
+
+def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, rounded=False,
+                   scaled_activation=False):
+    """One pass over h13 and r: returns (dscore [rows] fp32, grad_h13_q, grad_h13_scales,
+    grad_h13_bf16, act_scaled)."""
+    _need_cuda(h13, r, route_weights, order)
+    rows, two_f = h13.shape
+    width = two_f // 2
+    device = h13.device
+    dscore = torch.empty(rows, dtype=torch.float32, device=device)
+    gq = gs = gb = a_s = None
+    if quantized:
+        gq = torch.empty((rows, two_f), dtype=FP8, device=device)
+        gs = _scale_buffer(rows, (two_f + 127) // 128, device)
+    if rounded:
+        gb = torch.empty((rows, two_f), dtype=torch.bfloat16, device=device)
+    if scaled_activation:
+        a_s = torch.empty((rows, width), dtype=torch.bfloat16, device=device)
+    weights_flat = route_weights.reshape(-1)
+    check(
+        lib.b200moe_dswiglu_routed(
+            h13.data_ptr(), h13.stride(0), r.data_ptr(), r.stride(0), weights_flat.data_ptr(),
+            order.data_ptr(), rows, width, dscore.data_ptr(), _ptr(gq), two_f, _ptr(gs),
+            0 if gs is None else gs.stride(0), 0 if gs is None else gs.stride(1), _ptr(gb), two_f,
+            _ptr(a_s), width, 0.0 if limit is None else float(limit), 0 if limit is None else 1,
+            _stream(),
+        ),
+        "dswiglu_routed",
+    )
+    return dscore, gq, gs, gb, a_s
+
+
+def quantize_blocks(weight):
+    """(data E4M3 [E,out,in], scale fp32 [E, ceil(out/128), ceil(in/128)]) of a bf16 or
+    fp32 weight."""
+    _need_cuda(weight)
+    if weight.dim() != 3:
+        raise NativeError("Expected an [experts, out, in] weight")
+    weight = weight.contiguous()
+    if weight.dtype not in (torch.bfloat16, torch.float32):
+        weight = weight.float()
+    experts, out, inner = weight.shape
+    data = torch.empty(weight.shape, dtype=FP8, device=weight.device)
+    scale = torch.empty(
+        (experts, (out + 127) // 128, (inner + 127) // 128), dtype=torch.float32, device=weight.device
+    )
+    check(
+        lib.b200moe_quantize_blocks(
+            weight.data_ptr(), 1 if weight.dtype == torch.float32 else 0, experts, out, inner,
+            data.data_ptr(), scale.data_ptr(), _stream(),
+        ),
+        "quantize_blocks",
+    )
+    return data, scale
+
+
+# ------------------------------------------------------------------------------- GEMMs
+def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, block_n=128, out=None):
+    """bf16 `[rows, N]` of the grouped block-FP8 product. `b_q` is `[G, N, K]`
+    (`b_mn_major=False`) or `[G, K, N]` read along its rows (`b_mn_major=True`);
+    `a_scale` is `[rows, K/128]` (any strides) or `[rows]`/`[rows, 1]` for one scale per row."""
+    device = _need_cuda(a_q, a_scale, b_q, b_scale, offsets)
+    rows, k = a_q.shape
+    groups = b_q.shape[0]
+    n = b_q.shape[2] if b_mn_major else b_q.shape[1]
+    kb = b_q.shape[1] if b_mn_major else b_q.shape[2]
+    if kb != k:
+        raise NativeError(f"contraction sizes differ: A has {k}, B has {kb}")
+    if not b_q.is_contiguous() or not b_scale.is_contiguous():
+        raise NativeError("weights and their scales must be contiguous")
+    if a_scale.dim() == 1:
+        a_scale = a_scale.unsqueeze(1)
+    kblocks = (k + 127) // 128
+    if a_scale.shape[1] == 1:
+        as_kb = 0  # one scale per row, applied to every K block
+    elif a_scale.shape[1] == kblocks:
+        as_kb = a_scale.stride(1)
+    else:
+        raise NativeError("a_scale must have 1 or ceil(K/128) columns")
+    if out is None:
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
+    check(
+        lib.b200moe_grouped_gemm_fp8(
+            a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
+            b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), offsets.data_ptr(),
+            groups, rows, n, k, 1 if b_mn_major else 0, int(block_n),
+            status_block(device).data_ptr(), _stream(),
+        ),
+        "grouped_gemm_fp8",
+    )
+    return out
+
+
+def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
+    """`[G, M, N]` with `out[e] = g[rows_e].T @ x[rows_e]` (bf16 operands, fp32 sums)."""
+    device = _need_cuda(g, x, offsets)
+    rows, m = g.shape
+    n = x.shape[1]
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise NativeError("weight gradients are written as bf16 or fp32")
+    out = torch.empty((groups, m, n), dtype=out_dtype, device=device)
+    check(
+        lib.b200moe_grouped_wgrad_bf16(
+            g.data_ptr(), g.stride(0), x.data_ptr(), x.stride(0), offsets.data_ptr(), groups, rows,
+            m, n, out.data_ptr(), 1 if out_dtype == torch.float32 else 0,
+            status_block(device).data_ptr(), _stream(),
+        ),
+        "grouped_wgrad",
+    )
+    return out
+
+
+# ---------------------------------------------------------------------- permutation I/O
+def combine(source, slots, weights, residual):
+    """`residual + sum_k weights[:, k] * source[slots[:, k]]` as bf16 `[T, D]`."""
+    device = _need_cuda(source, slots, weights, residual)
+    tokens, top_k = slots.shape
+    width = source.shape[1]
+    out = torch.empty((tokens, width), dtype=torch.bfloat16, device=device)
+    check(
+        lib.b200moe_combine(
+            source.data_ptr(), source.stride(0), source.shape[0], slots.data_ptr(), _ptr(weights),
+            _ptr(residual), 0 if residual is None else residual.stride(0), out.data_ptr(),
+            out.stride(0), tokens, width, top_k, _stream(),
+        ),
+        "combine",
+    )
+    return out
+
+
+def dispatch_backward(source, slots):
+    """Scatter-sum of expert-ordered rows back to their tokens."""
+    return combine(source, slots, None, None)
+
+
+def dispatch(x, order, top_k):
+    """bf16 rows of `x` in expert order: row j is `x[order[j] // top_k]`."""
+    device = _need_cuda(x, order)
+    rows = order.numel()
+    out = torch.empty((rows, x.shape[1]), dtype=torch.bfloat16, device=device)
+    check(
+        lib.b200moe_gather_rows(
+            x.data_ptr(), x.stride(0), order.data_ptr(), int(top_k), rows, x.shape[1],
+            out.data_ptr(), out.stride(0), _stream(),
+        ),
+        "dispatch",
+    )
+    return out
+
+
+def gather_scalar(values, slots):
+    """`values[slots]` (fp32), shaped like `slots`."""
+    _need_cuda(values, slots)
+    out = torch.empty(slots.shape, dtype=torch.float32, device=values.device)
+    check(
+        lib.b200moe_gather_scalar(
+            values.data_ptr(), slots.data_ptr(), slots.numel(), out.data_ptr(), _stream()
+        ),
+        "gather_scalar",
+    )
+    return out

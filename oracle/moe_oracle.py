@@ -1,0 +1,317 @@
+"""CPU restatement of the reference's routed-MoE expert path (als244/mlops).
+
+TEST INFRASTRUCTURE ONLY. Nothing in the `mlops_b200` package imports this module; it
+is called by `tests/`, by `__graft_entry__.smoke()` as the checker and by `bench.py`'s
+CPU-baseline leg. It is plain PyTorch on CPU tensors and follows the reference function
+by function (citations are paths inside the reference project).
+
+Pinned against the reference itself: `tests/golden/make_golden.py` imports the reference
+(`src/mlops`) in the build container, runs its `route`, `sort_assignments`,
+`quantize_blocks`, `quantize_rows_fp8_reference`, `native_torch.moe` and the
+expert-parallel reference on seeded inputs and stores the results as fixtures;
+`tests/test_oracle_golden.py` checks every function below against those fixtures.
+The 1x128 activation-scale quantiser has no counterpart in the reference's
+registry-dispatched path (its in-tree recipe is one scale per row): for that mode the
+*quantiser* parity is unpinned; the GEMM on given operands is pinned by the
+float64-of-dequantised-operands method the reference's own tests use
+(tests/test_block_fp8_transpose_gemm.py:447-459).
+"""
+
+from __future__ import annotations
+
+import torch
+
+BLOCK = 128
+E4M3_MAX = 448.0
+FP8 = torch.float8_e4m3fn
+
+
+# --------------------------------------------------------------------------- routing
+def route(logits, top_k, mode, *, bias=None, n_group=1, topk_group=1, routed_scaling=1.0):
+    """(weights fp32 [T,K], ids int32 [T,K]).
+
+    Follows src/mlops/kernels/moe_router.py:290-344 (`route`, CPU branch) and its twin
+    `route_torch` :347-400: stable descending sorts, so ties go to the lowest index."""
+    logits = logits.float()
+    tokens, experts = logits.shape
+    if mode == "sigmoid_noaux_tc":
+        scores = torch.sigmoid(logits)
+        selection = scores + (0.0 if bias is None else bias.float())
+        if int(topk_group) >= int(n_group):
+            masked = selection
+        else:
+            grouped = selection.view(tokens, int(n_group), experts // int(n_group))
+            grouped, _ = torch.sort(grouped, dim=-1, descending=True, stable=True)
+            group_scores = grouped[..., : min(2, grouped.shape[-1])].sum(-1)
+            _, group_ids = torch.sort(group_scores, dim=-1, descending=True, stable=True)
+            group_mask = torch.zeros(tokens, int(n_group), dtype=torch.bool)
+            group_mask.scatter_(1, group_ids[:, : int(topk_group)], True)
+            expert_mask = group_mask.repeat_interleave(experts // int(n_group), dim=1)
+            masked = selection.masked_fill(~expert_mask, float("-inf"))
+        _, selected = torch.sort(masked, dim=-1, descending=True, stable=True)
+        selected = selected[:, : int(top_k)]
+        picked = scores.gather(1, selected)
+        weights = picked / picked.sum(-1, keepdim=True) * float(routed_scaling)
+        return weights, selected.to(torch.int32)
+    if mode not in ("softmax_then_topk", "topk_then_softmax"):
+        raise ValueError(f"unsupported routing mode {mode!r}")
+    values = torch.softmax(logits, -1) if mode == "softmax_then_topk" else logits
+    values, indices = torch.sort(values, dim=-1, descending=True, stable=True)
+    selected = values[:, :top_k]
+    if mode == "topk_then_softmax":
+        selected = torch.softmax(selected, -1)
+    return selected.contiguous(), indices[:, :top_k].to(torch.int32)
+
+
+def sort_assignments(route_ids, experts):
+    """(order int32 [R], offsets int32 [E+1], slots int32 like route_ids).
+    Follows src/mlops/kernels/moe_dispatch.py:106-119."""
+    flat = route_ids.reshape(-1).long()
+    order = torch.argsort(flat, stable=True).to(torch.int32)
+    counts = torch.bincount(flat, minlength=experts)
+    offsets = torch.zeros(experts + 1, dtype=torch.int32)
+    offsets[1:] = counts.cumsum(0).to(torch.int32)
+    slots = torch.empty_like(flat, dtype=torch.int32)
+    slots[order.long()] = torch.arange(flat.numel(), dtype=torch.int32)
+    return order, offsets, slots.view_as(route_ids)
+
+
+def routing_statistics(logits, route_ids, *, routing_mode, lengths, experts):
+    """(aux, counts int64 [E], probability_sum fp32 [E]).
+    Follows src/mlops/providers/moe_common.py:32-71."""
+    rows = logits.shape[0]
+    if routing_mode == "sigmoid_noaux_tc":
+        scores = torch.sigmoid(logits.float())
+        probabilities = scores / scores.sum(-1, keepdim=True)
+    else:
+        probabilities = torch.softmax(logits.float(), dim=-1)
+    probability_sum = probabilities.sum(0)
+    counts = torch.bincount(route_ids.reshape(-1).long(), minlength=experts)
+    if routing_mode == "sigmoid_noaux_tc":
+        aux = torch.zeros((), dtype=torch.float32)
+        start = 0
+        for length in lengths:
+            stop = start + int(length)
+            seg = torch.bincount(route_ids[start:stop].reshape(-1).long(), minlength=experts)
+            frequency = seg.float() * experts / (route_ids.shape[1] * int(length))
+            aux = aux + (frequency * probabilities[start:stop].mean(0)).sum()
+            start = stop
+    else:
+        frequency = counts.float() / route_ids.numel()
+        aux = experts * (frequency * (probability_sum / rows)).sum()
+    return aux, counts, probability_sum
+
+
+# ---------------------------------------------------------------------- quantisation
+def _blocks(width):
+    return -(-width // BLOCK)
+
+
+def _expanded(scale, out, inner):
+    return scale.repeat_interleave(BLOCK, 1).repeat_interleave(BLOCK, 2)[:, :out, :inner]
+
+
+def quantize_blocks(weight):
+    """(data E4M3, scale fp32 [E, ceil(out/128), ceil(in/128)]): scale = max(amax/448,
+    1e-12). Follows src/mlops/kernels/block_fp8.py:88-93 (the non-Triton branch)."""
+    value = weight.float()
+    experts, out, inner = value.shape
+    rows, cols = _blocks(out) * BLOCK, _blocks(inner) * BLOCK
+    padded = value
+    if (rows, cols) != (out, inner):
+        padded = value.new_zeros(experts, rows, cols)
+        padded[:, :out, :inner] = value
+    blocks = padded.view(experts, rows // BLOCK, BLOCK, cols // BLOCK, BLOCK)
+    scale = (blocks.abs().amax(dim=(2, 4)) / E4M3_MAX).clamp_min(1e-12)
+    data = (value / _expanded(scale, out, inner)).clamp(-E4M3_MAX, E4M3_MAX)
+    return data.to(FP8), scale
+
+
+def dequantize_blocks(data, scale, dtype=torch.float32):
+    """Follows src/mlops/kernels/block_fp8.py:96-99."""
+    _e, out, inner = data.shape
+    return (data.float() * _expanded(scale.float(), out, inner)).to(dtype)
+
+
+def quantize_rows(value, *, gather=None, mode="1x128"):
+    """(data E4M3 [rows, N], scales fp32 [rows, blocks]).
+
+    mode "row": src/mlops/kernels/quack_moe/quantize_rows.py:210-226
+    (`quantize_rows_fp8_reference`): scale = max(amax * (1/448), 1e-12).
+    mode "1x128": the same equations applied to every 128-column block of the row."""
+    rows = value if gather is None else value[gather.long()]
+    rows = rows.float()
+    n = rows.shape[1]
+    if mode == "row":
+        amax = rows.abs().amax(dim=1)
+        scales = torch.clamp_min(amax * (1.0 / 448.0), 1e-12)
+        quantized = torch.clamp(rows / scales[:, None], -448.0, 448.0)
+        return quantized.to(FP8), scales[:, None].contiguous()
+    nb = _blocks(n)
+    padded = rows
+    if nb * BLOCK != n:
+        padded = rows.new_zeros(rows.shape[0], nb * BLOCK)
+        padded[:, :n] = rows
+    blocks = padded.view(rows.shape[0], nb, BLOCK)
+    amax = blocks.abs().amax(dim=2)
+    scales = torch.clamp_min(amax * (1.0 / 448.0), 1e-12)
+    quantized = torch.clamp(blocks / scales[:, :, None], -448.0, 448.0)
+    return quantized.view(rows.shape[0], nb * BLOCK)[:, :n].to(FP8).contiguous(), scales
+
+
+def dequantize_rows(data, scales, dtype=torch.float64):
+    """`data * scale` per row or per 1x128 block, at `dtype`."""
+    rows, n = data.shape
+    value = data.to(dtype)
+    if scales.dim() == 1 or scales.shape[1] == 1:
+        return value * scales.reshape(rows, 1).to(dtype)
+    expanded = scales.to(dtype).repeat_interleave(BLOCK, 1)[:, :n]
+    return value * expanded
+
+
+# ------------------------------------------------------------------------------ GEMMs
+def grouped_block_gemm(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False,
+                       dtype=torch.float64):
+    """Product of the dequantised operands per group, at `dtype` (float64 by default:
+    the comparison the reference's GEMM tests make,
+    tests/test_block_fp8_transpose_gemm.py:447-459,486-498).
+    `b_q [G,N,K]` with scales `[G,N/128,K/128]`; with `b_mn_major` the stored weight is
+    `[G,K,N]` (scales `[G,K/128,N/128]`) and is read along its rows (an input gradient)."""
+    a = dequantize_rows(a_q, a_scale, dtype)
+    b = dequantize_blocks(b_q, b_scale, dtype)
+    groups = b_q.shape[0]
+    n = b_q.shape[2] if b_mn_major else b_q.shape[1]
+    out = torch.zeros((a_q.shape[0], n), dtype=dtype)
+    offs = offsets.tolist()
+    for g in range(groups):
+        lo, hi = offs[g], offs[g + 1]
+        if hi > lo:
+            out[lo:hi] = a[lo:hi] @ (b[g] if b_mn_major else b[g].t())
+    return out
+
+
+def grouped_wgrad(g, x, offsets, groups, dtype=torch.float64):
+    """`out[e] = g[rows_e].T @ x[rows_e]`; zeros for an expert without rows.
+    Follows src/mlops/kernels/moe_grouped_gemm.py:185-198,300-342."""
+    out = torch.zeros((groups, g.shape[1], x.shape[1]), dtype=dtype)
+    offs = offsets.tolist()
+    for e in range(groups):
+        lo, hi = offs[e], offs[e + 1]
+        if hi > lo:
+            out[e] = g[lo:hi].to(dtype).t() @ x[lo:hi].to(dtype)
+    return out
+
+
+# ------------------------------------------------------------------ SwiGLU and combine
+def swiglu(h13, limit=None):
+    """fp32 `silu(gate) * up` of h13 = [gate | up], GLM clamp when `limit` is given.
+    Follows src/mlops/kernels/quack_moe/swiglu_rows.py:49-80 (fp32, rounded by the
+    caller once) and src/mlops/kernels/moe_reference.py:12-17 (clamp)."""
+    width = h13.shape[1] // 2
+    gate, up = h13[:, :width].float(), h13[:, width:].float()
+    if limit is not None:
+        gate, up = gate.clamp(max=limit), up.clamp(-limit, limit)
+    return gate * torch.sigmoid(gate) * up
+
+
+def dswiglu_routed(h13, r, score, limit=None):
+    """(dscore [rows], grad_h13 fp32 [rows, 2F], act_scaled fp32 [rows, F]).
+    Follows src/mlops/kernels/quack_moe/swiglu_rows.py:100-199."""
+    width = h13.shape[1] // 2
+    raw_gate, raw_up = h13[:, :width].float(), h13[:, width:].float()
+    gate, up = raw_gate, raw_up
+    if limit is not None:
+        gate, up = raw_gate.clamp(max=limit), raw_up.clamp(-limit, limit)
+    sig = torch.sigmoid(gate)
+    silu = gate * sig
+    act = silu * up
+    rf = r.float()
+    dscore = (rf * act).sum(-1)
+    g = score[:, None].float() * rf
+    dgate = g * up * (sig + silu * (1.0 - sig))
+    dup = g * silu
+    if limit is not None:
+        dgate = torch.where(raw_gate <= limit, dgate, torch.zeros_like(dgate))
+        dup = torch.where((raw_up >= -limit) & (raw_up <= limit), dup, torch.zeros_like(dup))
+    return dscore, torch.cat([dgate, dup], dim=1), score[:, None].float() * act
+
+
+def combine(source, slots, weights, residual):
+    """`residual + sum_k w[:,k] * source[slots[:,k]]`, fp32 sums in slot order, one
+    rounding to bf16. Follows the kernel order of
+    src/mlops/kernels/moe_dispatch.py:21-72 (residual first, then k = 0..K-1)."""
+    tokens, top_k = slots.shape
+    acc = (torch.zeros((tokens, source.shape[1]), dtype=torch.float32) if residual is None
+           else residual.float().clone())
+    for k in range(top_k):
+        rows = source[slots[:, k].long()].float()
+        if weights is not None:
+            acc = torch.addcmul(acc, rows, weights[:, k].float()[:, None])
+        else:
+            acc = acc + rows
+    return acc.to(torch.bfloat16)
+
+
+# -------------------------------------------------------------------- the whole layer
+def router_logits(h2, router_weight, operand_dtype=torch.bfloat16):
+    """fp32 logits from operands at the activation's dtype with fp32 sums: what the
+    reference computes on CUDA (src/mlops/kernels/router.py:53-64)."""
+    return h2.to(operand_dtype).float() @ router_weight.to(operand_dtype).float().t()
+
+
+def forward_block_fp8(h2, residual, logits, w13_q, w13_s, w2_q, w2_s, *, top_k, routing_mode,
+                      router_bias=None, n_group=1, topk_group=1, routed_scaling=1.0,
+                      swiglu_limit=None, act_scale="1x128"):
+    """The routed layer with quantised activations ("identical block-FP8 operands"):
+    route -> sort -> gather+quantise -> up GEMM (bf16 h13, gate rows then up rows) ->
+    SwiGLU (fp32) -> quantise -> down GEMM (bf16 rows) -> combine.
+    Orchestration follows src/mlops/providers/moe_common.py:174-266 with the FP8 steps
+    of src/mlops/providers/sonicmoe/block_fp8.py:114-166 in place of the bf16 GEMMs.
+    Returns a dict of every intermediate."""
+    experts = w13_q.shape[0]
+    weights, ids = route(logits, top_k, routing_mode, bias=router_bias, n_group=n_group,
+                         topk_group=topk_group, routed_scaling=routed_scaling)
+    order, offsets, slots = sort_assignments(ids, experts)
+    token_of_row = torch.div(order.long(), int(top_k), rounding_mode="floor")
+    x_q, x_s = quantize_rows(h2, gather=token_of_row, mode=act_scale)
+    h13 = grouped_block_gemm(x_q, x_s, w13_q, w13_s, offsets).to(torch.bfloat16)
+    act = swiglu(h13, swiglu_limit)
+    a_q, a_s = quantize_rows(act, mode=act_scale)
+    y = grouped_block_gemm(a_q, a_s, w2_q, w2_s, offsets).to(torch.bfloat16)
+    output = combine(y, slots, weights, residual)
+    return dict(weights=weights, ids=ids, order=order, offsets=offsets, slots=slots, x_q=x_q,
+                x_s=x_s, h13=h13, a_q=a_q, a_s=a_s, y=y, output=output)
+
+
+def backward_block_fp8(grad_output, h2, fwd, w13_q, w13_s, w2_q, w2_s, *, top_k, swiglu_limit=None,
+                       act_scale="1x128"):
+    """VJP of `forward_block_fp8` for (h2 routed part, route weights, w13, w2), FP8 input
+    gradients and bf16-operand weight gradients (as the reference's fp8_block form:
+    src/mlops/providers/sonicmoe/moe.py:517-619, providers/sonicmoe/fp8.py:15-17).
+    Orchestration follows src/mlops/providers/moe_common.py:269-378."""
+    experts = w13_q.shape[0]
+    order, offsets, slots, weights = fwd["order"], fwd["offsets"], fwd["slots"], fwd["weights"]
+    token_of_row = torch.div(order.long(), int(top_k), rounding_mode="floor")
+    dy_q, dy_s = quantize_rows(grad_output, gather=token_of_row, mode=act_scale)
+    r = grouped_block_gemm(dy_q, dy_s, w2_q, w2_s, offsets, b_mn_major=True).to(torch.bfloat16)
+    score = weights.reshape(-1)[order.long()].float()
+    dscore, grad_h13, act_scaled = dswiglu_routed(fwd["h13"], r, score, swiglu_limit)
+    grad_route_weights = dscore[slots.reshape(-1).long()].view_as(weights)
+    gh_q, gh_s = quantize_rows(grad_h13, mode=act_scale)
+    grad_rows = grouped_block_gemm(gh_q, gh_s, w13_q, w13_s, offsets, b_mn_major=True).to(torch.bfloat16)
+    grad_h2 = combine(grad_rows, slots, None, None)
+    dy_rows = grad_output[token_of_row].to(torch.bfloat16)
+    x_rows = h2[token_of_row].to(torch.bfloat16)
+    grad_w2 = grouped_wgrad(dy_rows, act_scaled.to(torch.bfloat16), offsets, experts)
+    grad_w13 = grouped_wgrad(grad_h13.to(torch.bfloat16), x_rows, offsets, experts)
+    return dict(r=r, dscore=dscore, grad_route_weights=grad_route_weights, grad_h13=grad_h13,
+                grad_rows=grad_rows, grad_h2=grad_h2, grad_w2=grad_w2, grad_w13=grad_w13)
+
+
+def rel_errors(actual, expected):
+    """(max, mean) of |actual - expected| relative to the RMS of `expected`: the bf16
+    tolerance metric of the parity tests (max <= 2e-2, mean <= 2e-3)."""
+    a, e = actual.double(), expected.double()
+    scale = e.pow(2).mean().sqrt().clamp_min(1e-30)
+    diff = (a - e).abs() / scale
+    return diff.max().item(), diff.mean().item()
