@@ -1,0 +1,279 @@
+"""The routed MoE layer on block-FP8 experts: stateless forward and VJP.
+
+`forward_routed` / `backward_routed` mirror the reference's shared mechanics
+(`src/mlops/providers/moe_common.py:174-378`): same argument meaning, same ordered
+results and the same residual tuple `(logits, route_weights, route_ids, order, offsets,
+slots, h13)` with `h13` holding gate columns then up columns, so the explicit VJP surface
+(`src/mlops/explicit/moe.py:12-119`) can be served from here. What differs is below that
+boundary: the expert products are E4M3 x E4M3 on tcgen05 with 128x128 weight-block and
+1x128 activation-block scales, the gather is fused into the quantiser, SwiGLU into the
+activation quantiser, and the route-weight gradient, the SwiGLU backward and the
+quantisation of the pre-activation gradient are one pass.
+
+Every step is an asynchronous launch on the current CUDA stream; nothing here reads
+device memory on the host.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Sequence
+
+import torch
+
+from . import ops
+
+BLOCK_N_DEFAULT = 256
+
+
+# ------------------------------------------------------------------------- router GEMM
+def router_logits(hidden, router_weight):
+    """fp32 logits `[rows, E]`: operands at the activation's dtype, fp32 sums and output
+    (reference: src/mlops/kernels/router.py:53-64). A plain library GEMM."""
+    weight = getattr(router_weight, "_data", router_weight)
+    return torch.mm(hidden, weight.to(hidden.dtype).t(), out_dtype=torch.float32)
+
+
+def _router_weight_gradient(grad_logits, hidden, dtype):
+    """`grad_logits.T @ hidden` with the cotangent carried as two bf16 pieces so an fp32
+    master keeps an fp32-quality gradient (reference: src/mlops/kernels/router.py:92-110)."""
+    high = grad_logits.to(hidden.dtype)
+    gradient = torch.mm(high.t(), hidden, out_dtype=torch.float32)
+    residue = (grad_logits.float() - high.float()).to(hidden.dtype)
+    gradient.add_(torch.mm(residue.t(), hidden, out_dtype=torch.float32))
+    return gradient.to(dtype)
+
+
+# ---------------------------------------------------------------- routing statistics
+def _probabilities(logits, routing_mode):
+    if routing_mode == "sigmoid_noaux_tc":
+        scores = torch.sigmoid(logits.float())
+        return scores, scores / scores.sum(-1, keepdim=True)
+    return None, torch.softmax(logits.float(), dim=-1)
+
+
+def routing_statistics(logits, route_ids, counts, *, routing_mode, lengths, experts):
+    """`(aux, counts, probability_sum)` of one routing decision (reference:
+    src/mlops/providers/moe_common.py:32-71). `counts` is the int64 histogram the sort
+    kernel already produced."""
+    rows = logits.shape[0]
+    _scores, probabilities = _probabilities(logits, routing_mode)
+    probability_sum = probabilities.sum(0)
+    if routing_mode == "sigmoid_noaux_tc":
+        aux = torch.zeros((), dtype=torch.float32, device=logits.device)
+        start = 0
+        for length in lengths:
+            stop = start + int(length)
+            if len(lengths) == 1:
+                segment = counts
+            else:
+                segment = torch.bincount(route_ids[start:stop].reshape(-1).long(), minlength=experts)
+            frequency = segment.float() * experts / (route_ids.shape[1] * int(length))
+            aux = aux + (frequency * probabilities[start:stop].mean(0)).sum()
+            start = stop
+    else:
+        frequency = counts.float() / route_ids.numel()
+        aux = experts * (frequency * (probability_sum / rows)).sum()
+    return aux, counts, probability_sum
+
+
+def routing_gradient(grad_aux, grad_probability_sum, grad_route_weights, route_weights, route_ids,
+                     logits, counts, *, routing_mode, lengths):
+    """fp32 gradient of the logits from the cotangents of the route weights, the auxiliary
+    loss and the probability sum (reference: src/mlops/providers/moe_common.py:74-124,
+    src/mlops/kernels/moe_router.py:403-502)."""
+    tokens, experts = logits.shape
+    selected = route_ids.long()
+    grad_w = grad_route_weights.float()
+    scores, probabilities = _probabilities(logits, routing_mode)
+    grad_logits = torch.zeros_like(logits, dtype=torch.float32)
+    if routing_mode == "sigmoid_noaux_tc":
+        weights = route_weights.float()
+        picked = scores.gather(1, selected)
+        picked_sum = picked.sum(-1, keepdim=True)
+        scaling = weights.sum(-1, keepdim=True)
+        dot = (grad_w * weights).sum(-1, keepdim=True)
+        grad_logits.scatter_(1, selected, ((scaling * grad_w - dot) / picked_sum) * picked * (1.0 - picked))
+    elif routing_mode == "topk_then_softmax":
+        weights = route_weights.float()
+        grad_logits.scatter_(1, selected, weights * (grad_w - (grad_w * weights).sum(-1, keepdim=True)))
+    else:
+        top = probabilities.gather(1, selected)
+        dot = (grad_w * top).sum(-1, keepdim=True)
+        grad_logits.copy_(-probabilities * dot)
+        grad_logits.scatter_add_(1, selected, grad_w * top)
+
+    if grad_aux is not None:
+        if routing_mode == "sigmoid_noaux_tc":
+            row_sum = scores.sum(-1, keepdim=True)
+            start = 0
+            for length in lengths:
+                stop = start + int(length)
+                if len(lengths) == 1:
+                    segment = counts.float()
+                else:
+                    segment = torch.bincount(
+                        route_ids[start:stop].reshape(-1).long(), minlength=experts
+                    ).float()
+                frequency = segment * experts / (route_ids.shape[1] * int(length))
+                coefficient = grad_aux.float() / (int(length) * row_sum[start:stop])
+                part = probabilities[start:stop]
+                score_gradient = coefficient * (frequency.unsqueeze(0) - (part @ frequency).unsqueeze(1))
+                grad_logits[start:stop].add_(score_gradient * scores[start:stop] * (1.0 - scores[start:stop]))
+                start = stop
+        else:
+            frequency = counts.float() / route_ids.numel()
+            coefficient = grad_aux.float() * experts / tokens
+            grad_logits.add_(
+                coefficient * probabilities * (frequency.unsqueeze(0) - (probabilities @ frequency).unsqueeze(1))
+            )
+
+    if grad_probability_sum is not None:
+        jacobian_scale = probabilities if scores is None else (1.0 - scores) * probabilities
+        grad_sum = grad_probability_sum.float()
+        grad_logits.add_(jacobian_scale * (grad_sum.unsqueeze(0) - (probabilities @ grad_sum).unsqueeze(1)))
+    return grad_logits
+
+
+# ------------------------------------------------------------------------------ forward
+def _normalized_lengths(lengths, rows):
+    normalized = (rows,) if lengths is None else tuple(int(v) for v in lengths)
+    if not normalized or any(v <= 0 for v in normalized) or sum(normalized) != rows:
+        raise ValueError("MoE lengths must be positive and cover every hidden row")
+    return normalized
+
+
+def forward_routed(
+    h2: torch.Tensor,
+    residual: torch.Tensor,
+    router_weight: torch.Tensor,
+    w13: tuple[torch.Tensor, torch.Tensor],
+    w2: tuple[torch.Tensor, torch.Tensor],
+    *,
+    top_k: int,
+    routing_mode: str,
+    router_bias: torch.Tensor | None = None,
+    n_group: int = 1,
+    topk_group: int = 1,
+    routed_scaling: float = 1.0,
+    lengths: Sequence[int] | None = None,
+    swiglu_limit: float | None = None,
+    block_n: int = BLOCK_N_DEFAULT,
+    route: tuple[torch.Tensor, torch.Tensor] | None = None,
+) -> tuple[torch.Tensor, ...]:
+    """Returns `(output, aux, counts, probability_sum, logits, route_weights, route_ids,
+    order, offsets, slots, h13)`.
+
+    `w13 = (data E4M3 [E, 2F, D], scale fp32 [E, 2F/128, D/128])` with gate rows then up
+    rows, `w2 = (data [E, D, F], scale)`: the components of a block-FP8 weight container.
+    `route = (route_weights, route_ids)` bypasses the selection (the logits and the
+    statistics are still computed)."""
+    w13_data, w13_scale = w13
+    w2_data, w2_scale = w2
+    experts = w13_data.shape[0]
+    with torch.no_grad():
+        original_shape = h2.shape
+        h2_flat = h2.reshape(-1, h2.shape[-1]).contiguous()
+        residual_flat = residual.reshape_as(h2_flat).contiguous()
+        normalized = _normalized_lengths(lengths, h2_flat.shape[0])
+        logits = router_logits(h2_flat, router_weight)
+        if route is None:
+            bias = None if router_bias is None or router_bias.numel() == 0 else router_bias
+            route_weights, route_ids = ops.route_topk(
+                logits, int(top_k), str(routing_mode), bias=bias, n_group=int(n_group),
+                topk_group=int(topk_group), routed_scaling=float(routed_scaling),
+            )
+        else:
+            route_weights, route_ids = route
+            route_weights = route_weights.float().contiguous()
+            route_ids = route_ids.to(torch.int32).contiguous()
+        order, offsets, slots, counts = ops.sort_assignments(route_ids, experts)
+        x_q, x_s = ops.quantize_rows(h2_flat, gather=order, gather_div=int(top_k))
+        h13 = ops.grouped_gemm_fp8(x_q, x_s, w13_data, w13_scale, offsets, block_n=block_n)
+        a_q, a_s, _ = ops.swiglu_quantize(h13, limit=swiglu_limit)
+        expert_output = ops.grouped_gemm_fp8(a_q, a_s, w2_data, w2_scale, offsets, block_n=block_n)
+        output = ops.combine(expert_output, slots, route_weights, residual_flat).reshape(original_shape)
+        aux, counts, probability_sum = routing_statistics(
+            logits, route_ids, counts, routing_mode=str(routing_mode), lengths=normalized, experts=experts
+        )
+    return (output, aux, counts, probability_sum, logits, route_weights, route_ids, order, offsets, slots, h13)
+
+
+# ----------------------------------------------------------------------------- backward
+def backward_routed(
+    grad_output: torch.Tensor,
+    grad_aux: torch.Tensor | None,
+    grad_probability_sum: torch.Tensor | None,
+    h2: torch.Tensor,
+    router_weight: torch.Tensor,
+    w13: tuple[torch.Tensor, torch.Tensor],
+    w2: tuple[torch.Tensor, torch.Tensor],
+    logits: torch.Tensor,
+    route_weights: torch.Tensor,
+    route_ids: torch.Tensor,
+    order: torch.Tensor,
+    offsets: torch.Tensor,
+    slots: torch.Tensor,
+    h13: torch.Tensor,
+    *,
+    top_k: int,
+    routing_mode: str,
+    lengths: Sequence[int] | None = None,
+    weight_grad_dtype: torch.dtype | None = None,
+    swiglu_limit: float | None = None,
+    need_router: bool = True,
+    need_w13: bool = True,
+    need_w2: bool = True,
+    router_grad_dtype: torch.dtype | None = None,
+    block_n: int = BLOCK_N_DEFAULT,
+) -> tuple[torch.Tensor, ...]:
+    """VJPs for `h2, residual, router_weight, w13, w2` in order. A gradient nobody asked
+    for (`need_* = False`) is an empty placeholder and its GEMM is not launched
+    (reference: src/mlops/providers/moe_common.py:127-139, 269-378). Input gradients are
+    E4M3 products against the stored weights read along their rows; weight gradients are
+    bf16-operand products with fp32 sums, written at `weight_grad_dtype` (bf16 when None)."""
+    w13_data, w13_scale = w13
+    w2_data, w2_scale = w2
+    experts = w13_data.shape[0]
+    wdtype = torch.bfloat16 if weight_grad_dtype is None else weight_grad_dtype
+    with torch.no_grad():
+        original_shape = h2.shape
+        h2_flat = h2.reshape(-1, h2.shape[-1]).contiguous()
+        grad_flat = grad_output.reshape_as(h2_flat).contiguous()
+        normalized = _normalized_lengths(lengths, h2_flat.shape[0])
+        counts = (offsets[1:] - offsets[:-1]).long()
+
+        dy_q, dy_s = ops.quantize_rows(grad_flat, gather=order, gather_div=int(top_k))
+        r = ops.grouped_gemm_fp8(dy_q, dy_s, w2_data, w2_scale, offsets, b_mn_major=True, block_n=block_n)
+        dscore, gh_q, gh_s, gh_b, act_scaled = ops.dswiglu_routed(
+            h13, r, route_weights, order, limit=swiglu_limit, quantized=True, rounded=need_w13,
+            scaled_activation=need_w2,
+        )
+        grad_route_weights = ops.gather_scalar(dscore, slots)
+        if need_w2:
+            dy_rows = ops.dispatch(grad_flat, order, int(top_k))
+            grad_w2 = ops.grouped_wgrad(dy_rows, act_scaled, offsets, experts, wdtype)
+            del dy_rows, act_scaled
+        else:
+            grad_w2 = torch.empty(0, dtype=wdtype, device=h2.device)
+        if need_w13:
+            x_rows = ops.dispatch(h2_flat, order, int(top_k))
+            grad_w13 = ops.grouped_wgrad(gh_b, x_rows, offsets, experts, wdtype)
+            del x_rows, gh_b
+        else:
+            grad_w13 = torch.empty(0, dtype=wdtype, device=h2.device)
+        grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, w13_data, w13_scale, offsets, b_mn_major=True,
+                                         block_n=block_n)
+        grad_h2 = ops.dispatch_backward(grad_rows, slots)
+
+        grad_logits = routing_gradient(
+            grad_aux, grad_probability_sum, grad_route_weights, route_weights, route_ids, logits, counts,
+            routing_mode=str(routing_mode), lengths=normalized,
+        )
+        router_operand = getattr(router_weight, "_data", router_weight)
+        if need_router:
+            rdtype = router_weight.dtype if router_grad_dtype is None else router_grad_dtype
+            grad_router = _router_weight_gradient(grad_logits, h2_flat, rdtype)
+        else:
+            grad_router = torch.empty(0, dtype=router_weight.dtype, device=h2.device)
+        grad_h2.addmm_(grad_logits.to(h2_flat.dtype), router_operand.to(h2_flat.dtype))
+    return (grad_h2.reshape(original_shape), grad_output.clone(), grad_router, grad_w13, grad_w2)
