@@ -19,6 +19,36 @@ FP8 = torch.float8_e4m3fn
 
 _STATUS: dict[int, torch.Tensor] = {}
 
+# Instrumentation read by the bench: kernels launched through this module, and (when a list
+# is installed) one (start_event, end_event, kind, flops) record per tensor-core launch.
+LAUNCHES = 0
+GEMM_TIMINGS: list | None = None
+
+
+def _count(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
+class _Timed:
+    """Brackets a launch with CUDA events on the launching stream when timings are wanted."""
+
+    def __init__(self, kind: str, flops: float):
+        self.kind, self.flops = kind, flops
+
+    def __enter__(self):
+        if GEMM_TIMINGS is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.stop = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if GEMM_TIMINGS is not None:
+            self.stop.record()
+            GEMM_TIMINGS.append((self.start, self.stop, self.kind, self.flops))
+        return False
+
 
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
@@ -90,6 +120,7 @@ def route_topk(logits, top_k, mode, *, bias=None, n_group=1, topk_group=1, route
         ),
         "route_topk",
     )
+    _count()
     return weights, ids
 
 
@@ -114,6 +145,7 @@ def sort_assignments(route_ids, experts):
         ),
         "sort_assignments",
     )
+    _count(3 if n > 0 else 1)
     return order, offsets, slots.view(route_ids.shape), counts
 
 
@@ -143,6 +175,7 @@ def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128"):
         ),
         "quantize_rows",
     )
+    _count()
     return q, scales
 
 
@@ -168,6 +201,7 @@ def swiglu_quantize(h13, *, limit=None, quantized=True, rounded=False):
         ),
         "swiglu_quantize",
     )
+    _count()
     return act_q, scales, act
 
 
@@ -199,6 +233,7 @@ def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, 
         ),
         "dswiglu_routed",
     )
+    _count()
     return dscore, gq, gs, gb, a_s
 
 
@@ -223,6 +258,7 @@ def quantize_blocks(weight):
         ),
         "quantize_blocks",
     )
+    _count()
     return data, scale
 
 
@@ -251,15 +287,17 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
         raise NativeError("a_scale must have 1 or ceil(K/128) columns")
     if out is None:
         out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
-    check(
-        lib.b200moe_grouped_gemm_fp8(
-            a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
-            b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), offsets.data_ptr(),
-            groups, rows, n, k, 1 if b_mn_major else 0, int(block_n),
-            status_block(device).data_ptr(), _stream(),
-        ),
-        "grouped_gemm_fp8",
-    )
+    with _Timed("fp8", 2.0 * rows * n * k):
+        check(
+            lib.b200moe_grouped_gemm_fp8(
+                a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
+                b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), offsets.data_ptr(),
+                groups, rows, n, k, 1 if b_mn_major else 0, int(block_n),
+                status_block(device).data_ptr(), _stream(),
+            ),
+            "grouped_gemm_fp8",
+        )
+    _count()
     return out
 
 
@@ -271,14 +309,16 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise NativeError("weight gradients are written as bf16 or fp32")
     out = torch.empty((groups, m, n), dtype=out_dtype, device=device)
-    check(
-        lib.b200moe_grouped_wgrad_bf16(
-            g.data_ptr(), g.stride(0), x.data_ptr(), x.stride(0), offsets.data_ptr(), groups, rows,
-            m, n, out.data_ptr(), 1 if out_dtype == torch.float32 else 0,
-            status_block(device).data_ptr(), _stream(),
-        ),
-        "grouped_wgrad",
-    )
+    with _Timed("wgrad_bf16", 2.0 * rows * m * n):
+        check(
+            lib.b200moe_grouped_wgrad_bf16(
+                g.data_ptr(), g.stride(0), x.data_ptr(), x.stride(0), offsets.data_ptr(), groups, rows,
+                m, n, out.data_ptr(), 1 if out_dtype == torch.float32 else 0,
+                status_block(device).data_ptr(), _stream(),
+            ),
+            "grouped_wgrad",
+        )
+    _count()
     return out
 
 
@@ -297,6 +337,7 @@ def combine(source, slots, weights, residual):
         ),
         "combine",
     )
+    _count()
     return out
 
 
@@ -317,6 +358,7 @@ def dispatch(x, order, top_k):
         ),
         "dispatch",
     )
+    _count()
     return out
 
 
@@ -330,4 +372,5 @@ def gather_scalar(values, slots):
         ),
         "gather_scalar",
     )
+    _count()
     return out

@@ -178,15 +178,15 @@ def grouped_block_gemm(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False,
     `b_q [G,N,K]` with scales `[G,N/128,K/128]`; with `b_mn_major` the stored weight is
     `[G,K,N]` (scales `[G,K/128,N/128]`) and is read along its rows (an input gradient)."""
     a = dequantize_rows(a_q, a_scale, dtype)
-    b = dequantize_blocks(b_q, b_scale, dtype)
     groups = b_q.shape[0]
     n = b_q.shape[2] if b_mn_major else b_q.shape[1]
     out = torch.zeros((a_q.shape[0], n), dtype=dtype)
     offs = offsets.tolist()
     for g in range(groups):
         lo, hi = offs[g], offs[g + 1]
-        if hi > lo:
-            out[lo:hi] = a[lo:hi] @ (b[g] if b_mn_major else b[g].t())
+        if hi > lo:  # weights are dequantised one expert at a time (memory)
+            b = dequantize_blocks(b_q[g:g + 1], b_scale[g:g + 1], dtype)[0]
+            out[lo:hi] = a[lo:hi] @ (b if b_mn_major else b.t())
     return out
 
 

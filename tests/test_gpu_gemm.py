@@ -1,0 +1,204 @@
+"""Parity of the tcgen05 grouped GEMMs through the C ABI against the float64 product of the
+same dequantised operands (the comparison of the reference's
+tests/test_block_fp8_transpose_gemm.py:447-498). Tolerance: bf16 output, max relative error
+<= 2e-2 and mean <= 2e-3 (see `oracle.moe_oracle.rel_errors`)."""
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+FP8 = torch.float8_e4m3fn
+MAX_REL, MEAN_REL = 2e-2, 2e-3
+
+
+def _ops():
+    from mlops_b200 import ops
+
+    return ops
+
+
+def _offsets(counts):
+    offs = torch.zeros(len(counts) + 1, dtype=torch.int32)
+    offs[1:] = torch.tensor(counts).cumsum(0).to(torch.int32)
+    return offs
+
+
+def _case(counts, n, k, seed, mn_major, spread=False):
+    g = torch.Generator().manual_seed(seed)
+    rows, groups = sum(counts), len(counts)
+    a = torch.randn(rows, k, generator=g)
+    b = torch.randn(groups, n, k, generator=g)
+    if spread:  # block scales across 2^+-14 and one all-zero block (reference test shapes)
+        b[0, :128, :128] = 0
+        b[-1, :, :128] *= 2.0 ** 14
+        a[:, :128] *= 2.0 ** -14
+    a_q, a_s = O.quantize_rows(a, mode="1x128")
+    b_q, b_s = O.quantize_blocks(b)
+    if mn_major:
+        b_q = b_q.view(torch.uint8).transpose(1, 2).contiguous().view(FP8)
+        b_s = b_s.transpose(1, 2).contiguous()
+    return a_q, a_s, b_q, b_s, _offsets(counts)
+
+
+def _run(a_q, a_s, b_q, b_s, offs, mn_major, block_n, scale_layout="block_major"):
+    ops = _ops()
+    n = b_q.shape[2] if mn_major else b_q.shape[1]
+    scales = a_s.to(DEV) if scale_layout == "row_major" else a_s.t().contiguous().to(DEV).t()
+    out = torch.full((a_q.shape[0], n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.grouped_gemm_fp8(a_q.to(DEV), scales, b_q.to(DEV), b_s.to(DEV), offs.to(DEV),
+                         b_mn_major=mn_major, block_n=block_n, out=out)
+    ops.check_status(DEV)
+    return out
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("mn_major", [False, True])
+def test_integer_operands_are_exact(block_n, mn_major):
+    g = torch.Generator().manual_seed(1)
+    counts, n, k = [128, 64], 256, 384
+    rows = sum(counts)
+    a = torch.randint(-3, 4, (rows, k), generator=g).float()
+    b = torch.randint(-3, 4, (2, n, k), generator=g).float()
+    a_q, b_q = a.to(FP8), b.to(FP8)
+    a_s = torch.ones(rows, 3)
+    b_s = torch.ones(2, 2, 3)
+    offs = _offsets(counts)
+    ref = O.grouped_block_gemm(a_q, a_s, b_q, b_s, offs)
+    if mn_major:
+        b_q = b_q.view(torch.uint8).transpose(1, 2).contiguous().view(FP8)
+        b_s = b_s.transpose(1, 2).contiguous()
+    out = _run(a_q, a_s, b_q, b_s, offs, mn_major, block_n)
+    assert torch.equal(out.float().cpu().double(), ref)
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("mn_major", [False, True])
+@pytest.mark.parametrize(
+    "counts,n,k",
+    [
+        ([128, 256], 256, 512),
+        ([0, 70, 131, 15, 260], 384, 640),     # empty expert, partial M tiles
+        ([1, 0, 0, 513], 128, 128),
+        ([300], 2048, 7168),                   # the DeepSeek-shaped K loop (56 blocks)
+    ],
+)
+def test_random_operands(counts, n, k, mn_major, block_n):
+    a_q, a_s, b_q, b_s, offs = _case(counts, n, k, seed=n + k, mn_major=mn_major)
+    out = _run(a_q, a_s, b_q, b_s, offs, mn_major, block_n)
+    ref = O.grouped_block_gemm(a_q, a_s, b_q, b_s, offs, b_mn_major=mn_major)
+    assert not torch.isnan(out.float()).any()
+    mx, mean = O.rel_errors(out.float().cpu(), ref)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+def test_partial_blocks_and_scale_spread(block_n):
+    """K and N that are not multiples of 128 (reference shapes D=192, F=80 scaled to the
+    16-byte pitch rule), block scales spread over 2^+-14, an all-zero weight block."""
+    a_q, a_s, b_q, b_s, offs = _case([5, 300, 70], 200, 192, seed=4, mn_major=False)
+    out = _run(a_q, a_s, b_q, b_s, offs, False, block_n)
+    mx, mean = O.rel_errors(out.float().cpu(), O.grouped_block_gemm(a_q, a_s, b_q, b_s, offs))
+    assert mx <= MAX_REL and mean <= MEAN_REL
+    a_q, a_s, b_q, b_s, offs = _case([130, 70], 256, 384, seed=5, mn_major=False, spread=True)
+    out = _run(a_q, a_s, b_q, b_s, offs, False, block_n)
+    ref = O.grouped_block_gemm(a_q, a_s, b_q, b_s, offs)
+    for lo in range(0, 256, 128):  # per 128-column cell, as the reference's tests judge it
+        mx, mean = O.rel_errors(out.float().cpu()[:, lo:lo + 128], ref[:, lo:lo + 128])
+        assert mx <= MAX_REL and mean <= MEAN_REL
+
+
+def test_scale_layouts_and_row_scales_agree():
+    """Row-major and block-major activation scales give identical bytes; one scale per row
+    (the reference's in-tree recipe) goes through the same kernel."""
+    a_q, a_s, b_q, b_s, offs = _case([100, 156], 256, 512, seed=6, mn_major=False)
+    o1 = _run(a_q, a_s, b_q, b_s, offs, False, 128, "block_major")
+    o2 = _run(a_q, a_s, b_q, b_s, offs, False, 128, "row_major")
+    assert torch.equal(o1, o2)
+    g = torch.Generator().manual_seed(7)
+    a = torch.randn(256, 512, generator=g)
+    a_qr, a_sr = O.quantize_rows(a, mode="row")
+    out = _run(a_qr, a_sr, b_q, b_s, offs, False, 256)
+    mx, mean = O.rel_errors(out.float().cpu(), O.grouped_block_gemm(a_qr, a_sr, b_q, b_s, offs))
+    assert mx <= MAX_REL and mean <= MEAN_REL
+
+
+def test_rows_outside_every_group_are_left_untouched():
+    a_q, a_s, b_q, b_s, _ = _case([200], 128, 128, seed=8, mn_major=False)
+    offs = torch.tensor([10, 150], dtype=torch.int32)
+    out = _run(a_q, a_s, b_q, b_s, offs, False, 128)
+    assert torch.isnan(out[:10].float()).all() and torch.isnan(out[150:].float()).all()
+    assert not torch.isnan(out[10:150].float()).any()
+
+
+def test_malformed_offsets_are_reported():
+    ops = _ops()
+    from mlops_b200._lib import NativeError
+
+    a_q, a_s, b_q, b_s, _ = _case([128], 128, 128, seed=9, mn_major=False)
+    bad = torch.tensor([0, 4096], dtype=torch.int32)  # past the last row
+    _ = ops.grouped_gemm_fp8(a_q.to(DEV), a_s.to(DEV), b_q.to(DEV), b_s.to(DEV), bad.to(DEV))
+    with pytest.raises(NativeError):
+        ops.check_status(DEV)
+
+
+def test_repeatable_bitwise():
+    a_q, a_s, b_q, b_s, offs = _case([0, 70, 131, 15, 260], 384, 640, seed=10, mn_major=False)
+    assert torch.equal(_run(a_q, a_s, b_q, b_s, offs, False, 256), _run(a_q, a_s, b_q, b_s, offs, False, 256))
+
+
+def test_config2_shape_linearity_and_sampled_parity():
+    """BASELINE config 2 at full size (32 groups, Zipf split of 65536 rows, K=4096, N=2048):
+    sampled rows against float64, plus linearity in the activation scales
+    (gemm(2 * a_scale) == 2 * gemm(a_scale) exactly, a power-of-two factor)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    p = torch.arange(1, 33).float().pow(-1.1)
+    counts = torch.bincount(torch.multinomial(p / p.sum(), 65536, replacement=True, generator=g), minlength=32)
+    offs = _offsets(counts.tolist()).to(DEV)
+    a = torch.randn(65536, 4096, device=DEV, dtype=torch.bfloat16)
+    a_q, a_s = ops.quantize_rows(a)
+    b_q, b_s = ops.quantize_blocks(torch.randn(32, 2048, 4096, device=DEV, dtype=torch.bfloat16))
+    out = ops.grouped_gemm_fp8(a_q, a_s, b_q, b_s, offs, block_n=256)
+    doubled = ops.grouped_gemm_fp8(a_q, (a_s * 2).t().contiguous().t(), b_q, b_s, offs, block_n=256)
+    assert torch.equal(doubled.float(), out.float() * 2)
+    ops.check_status(DEV)
+    offs_cpu = offs.cpu().tolist()
+    for group in (0, 5, 31):
+        lo, hi = offs_cpu[group], offs_cpu[group + 1]
+        if hi == lo:
+            continue
+        rows = slice(lo, min(hi, lo + 64))
+        ref = O.grouped_block_gemm(
+            a_q[rows].cpu(), a_s[rows].cpu(), b_q[group:group + 1].cpu(), b_s[group:group + 1].cpu(),
+            torch.tensor([0, rows.stop - rows.start], dtype=torch.int32),
+        )
+        mx, mean = O.rel_errors(out[rows].float().cpu(), ref)
+        assert mx <= MAX_REL and mean <= MEAN_REL
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize(
+    "counts,m,n",
+    [([64], 128, 256), ([128, 64], 128, 256), ([0, 70, 131, 15, 260], 256, 512),
+     ([0, 70, 131, 15, 260], 384, 320), ([1000, 3, 0, 500], 1024, 768)],
+)
+def test_wgrad(counts, m, n, out_dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + n)
+    rows, groups = sum(counts), len(counts)
+    grad = torch.randn(rows, m, generator=g).bfloat16()
+    x = torch.randn(rows, n, generator=g).bfloat16()
+    offs = _offsets(counts)
+    out = ops.grouped_wgrad(grad.to(DEV), x.to(DEV), offs.to(DEV), groups, out_dtype)
+    ops.check_status(DEV)
+    ref = O.grouped_wgrad(grad, x, offs, groups)
+    for e, count in enumerate(counts):
+        if count == 0:
+            assert int(torch.count_nonzero(out[e])) == 0      # exact zeros for an empty expert
+        else:
+            mx, mean = O.rel_errors(out[e].float().cpu(), ref[e])
+            assert mx <= (1e-5 if out_dtype == torch.float32 else MAX_REL), mx
+            assert mean <= (1e-6 if out_dtype == torch.float32 else MEAN_REL), mean

@@ -1,0 +1,122 @@
+"""Parity of the quantisers, SwiGLU rows and combine kernels through the C ABI: E4M3 bytes
+and fp32 scales bit-exact against the oracle and the reference's fixtures."""
+
+import pytest
+import torch
+
+import inputs
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+U8 = torch.uint8
+
+
+def _ops():
+    from mlops_b200 import ops
+
+    return ops
+
+
+def test_weight_blocks_match_reference_fixture(golden):
+    ops = _ops()
+    fixture = golden("quantize.pt")
+    w = inputs.block_weight()
+    for name, value in (("w_fp32", w), ("w_bf16", w.bfloat16())):
+        data, scale = ops.quantize_blocks(value.to(DEV))
+        assert torch.equal(data.cpu().view(U8), fixture[name + "_data"])
+        assert torch.equal(scale.cpu(), fixture[name + "_scale"])
+
+
+def test_row_quantiser_matches_reference_fixture(golden):
+    ops = _ops()
+    fixture = golden("quantize.pt")
+    x, gather = inputs.activation_rows()
+    data, scale = ops.quantize_rows(x.to(DEV), gather=gather.to(DEV), gather_div=1, mode="row")
+    assert torch.equal(data.cpu().view(U8), fixture["rows_data"])
+    assert torch.equal(scale.cpu()[:, 0], fixture["rows_scale"])
+
+
+@pytest.mark.parametrize("rows,width", [(300, 256), (64, 192), (1000, 7168), (33, 2048), (7, 8)])
+@pytest.mark.parametrize("mode", ["1x128", "row"])
+def test_quantize_rows_bit_exact(rows, width, mode):
+    ops = _ops()
+    g = torch.Generator().manual_seed(rows + width)
+    x = torch.randn(rows, width, generator=g).bfloat16()
+    x[0] = 0                     # all-zero row keeps the 1e-12 floor
+    x[rows // 2] *= 30000        # values that saturate nothing after scaling
+    gather = torch.randint(0, rows, (2 * rows,), generator=g).to(torch.int32)
+    q_ref, s_ref = O.quantize_rows(x, gather=torch.div(gather, 2, rounding_mode="floor"), mode=mode)
+    q, s = ops.quantize_rows(x.to(DEV), gather=gather.to(DEV), gather_div=2, mode=mode)
+    assert torch.equal(q.cpu().view(U8), q_ref.view(U8))
+    assert torch.equal(s.cpu(), s_ref)
+    q2, s2 = ops.quantize_rows(x.to(DEV), mode=mode)  # no gather
+    q2_ref, s2_ref = O.quantize_rows(x, mode=mode)
+    assert torch.equal(q2.cpu().view(U8), q2_ref.view(U8)) and torch.equal(s2.cpu(), s2_ref)
+
+
+def test_quantize_rows_empty():
+    ops = _ops()
+    q, s = ops.quantize_rows(torch.zeros(0, 256, dtype=torch.bfloat16, device=DEV))
+    assert q.shape == (0, 256) and s.shape == (0, 2)
+
+
+@pytest.mark.parametrize("rows,width", [(100, 512), (77, 640), (50, 80)])
+@pytest.mark.parametrize("limit", [None, 1.5])
+def test_swiglu_quantize(rows, width, limit):
+    """fp32 SwiGLU differs from the CPU's by an ulp of expf at most, which can move a value
+    across an E4M3 rounding boundary: bytes must agree on all but a 1e-3 fraction, and the
+    bf16 activation within bf16 rounding."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(rows)
+    h = (torch.randn(rows, 2 * width, generator=g) * 2).bfloat16()
+    act = O.swiglu(h, limit)
+    q_ref, s_ref = O.quantize_rows(act, mode="1x128")
+    q, s, a16 = ops.swiglu_quantize(h.to(DEV), limit=limit, quantized=True, rounded=True)
+    same = (q.cpu().view(U8) == q_ref.view(U8)).float().mean().item()
+    assert same > 0.999
+    torch.testing.assert_close(s.cpu(), s_ref, rtol=1e-6, atol=0)
+    mx, mean = O.rel_errors(a16.float().cpu(), act)
+    assert mx <= 2e-2 and mean <= 2e-3
+
+
+@pytest.mark.parametrize("limit", [None, 1.5])
+def test_dswiglu_routed(limit):
+    ops = _ops()
+    g = torch.Generator().manual_seed(11)
+    rows, width = 90, 256
+    h = (torch.randn(rows, 2 * width, generator=g) * 2).bfloat16()
+    r = torch.randn(rows, width, generator=g).bfloat16()
+    route_weights = torch.rand(rows, generator=g)
+    order = torch.randperm(rows, generator=g).to(torch.int32)
+    ds_ref, gh_ref, as_ref = O.dswiglu_routed(h, r, route_weights[order.long()], limit)
+    ds, gq, gs, gb, a_s = ops.dswiglu_routed(
+        h.to(DEV), r.to(DEV), route_weights.to(DEV), order.to(DEV), limit=limit, quantized=True,
+        rounded=True, scaled_activation=True,
+    )
+    torch.testing.assert_close(ds.cpu(), ds_ref, rtol=1e-5, atol=1e-5)
+    for actual, expected in ((gb, gh_ref), (a_s, as_ref)):
+        mx, mean = O.rel_errors(actual.float().cpu(), expected)
+        assert mx <= 2e-2 and mean <= 2e-3
+    q_ref, s_ref = O.quantize_rows(gh_ref, mode="1x128")
+    torch.testing.assert_close(gs.cpu(), s_ref, rtol=1e-5, atol=0)
+    assert (gq.cpu().view(U8) == q_ref.view(U8)).float().mean().item() > 0.995
+
+
+def test_combine_matches_reference_fixture_and_oracle(golden):
+    ops = _ops()
+    fixture = golden("combine.pt")
+    out = ops.combine(*(fixture[k].to(DEV) for k in ("source", "slots", "weights", "residual")))
+    assert torch.equal(out.cpu(), O.combine(fixture["source"], fixture["slots"], fixture["weights"], fixture["residual"]))
+    torch.testing.assert_close(out.cpu().float(), fixture["output"].float(), rtol=2 ** -7, atol=1e-6)
+    g = torch.Generator().manual_seed(3)
+    tokens, top_k, width = 200, 4, 384
+    src = torch.randn(tokens * top_k, width, generator=g).bfloat16()
+    slots = torch.randperm(tokens * top_k, generator=g).view(tokens, top_k).to(torch.int32)
+    again = ops.dispatch_backward(src.to(DEV), slots.to(DEV))
+    assert torch.equal(again.cpu(), O.combine(src, slots, None, None))
+    assert torch.equal(again, ops.dispatch_backward(src.to(DEV), slots.to(DEV)))  # repeatable
+    order = torch.randperm(tokens * top_k, generator=g).to(torch.int32)
+    x = torch.randn(tokens, width, generator=g).bfloat16()
+    rows = ops.dispatch(x.to(DEV), order.to(DEV), top_k)
+    assert torch.equal(rows.cpu(), x[order.long() // top_k])

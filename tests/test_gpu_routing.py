@@ -1,0 +1,110 @@
+"""Parity of the routing / permutation kernels, called through the C ABI on a B200:
+expert ids, order, offsets, slots and counts bit-exact; route weights within fp32 rounding."""
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ops():
+    from mlops_b200 import ops
+
+    return ops
+
+
+def test_route_matches_reference_fixtures(golden):
+    ops = _ops()
+    for case in golden("routing.pt"):
+        bias = None if case["bias"] is None else case["bias"].to(DEV)
+        weights, ids = ops.route_topk(
+            case["logits"].to(DEV), case["top_k"], case["mode"], bias=bias, n_group=case["n_group"],
+            topk_group=case["topk_group"], routed_scaling=case["scaling"],
+        )
+        assert torch.equal(ids.cpu(), case["ids"]), case["mode"]
+        torch.testing.assert_close(weights.cpu(), case["weights"], rtol=2e-6, atol=1e-7)
+        order, offsets, slots, counts = ops.sort_assignments(case["ids"].to(DEV), case["logits"].shape[1])
+        assert torch.equal(order.cpu(), case["order"])
+        assert torch.equal(offsets.cpu(), case["offsets"])
+        assert torch.equal(slots.cpu(), case["slots"])
+        assert torch.equal(counts.cpu(), case["counts"])
+    ops.check_status(DEV)
+
+
+@pytest.mark.parametrize(
+    "tokens,experts,top_k,mode,n_group,topk_group",
+    [
+        (4096, 8, 2, "softmax_then_topk", 1, 1),
+        (4096, 128, 8, "softmax_then_topk", 1, 1),
+        (4096, 256, 8, "sigmoid_noaux_tc", 8, 4),
+        (2048, 256, 8, "topk_then_softmax", 1, 1),
+        (1000, 96, 4, "sigmoid_noaux_tc", 8, 3),
+        (1, 8, 8, "softmax_then_topk", 1, 1),
+    ],
+)
+def test_route_ids_bit_exact_on_seeded_logits(tokens, experts, top_k, mode, n_group, topk_group):
+    """Seeded fp32 logits fed to both sides; a row whose ids differ must be a genuine
+    near-tie (counted and reported), and none is tolerated on these seeds."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(tokens + experts)
+    logits = torch.randn(tokens, experts, generator=g)
+    bias = torch.randn(experts, generator=g) * 0.1 if mode == "sigmoid_noaux_tc" else None
+    w_ref, id_ref = O.route(logits, top_k, mode, bias=bias, n_group=n_group, topk_group=topk_group,
+                            routed_scaling=2.5)
+    w, ids = ops.route_topk(logits.to(DEV), top_k, mode, bias=None if bias is None else bias.to(DEV),
+                            n_group=n_group, topk_group=topk_group, routed_scaling=2.5)
+    flipped = (ids.cpu() != id_ref).any(1).sum().item()
+    assert flipped == 0, f"{flipped} of {tokens} rows selected different experts"
+    torch.testing.assert_close(w.cpu(), w_ref, rtol=2e-6, atol=1e-7)
+
+
+def test_sort_at_full_size_is_a_stable_permutation():
+    """Config 5 size (T*K = 524288, E = 128, Zipf-skewed ids): bit-exact against the oracle and
+    the size-independent properties (permutation, sortedness, stability, inverse)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    experts = 128
+    p = torch.arange(1, experts + 1).float().pow(-1.2)
+    ids = torch.multinomial(p / p.sum(), 65536 * 8, replacement=True, generator=g).to(torch.int32).view(65536, 8)
+    order, offsets, slots, counts = ops.sort_assignments(ids.to(DEV), experts)
+    o_ref, f_ref, s_ref = O.sort_assignments(ids, experts)
+    assert torch.equal(order.cpu(), o_ref) and torch.equal(offsets.cpu(), f_ref) and torch.equal(slots.cpu(), s_ref)
+    order_l = order.long()
+    flat = ids.reshape(-1).to(DEV)
+    sorted_ids = flat[order_l]
+    assert bool((sorted_ids[1:] >= sorted_ids[:-1]).all())                         # sortedness
+    same = sorted_ids[1:] == sorted_ids[:-1]
+    assert bool((order_l[1:][same] > order_l[:-1][same]).all())                    # stability
+    assert torch.equal(torch.sort(order_l).values, torch.arange(flat.numel(), device=DEV))  # permutation
+    assert torch.equal(slots.reshape(-1).long()[order_l], torch.arange(flat.numel(), device=DEV))  # inverse
+    assert int(counts.sum()) == flat.numel()
+    ops.check_status(DEV)
+
+
+def test_sort_edge_cases():
+    ops = _ops()
+    # every assignment on one expert; experts without rows; a single assignment
+    for ids, experts in (
+        (torch.full((300, 2), 3, dtype=torch.int32), 8),
+        (torch.tensor([[0, 7]], dtype=torch.int32), 8),
+        (torch.tensor([[5]], dtype=torch.int32), 6),
+    ):
+        order, offsets, slots, counts = ops.sort_assignments(ids.to(DEV), experts)
+        o_ref, f_ref, s_ref = O.sort_assignments(ids, experts)
+        assert torch.equal(order.cpu(), o_ref) and torch.equal(offsets.cpu(), f_ref)
+        assert torch.equal(slots.cpu(), s_ref)
+    ops.check_status(DEV)
+
+
+def test_out_of_range_expert_id_is_reported_not_written():
+    ops = _ops()
+    from mlops_b200._lib import NativeError
+
+    ids = torch.tensor([[0, 9]], dtype=torch.int32, device=DEV)  # 9 >= experts
+    ops.sort_assignments(ids, 8)
+    with pytest.raises(NativeError):
+        ops.check_status(DEV)
+    ops.check_status(DEV)  # the block was cleared
