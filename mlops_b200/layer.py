@@ -277,3 +277,34 @@ def backward_routed(
             grad_router = torch.empty(0, dtype=router_weight.dtype, device=h2.device)
         grad_h2.addmm_(grad_logits.to(h2_flat.dtype), router_operand.to(h2_flat.dtype))
     return (grad_h2.reshape(original_shape), grad_output.clone(), grad_router, grad_w13, grad_w2)
+
+
+# ------------------------------------------------------------------------ shared expert
+def shared_expert_forward(h2_flat, shared_w13, shared_w2, *, swiglu_limit=None):
+    """The always-on shared expert: `W2s . swiglu(W13s . x)` with bf16 dense library GEMMs
+    (the reference never quantises it: src/mlops/moe.py:12-37, docs/EXPERT_PARALLEL.md) and
+    this library's SwiGLU kernel in between. Returns `(y [T, D], h13 [T, 2Fs])`; h13 is the
+    residual its backward needs."""
+    with torch.no_grad():
+        h13 = h2_flat @ shared_w13.t()
+        _, _, act = ops.swiglu_quantize(h13, limit=swiglu_limit, quantized=False, rounded=True)
+        return act @ shared_w2.t(), h13
+
+
+def shared_expert_backward(grad_y, h2_flat, shared_w13, shared_w2, h13, *, swiglu_limit=None,
+                           need_weights=True):
+    """VJP of `shared_expert_forward`: `(grad_h2, grad_w13, grad_w2)` (weights' entries are
+    None when not needed)."""
+    with torch.no_grad():
+        rows = h2_flat.shape[0]
+        r = grad_y @ shared_w2
+        ones = torch.ones(rows, dtype=torch.float32, device=h2_flat.device)
+        identity = torch.arange(rows, dtype=torch.int32, device=h2_flat.device)
+        _, _, _, grad_h13, act = ops.dswiglu_routed(
+            h13, r, ones, identity, limit=swiglu_limit, quantized=False, rounded=True,
+            scaled_activation=need_weights,
+        )
+        grad_h2 = grad_h13 @ shared_w13
+        if not need_weights:
+            return grad_h2, None, None
+        return grad_h2, grad_h13.t() @ h2_flat, grad_y.t() @ act

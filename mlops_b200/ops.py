@@ -167,6 +167,8 @@ def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128"):
     q = torch.empty((rows, width), dtype=FP8, device=x.device)
     blocks = (width + 127) // 128 if mode == "1x128" else 1
     scales = _scale_buffer(rows, blocks, x.device)
+    if rows == 0:
+        return q, scales
     check(
         lib.b200moe_quantize_rows(
             x.data_ptr(), x.stride(0), _ptr(gather), int(gather_div), rows, width, q.data_ptr(),
@@ -192,6 +194,8 @@ def swiglu_quantize(h13, *, limit=None, quantized=True, rounded=False):
         scales = _scale_buffer(rows, (width + 127) // 128, device)
     if rounded:
         act = torch.empty((rows, width), dtype=torch.bfloat16, device=device)
+    if rows == 0:
+        return act_q, scales, act
     check(
         lib.b200moe_swiglu_quantize(
             h13.data_ptr(), h13.stride(0), rows, width, _ptr(act_q), width, _ptr(scales),
@@ -223,6 +227,8 @@ def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, 
     if scaled_activation:
         a_s = torch.empty((rows, width), dtype=torch.bfloat16, device=device)
     weights_flat = route_weights.reshape(-1)
+    if rows == 0:
+        return dscore, gq, gs, gb, a_s
     check(
         lib.b200moe_dswiglu_routed(
             h13.data_ptr(), h13.stride(0), r.data_ptr(), r.stride(0), weights_flat.data_ptr(),
@@ -287,6 +293,8 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
         raise NativeError("a_scale must have 1 or ceil(K/128) columns")
     if out is None:
         out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
+    if rows == 0:
+        return out
     with _Timed("fp8", 2.0 * rows * n * k):
         check(
             lib.b200moe_grouped_gemm_fp8(
@@ -308,6 +316,8 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
     n = x.shape[1]
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise NativeError("weight gradients are written as bf16 or fp32")
+    if rows == 0:
+        return torch.zeros((groups, m, n), dtype=out_dtype, device=device)
     out = torch.empty((groups, m, n), dtype=out_dtype, device=device)
     with _Timed("wgrad_bf16", 2.0 * rows * m * n):
         check(
@@ -329,6 +339,8 @@ def combine(source, slots, weights, residual):
     tokens, top_k = slots.shape
     width = source.shape[1]
     out = torch.empty((tokens, width), dtype=torch.bfloat16, device=device)
+    if tokens == 0:
+        return out
     check(
         lib.b200moe_combine(
             source.data_ptr(), source.stride(0), source.shape[0], slots.data_ptr(), _ptr(weights),
@@ -351,6 +363,8 @@ def dispatch(x, order, top_k):
     device = _need_cuda(x, order)
     rows = order.numel()
     out = torch.empty((rows, x.shape[1]), dtype=torch.bfloat16, device=device)
+    if rows == 0:
+        return out
     check(
         lib.b200moe_gather_rows(
             x.data_ptr(), x.stride(0), order.data_ptr(), int(top_k), rows, x.shape[1],

@@ -261,7 +261,7 @@ def router_logits(h2, router_weight, operand_dtype=torch.bfloat16):
 
 def forward_block_fp8(h2, residual, logits, w13_q, w13_s, w2_q, w2_s, *, top_k, routing_mode,
                       router_bias=None, n_group=1, topk_group=1, routed_scaling=1.0,
-                      swiglu_limit=None, act_scale="1x128"):
+                      swiglu_limit=None, act_scale="1x128", gemm_dtype=torch.float64):
     """The routed layer with quantised activations ("identical block-FP8 operands"):
     route -> sort -> gather+quantise -> up GEMM (bf16 h13, gate rows then up rows) ->
     SwiGLU (fp32) -> quantise -> down GEMM (bf16 rows) -> combine.
@@ -274,17 +274,17 @@ def forward_block_fp8(h2, residual, logits, w13_q, w13_s, w2_q, w2_s, *, top_k, 
     order, offsets, slots = sort_assignments(ids, experts)
     token_of_row = torch.div(order.long(), int(top_k), rounding_mode="floor")
     x_q, x_s = quantize_rows(h2, gather=token_of_row, mode=act_scale)
-    h13 = grouped_block_gemm(x_q, x_s, w13_q, w13_s, offsets).to(torch.bfloat16)
+    h13 = grouped_block_gemm(x_q, x_s, w13_q, w13_s, offsets, dtype=gemm_dtype).to(torch.bfloat16)
     act = swiglu(h13, swiglu_limit)
     a_q, a_s = quantize_rows(act, mode=act_scale)
-    y = grouped_block_gemm(a_q, a_s, w2_q, w2_s, offsets).to(torch.bfloat16)
+    y = grouped_block_gemm(a_q, a_s, w2_q, w2_s, offsets, dtype=gemm_dtype).to(torch.bfloat16)
     output = combine(y, slots, weights, residual)
     return dict(weights=weights, ids=ids, order=order, offsets=offsets, slots=slots, x_q=x_q,
                 x_s=x_s, h13=h13, a_q=a_q, a_s=a_s, y=y, output=output)
 
 
 def backward_block_fp8(grad_output, h2, fwd, w13_q, w13_s, w2_q, w2_s, *, top_k, swiglu_limit=None,
-                       act_scale="1x128"):
+                       act_scale="1x128", gemm_dtype=torch.float64):
     """VJP of `forward_block_fp8` for (h2 routed part, route weights, w13, w2), FP8 input
     gradients and bf16-operand weight gradients (as the reference's fp8_block form:
     src/mlops/providers/sonicmoe/moe.py:517-619, providers/sonicmoe/fp8.py:15-17).
@@ -293,17 +293,18 @@ def backward_block_fp8(grad_output, h2, fwd, w13_q, w13_s, w2_q, w2_s, *, top_k,
     order, offsets, slots, weights = fwd["order"], fwd["offsets"], fwd["slots"], fwd["weights"]
     token_of_row = torch.div(order.long(), int(top_k), rounding_mode="floor")
     dy_q, dy_s = quantize_rows(grad_output, gather=token_of_row, mode=act_scale)
-    r = grouped_block_gemm(dy_q, dy_s, w2_q, w2_s, offsets, b_mn_major=True).to(torch.bfloat16)
+    r = grouped_block_gemm(dy_q, dy_s, w2_q, w2_s, offsets, b_mn_major=True, dtype=gemm_dtype).to(torch.bfloat16)
     score = weights.reshape(-1)[order.long()].float()
     dscore, grad_h13, act_scaled = dswiglu_routed(fwd["h13"], r, score, swiglu_limit)
     grad_route_weights = dscore[slots.reshape(-1).long()].view_as(weights)
     gh_q, gh_s = quantize_rows(grad_h13, mode=act_scale)
-    grad_rows = grouped_block_gemm(gh_q, gh_s, w13_q, w13_s, offsets, b_mn_major=True).to(torch.bfloat16)
+    grad_rows = grouped_block_gemm(gh_q, gh_s, w13_q, w13_s, offsets, b_mn_major=True,
+                                   dtype=gemm_dtype).to(torch.bfloat16)
     grad_h2 = combine(grad_rows, slots, None, None)
     dy_rows = grad_output[token_of_row].to(torch.bfloat16)
     x_rows = h2[token_of_row].to(torch.bfloat16)
-    grad_w2 = grouped_wgrad(dy_rows, act_scaled.to(torch.bfloat16), offsets, experts)
-    grad_w13 = grouped_wgrad(grad_h13.to(torch.bfloat16), x_rows, offsets, experts)
+    grad_w2 = grouped_wgrad(dy_rows, act_scaled.to(torch.bfloat16), offsets, experts, gemm_dtype)
+    grad_w13 = grouped_wgrad(grad_h13.to(torch.bfloat16), x_rows, offsets, experts, gemm_dtype)
     return dict(r=r, dscore=dscore, grad_route_weights=grad_route_weights, grad_h13=grad_h13,
                 grad_rows=grad_rows, grad_h2=grad_h2, grad_w2=grad_w2, grad_w13=grad_w13)
 

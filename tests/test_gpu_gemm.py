@@ -71,7 +71,8 @@ def test_integer_operands_are_exact(block_n, mn_major):
         b_q = b_q.view(torch.uint8).transpose(1, 2).contiguous().view(FP8)
         b_s = b_s.transpose(1, 2).contiguous()
     out = _run(a_q, a_s, b_q, b_s, offs, mn_major, block_n)
-    assert torch.equal(out.float().cpu().double(), ref)
+    # integer products and sums are exact in fp32; only the bf16 store rounds
+    assert torch.equal(out.cpu(), ref.float().bfloat16())
 
 
 @pytest.mark.parametrize("block_n", [128, 256])
