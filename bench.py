@@ -13,6 +13,8 @@ workload on this machine's host cores. `--impl reference` times that CPU path al
 Workloads (shapes only; weights are random, data synthetic, seeded):
   c4  DeepSeek-V3-shaped: D=7168, 256 experts, F=2048, sigmoid/group top-8, one shared expert,
       T=32768 tokens per GPU (the configuration the headline metric is quoted on)
+  c4p the same layer at profiling size (32 experts, T=4096: the same 1024 rows per expert,
+      a few GB on the device) for ncu captures
   c3  Mixtral-8x7B-shaped: D=4096, 8 experts, F=14336, softmax top-2, T=16384
   c1  the small CPU-runnable case: D=256, 8 experts, F=512, softmax top-2, T=512
 """
@@ -37,6 +39,8 @@ sys.path.insert(0, str(ROOT))
 WORKLOADS = {
     "c4": dict(name="deepseek_v3_shaped_moe_layer", T=32768, D=7168, E=256, F=2048, K=8,
                mode="sigmoid_noaux_tc", n_group=8, topk_group=4, scaling=2.5, shared=True),
+    "c4p": dict(name="deepseek_v3_shaped_moe_layer_profile_size", T=4096, D=7168, E=32, F=2048, K=8,
+                mode="sigmoid_noaux_tc", n_group=8, topk_group=4, scaling=2.5, shared=True),
     "c3": dict(name="mixtral_8x7b_shaped_moe_layer", T=16384, D=4096, E=8, F=14336, K=2,
                mode="softmax_then_topk", n_group=1, topk_group=1, scaling=1.0, shared=False),
     "c1": dict(name="small_moe_layer", T=512, D=256, E=8, F=512, K=2,

@@ -242,6 +242,24 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Packed fp32 pairs (Blackwell fma.rn.f32x2: two fused multiply-adds per instruction).
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
+  return v;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  return pack_u32x2(__float_as_uint(lo), __float_as_uint(hi));
+}
+// acc = a * b + acc, element-wise on two packed fp32 values
+__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint64_t a, uint64_t b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(uint64_t packed) {
+  uint32_t lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(packed));
+  return pack_bf16x2(__uint_as_float(lo), __uint_as_float(hi));
+}
 // RN-even conversion to E4M3 with saturation to +-448 (finite).
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);

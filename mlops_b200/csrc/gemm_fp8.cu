@@ -28,6 +28,7 @@ constexpr int kMaxGroups = 1024;
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 128;  // bytes == elements for E4M3
 constexpr int kGemmThreads = 384;
+constexpr int kScaleBatch = 4;  // K blocks of scales fetched ahead by the epilogue
 
 struct GemmFp8Params {
   const float* a_scale;
@@ -167,8 +168,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // The wide tile keeps 128 fp32 sums per epilogue thread: registers move from the
   // producer warpgroup (warps 0-3) to the two epilogue warpgroups.  Each role adjusts
   // its own limit at the top of its branch so the branches never merge in between.
-#define B200_REG_DEC() do { if constexpr (BLOCK_N == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); } while (0)
-#define B200_REG_INC() do { if constexpr (BLOCK_N == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); } while (0)
+#define B200_REG_DEC() do { if constexpr (BLOCK_N == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); } while (0)
+#define B200_REG_INC() do { if constexpr (BLOCK_N == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); } while (0)
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -253,46 +254,90 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------- epilogue --------------------------------
     B200_REG_INC();
     constexpr int kCols = BLOCK_N / 2;  // columns owned by one thread
+    constexpr int kChunks = kCols / 32;
     const int q = warp & 3;             // TMEM lane quarter this warp may read
     const int half = (warp - 4) >> 2;   // which half of the tile's columns
     const int row_in_tile = q * 32 + lane;
     float acc[kCols];
     uint32_t ab = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+
+    // Everything the epilogue needs to know about one tile.
+    struct EpiTile {
+      int rows_valid, grow, col0;
+      const float* as_ptr;
+      const float* bs_ptr;
+    };
+    auto describe = [&](int t) {
+      EpiTile e;
       const int mt = t / num_n_tiles;
       const int n0 = (t - mt * num_n_tiles) * BLOCK_N;
       const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
-      const int grow = c.m0 + row_in_tile;
-      const int srow = min(grow, p.rows_total - 1);
-      const float* as_ptr = p.a_scale + (long long)srow * p.as_row_stride;
-      const int col0 = n0 + half * kCols;
-      const float* bs_ptr = p.b_scale + (long long)c.group * p.bs_group_stride +
-                            (long long)min(col0 / 128, (p.N - 1) / 128) * p.bs_n_stride;
+      e.rows_valid = c.rows_valid;
+      e.grow = c.m0 + row_in_tile;
+      e.col0 = n0 + half * kCols;
+      e.as_ptr = p.a_scale + (long long)min(e.grow, p.rows_total - 1) * p.as_row_stride;
+      e.bs_ptr = p.b_scale + (long long)c.group * p.bs_group_stride +
+                 (long long)min(e.col0 / 128, (p.N - 1) / 128) * p.bs_n_stride;
+      return e;
+    };
+    // The two scales of a K block come from global memory.  They are fetched one batch of
+    // kScaleBatch K blocks ahead -- across the tile boundary too -- so their latency never
+    // sits between two K blocks.
+    float sa_cur[kScaleBatch], sb_cur[kScaleBatch], sa_nxt[kScaleBatch], sb_nxt[kScaleBatch];
+    auto fetch = [&](const EpiTile& e, int kb0, float (&sa)[kScaleBatch], float (&sb)[kScaleBatch]) {
+#pragma unroll
+      for (int u = 0; u < kScaleBatch; ++u) {
+        const int kk = min(kb0 + u, num_kb - 1);
+        sa[u] = e.as_ptr[(long long)kk * p.as_kb_stride];
+        sb[u] = e.bs_ptr[(long long)kk * p.bs_k_stride];
+      }
+    };
+    EpiTile cur_tile, nxt_tile;
+    if ((int)blockIdx.x < total_tiles) {
+      cur_tile = describe(blockIdx.x);
+      fetch(cur_tile, 0, sa_cur, sb_cur);
+    }
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const bool has_next = t + (int)gridDim.x < total_tiles;
+      if (has_next) nxt_tile = describe(t + gridDim.x);
+      const EpiTile c = cur_tile;
+      const int grow = c.grow;
+      const int col0 = c.col0;
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
-      float s_next = as_ptr[0] * bs_ptr[0];
-      for (int kb = 0; kb < num_kb; ++kb, ++ab) {
-        const float s = s_next;
-        if (kb + 1 < num_kb)
-          s_next = as_ptr[(long long)(kb + 1) * p.as_kb_stride] * bs_ptr[(long long)(kb + 1) * p.bs_k_stride];
-        const int buf = ab & 1;
-        const uint32_t aph = (ab >> 1) & 1;
-        if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N + half * kCols;
+      for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kScaleBatch) {
+        if (kb0 + kScaleBatch < num_kb) fetch(c, kb0 + kScaleBatch, sa_nxt, sb_nxt);
+        else if (has_next) fetch(nxt_tile, 0, sa_nxt, sb_nxt);
 #pragma unroll
-        for (int cc = 0; cc < kCols / 32; ++cc) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + cc * 32, r);
-          tmem_ld_wait();
+        for (int u = 0; u < kScaleBatch; ++u) {
+          if (kb0 + u >= num_kb) break;
+          const float s = sa_cur[u] * sb_cur[u];
+          const int buf = ab & 1;
+          const uint32_t aph = (ab >> 1) & 1;
+          ++ab;
+          if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N + half * kCols;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(s, __uint_as_float(r[j]), acc[cc * 32 + j]);
+          for (int cc = 0; cc < kChunks; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(s, __uint_as_float(r[j]), acc[cc * 32 + j]);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[buf]);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[buf]);
+#pragma unroll
+        for (int u = 0; u < kScaleBatch; ++u) {
+          sa_cur[u] = sa_nxt[u];
+          sb_cur[u] = sb_nxt[u];
+        }
       }
+      cur_tile = nxt_tile;
       if (!ok) break;
       if (row_in_tile < c.rows_valid) {
         __nv_bfloat16* drow = p.d + (long long)grow * p.ldd + col0;
