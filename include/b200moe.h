@@ -68,6 +68,22 @@ int b200moe_sort_assignments(const int32_t* ids, long long assignments, int expe
                              int32_t* status, void* stream);
 
 /*
+ * b200moe_sort_assignments without a workspace argument, for callers that cannot allocate
+ * one (a process whose own arena owns all device memory; a call site where cudaMalloc, which
+ * may synchronise the device, must not run).  The scratch is a 1 MiB array inside the library
+ * image, resident on every GPU that loads the library until exit.  Same outputs as
+ * b200moe_sort_assignments.  Limit: ceil(assignments / 4096) * experts <= 262144, else
+ * B200MOE_ERR_LIMIT.  No allocation of any kind happens here.  The first call on a device
+ * resolves the array's address and should be made outside stream capture.  All calls share
+ * the array (its old contents are overwritten before they are read, nothing needs clearing);
+ * calls that overlap on the GPU race, so keep them ordered on one stream.
+ * This entry point has no counterpart in the reference.
+ */
+int b200moe_sort_assignments_static(const int32_t* ids, long long assignments, int experts,
+                                    int32_t* order, int32_t* offsets, int32_t* slots,
+                                    long long* counts64, int32_t* status, void* stream);
+
+/*
  * E4M3 quantisation of bf16 rows, optionally gathered: output row r reads input row
  * gather[r] / gather_div (gather may be NULL: row r).  q is [rows, width] bytes with
  * byte pitch ldq; scale of (row r, block b) is written to

@@ -337,6 +337,12 @@ extern "C" long long b200moe_sort_assignments_workspace_bytes(long long assignme
   return (nchunks > 0 ? nchunks : 1) * (long long)experts * 4;
 }
 
+// The launches of the sort, shared by the entry point that takes a caller workspace and the
+// one that uses the library's own static scratch.
+static int launch_sort(const int32_t* ids, int R, int experts, int32_t* order, int32_t* offsets,
+                       int32_t* slots, long long* counts64, int* chunk_hist, int32_t* status,
+                       cudaStream_t s);
+
 extern "C" int b200moe_sort_assignments(const int32_t* ids, long long assignments, int experts,
                                         int32_t* order, int32_t* offsets, int32_t* slots,
                                         long long* counts64, void* workspace, int32_t* status,
@@ -344,10 +350,14 @@ extern "C" int b200moe_sort_assignments(const int32_t* ids, long long assignment
   if (!ids || !order || !offsets || !slots || !workspace || !status) return B200MOE_ERR_ARG;
   if (assignments < 0 || experts <= 0) return B200MOE_ERR_ARG;
   if (experts > 1024 || assignments > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int R = (int)assignments;
+  return launch_sort(ids, (int)assignments, experts, order, offsets, slots, counts64,
+                     reinterpret_cast<int*>(workspace), status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+static int launch_sort(const int32_t* ids, int R, int experts, int32_t* order, int32_t* offsets,
+                       int32_t* slots, long long* counts64, int* chunk_hist, int32_t* status,
+                       cudaStream_t s) {
   const int nchunks = (R + kSortChunk - 1) / kSortChunk;
-  int* chunk_hist = reinterpret_cast<int*>(workspace);
   if (nchunks > 0) {
     sort_hist_kernel<<<nchunks, kSortThreads, experts * 4, s>>>(ids, R, experts, chunk_hist, status);
   }
@@ -357,4 +367,63 @@ extern "C" int b200moe_sort_assignments(const int32_t* ids, long long assignment
                                                                               offsets, order, slots);
   }
   return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// b200moe_sort_assignments_static: the same sort for callers that cannot obtain a workspace.
+//
+// Some hosts of this library have no allocator to offer: a serving process that handed all
+// of HBM to its own arena at start-up, or a call site (a driver callback, a latency-critical
+// loop) where cudaMalloc is off limits because it may synchronise the whole device.  For them
+// the per-chunk histogram lives in a fixed 1 MiB array that is part of the library image, so
+// this entry point allocates nothing and calls no allocating routine.  The price: every GPU
+// that loads the library carries the array until the process exits, the problem size is
+// capped (chunks * experts <= 262144 ints, chunks = ceil(assignments / 4096)), and all calls
+// share the one array.  The array keeps whatever the previous call left in it; that is
+// harmless because the histogram pass rewrites every entry the later passes read, so nothing
+// has to start at zero.  Two calls whose kernels overlap on the GPU (different streams,
+// several host threads) would race on the array: keep calls on one stream or order them.
+//
+// The array's device address is looked up on the first call made with a given device
+// current (cudaGetSymbolAddress); make that first call outside any stream capture.
+// ---------------------------------------------------------------------------
+namespace b200 {
+constexpr long long kStaticSortInts = 262144;  // 1 MiB
+static __device__ __align__(256) int g_sort_scratch[kStaticSortInts];
+}  // namespace b200
+
+#include <mutex>
+
+// In host code `g_sort_scratch` is only a handle for the symbol, not something a kernel can
+// dereference; the device address is looked up once per device, with that device current.
+static int static_sort_scratch(int** out) {
+  static std::mutex lock;
+  static int* address[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200MOE_ERR_ARG;
+  std::lock_guard<std::mutex> guard(lock);
+  if (address[dev] == nullptr) {
+    int* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), b200::g_sort_scratch) != cudaSuccess ||
+        ptr == nullptr)
+      return B200MOE_ERR_DRIVER;
+    address[dev] = ptr;
+  }
+  *out = address[dev];
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_sort_assignments_static(const int32_t* ids, long long assignments, int experts,
+                                               int32_t* order, int32_t* offsets, int32_t* slots,
+                                               long long* counts64, int32_t* status, void* stream) {
+  if (!ids || !order || !offsets || !slots || !status) return B200MOE_ERR_ARG;
+  if (assignments < 0 || experts <= 0) return B200MOE_ERR_ARG;
+  if (experts > 1024 || assignments > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  const long long nchunks = (assignments + kSortChunk - 1) / kSortChunk;
+  if (nchunks * experts > kStaticSortInts) return B200MOE_ERR_LIMIT;
+  int* scratch = nullptr;
+  const int rc = static_sort_scratch(&scratch);
+  if (rc != B200MOE_OK) return rc;
+  return launch_sort(ids, (int)assignments, experts, order, offsets, slots, counts64, scratch, status,
+                     reinterpret_cast<cudaStream_t>(stream));
 }

@@ -149,6 +149,26 @@ def sort_assignments(route_ids, experts):
     return order, offsets, slots.view(route_ids.shape), counts
 
 
+def sort_assignments_static(route_ids, experts, order, offsets, slots, counts):
+    """`sort_assignments` into caller-provided outputs, using the library's built-in scratch
+    instead of a workspace: for callers that cannot allocate (all device memory owned by their
+    own arena, or a call site where the CUDA allocator must not run). Nothing is allocated
+    here. Limit: ceil(assignments / 4096) * experts <= 262144. Calls share the scratch, so
+    keep them ordered on one stream; the first call on a device should happen outside stream
+    capture. `route_ids` must be contiguous int32."""
+    _need_cuda(route_ids, order, offsets, slots, counts)
+    if route_ids.dtype != torch.int32 or not route_ids.is_contiguous():
+        raise NativeError("route_ids must be contiguous int32 (no copy is made here)")
+    check(
+        lib.b200moe_sort_assignments_static(
+            route_ids.data_ptr(), route_ids.numel(), experts, order.data_ptr(), offsets.data_ptr(),
+            slots.data_ptr(), _ptr(counts), status_block(route_ids.device).data_ptr(), _stream(),
+        ),
+        "sort_assignments_static",
+    )
+    _count(3 if route_ids.numel() > 0 else 1)
+
+
 # ------------------------------------------------------------------------ quantisation
 def _scale_buffer(rows, blocks, device):
     """Scales are stored block-major ([blocks, rows]) so that the GEMM epilogue's 32
