@@ -146,25 +146,31 @@ int b200moe_quantize_blocks(const void* w, int src_is_fp32, int experts, int out
  *   block_n  128 or 256: tile width
  * Every 128-wide K block is accumulated on the tensor cores from zero and promoted in
  * fp32 by a_scale * b_scale.  N % 8 == 0, K % 16 == 0 (N % 16 for b_mn_major),
- * groups <= 1024.
+ * groups <= 1024.  `weights` is the number of weight matrices in b: group g multiplies
+ * matrix g % weights (groups must be a multiple of it), so rows that arrive as
+ * [source rank][local expert] segments need no regrouping; weights == groups is the plain case.
  * Reference: src/mlops/kernels/block_fp8.py:249-341 (`grouped_block_gemm`) and
  * src/mlops/kernels/quack_moe/block_fp8_gemm.py:1424-1484 (`block_fp8_gemm`,
  * `block_fp8_transposed_gemm`).
  */
 int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale, long long as_row_stride,
                              long long as_kb_stride, const void* b, const float* b_scale, void* d,
-                             long long ldd, const int32_t* offsets, int groups, long long rows_total,
-                             int N, int K, int b_mn_major, int block_n, int32_t* status, void* stream);
+                             long long ldd, const int32_t* offsets, int groups, int weights,
+                             long long rows_total, int N, int K, int b_mn_major, int block_n,
+                             int32_t* status, void* stream);
 
 /*
  * Grouped weight gradient: out[g] (M x N) = G[rows of g, 0:M]^T @ X[rows of g, 0:N],
  * bf16 operands (pitches ldg, ldx), fp32 sums, out [groups, M, N] contiguous in bf16 or
  * fp32 (out_is_fp32).  Groups without rows get zeros.  M % 8 == 0, N % 8 == 0.
+ * `offsets` holds segments*groups + 1 entries: group g sums over the row ranges
+ * offsets[s*groups+g] .. offsets[s*groups+g+1] for s < segments (segments == 1 is the plain
+ * expert-sorted layout; with rows laid out [source rank][local expert] it is the rank count).
  * Reference: src/mlops/kernels/moe_grouped_gemm.py:300-342 (`grouped_mm_wgrad`).
  */
 int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const void* x, long long ldx,
-                               const int32_t* offsets, int groups, long long rows_total, int M, int N,
-                               void* out, int out_is_fp32, int32_t* status, void* stream);
+                               const int32_t* offsets, int groups, int segments, long long rows_total,
+                               int M, int N, void* out, int out_is_fp32, int32_t* status, void* stream);
 
 /*
  * out[t] = residual[t] + sum_k weights[t,k] * src[slots[t,k]] (fp32 sums, k ascending, one

@@ -39,6 +39,7 @@ struct GemmFp8Params {
   long long ldd;
   const int* offsets;
   int groups, N, K, rows_total;
+  int weights;  // group g multiplies weight matrix g % weights
   int* status;
 };
 
@@ -188,12 +189,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           mbar_arrive_expect_tx(&full[s], Cfg::kABytes + Cfg::kBBytes);
           tma_load_2d(sA + s * Cfg::kABytes, &tmap_a, &full[s], kb * kBlockK, c.m0);
           if (!B_MN_MAJOR) {
-            tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], kb * kBlockK, n0, c.group);
+            tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], kb * kBlockK, n0, c.group % p.weights);
           } else {
 #pragma unroll
             for (int panel = 0; panel < BLOCK_N / 128; ++panel)
               tma_load_3d(sB + s * Cfg::kBBytes + panel * (128 * kBlockK), &tmap_b, &full[s],
-                          n0 + panel * 128, kb * kBlockK, c.group);
+                          n0 + panel * 128, kb * kBlockK, c.group % p.weights);
           }
         }
       }
@@ -277,7 +278,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       e.grow = c.m0 + row_in_tile;
       e.col0 = n0 + half * kCols;
       e.as_ptr = p.a_scale + (long long)min(e.grow, p.rows_total - 1) * p.as_row_stride;
-      e.bs_ptr = p.b_scale + (long long)c.group * p.bs_group_stride +
+      e.bs_ptr = p.b_scale + (long long)(c.group % p.weights) * p.bs_group_stride +
                  (long long)min(e.col0 / 128, (p.N - 1) / 128) * p.bs_n_stride;
       return e;
     };
@@ -395,11 +396,12 @@ using namespace b200;
 extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
                                         long long as_row_stride, long long as_kb_stride, const void* b,
                                         const float* b_scale, void* d, long long ldd,
-                                        const int32_t* offsets, int groups, long long rows_total, int N,
-                                        int K, int b_mn_major, int block_n, int32_t* status,
-                                        void* stream) {
+                                        const int32_t* offsets, int groups, int weights,
+                                        long long rows_total, int N, int K, int b_mn_major, int block_n,
+                                        int32_t* status, void* stream) {
   if (!a || !a_scale || !b || !b_scale || !d || !offsets || !status) return B200MOE_ERR_ARG;
   if (groups <= 0 || N <= 0 || K <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
+  if (weights <= 0 || groups % weights != 0) return B200MOE_ERR_ARG;
   if (groups > kMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
   if (block_n != 128 && block_n != 256) return B200MOE_ERR_ARG;
   if ((N % 8) || (K % 16) || (lda % 16) || (ldd % 8)) return B200MOE_ERR_ALIGN;
@@ -430,10 +432,11 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
   p.N = N;
   p.K = K;
   p.rows_total = (int)rows_total;
+  p.weights = weights;
   p.status = status;
   if (!b_mn_major) {
     // B is [groups, N, K], K contiguous; scales [groups, ceil(N/128), ceil(K/128)].
-    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)groups};
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)weights};
     uint64_t strides[2] = {(uint64_t)K, (uint64_t)K * (uint64_t)N};
     uint32_t box[3] = {128, (uint32_t)block_n, 1};
     int r = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box,
@@ -445,7 +448,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
   } else {
     // B is [groups, K, N], N contiguous (the stored weight read for an input gradient);
     // scales [groups, ceil(K/128), ceil(N/128)].
-    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)groups};
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)weights};
     uint64_t strides[2] = {(uint64_t)N, (uint64_t)K * (uint64_t)N};
     uint32_t box[3] = {128, 128, 1};
     int r = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box,

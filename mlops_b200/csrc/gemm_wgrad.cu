@@ -33,6 +33,7 @@ struct WgradParams {
   void* out;  // [groups, M, N]
   const int* offsets;
   int groups, M, N, rows_total;
+  int segments;  // offsets holds segments*groups+1 entries; group g owns segment ranges s*groups+g
   int* status;
 };
 
@@ -105,11 +106,12 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
 
   // Every role walks the same tile sequence and derives the same K range from `offsets`.
   // A malformed range (negative, decreasing, past the end) is treated as empty.
-  auto group_range = [&](int g, int& lo, int& hi) {
-    lo = p.offsets[g];
-    hi = p.offsets[g + 1];
+  auto group_range = [&](int g, int seg, int& lo, int& hi) {
+    const int at = seg * p.groups + g;
+    lo = p.offsets[at];
+    hi = p.offsets[at + 1];
     if (lo < 0 || hi < lo || hi > p.rows_total) {
-      report_error(p.status, ERR_BAD_OFFSETS, 20, g);
+      report_error(p.status, ERR_BAD_OFFSETS, 20, at);
       lo = hi = 0;
     }
   };
@@ -123,21 +125,23 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
         const int rem = (int)(t - (long long)g * tiles_per_group);
         const int m0 = (rem / n_tiles) * kWgBlockM;
         const int n0 = (rem % n_tiles) * kWgBlockN;
-        int lo, hi;
-        group_range(g, lo, hi);
-        const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kWgStages;
-          const uint32_t ph = (it / kWgStages) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
-          mbar_arrive_expect_tx(&full[s], kWgABytes + kWgBBytes);
-          const int krow = lo + kb * kWgBlockK;
+        for (int seg = 0; seg < p.segments && ok; ++seg) {
+          int lo, hi;
+          group_range(g, seg, lo, hi);
+          const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+          for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int s = it % kWgStages;
+            const uint32_t ph = (it / kWgStages) & 1;
+            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
+            mbar_arrive_expect_tx(&full[s], kWgABytes + kWgBBytes);
+            const int krow = lo + kb * kWgBlockK;
 #pragma unroll
-          for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl)
-            tma_load_2d(sA + s * kWgABytes + pnl * kWgPanelBytes, &tmap_g, &full[s], m0 + pnl * 64, krow);
+            for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl)
+              tma_load_2d(sA + s * kWgABytes + pnl * kWgPanelBytes, &tmap_g, &full[s], m0 + pnl * 64, krow);
 #pragma unroll
-          for (int pnl = 0; pnl < kWgBlockN / 64; ++pnl)
-            tma_load_2d(sB + s * kWgBBytes + pnl * kWgPanelBytes, &tmap_x, &full[s], n0 + pnl * 64, krow);
+            for (int pnl = 0; pnl < kWgBlockN / 64; ++pnl)
+              tma_load_2d(sB + s * kWgBBytes + pnl * kWgPanelBytes, &tmap_x, &full[s], n0 + pnl * 64, krow);
+          }
         }
       }
       if (!ok) {
@@ -158,46 +162,55 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
     bool ok = true;
     for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int g = (int)(t / tiles_per_group);
-      int lo, hi;
-      group_range(g, lo, hi);
-      const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
-      if (num_kb == 0) continue;
+      int total_kb = 0;
+      for (int seg = 0; seg < p.segments; ++seg) {
+        int lo, hi;
+        group_range(g, seg, lo, hi);
+        total_kb += (hi - lo + kWgBlockK - 1) / kWgBlockK;
+      }
+      if (total_kb == 0) continue;
       const int buf = tb & 1;
       const uint32_t aph = (tb >> 1) & 1;
       ++tb;
       if (!mbar_wait(&tempty[buf], aph ^ 1, abort_flag, p.status, 23)) { ok = false; break; }
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % kWgStages;
-        const uint32_t ph = (it / kWgStages) & 1;
-        if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22)) { ok = false; break; }
-        const int valid = hi - lo - kb * kWgBlockK;
-        if (valid < kWgBlockK) {
-          // rows [valid, 64) of both A panels: 128 bytes each, 16 bytes per lane-step
-          const int nbytes = (kWgBlockK - valid) * 128;
-          for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl) {
-            uint8_t* base = sA + s * kWgABytes + pnl * kWgPanelBytes + valid * 128;
-            for (int o = lane * 16; o < nbytes; o += 32 * 16)
-              *reinterpret_cast<uint4*>(base + o) = make_uint4(0, 0, 0, 0);
+      int done_kb = 0;
+      for (int seg = 0; seg < p.segments && ok; ++seg) {
+        int lo, hi;
+        group_range(g, seg, lo, hi);
+        const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+        for (int kb = 0; kb < num_kb; ++kb, ++it, ++done_kb) {
+          const int s = it % kWgStages;
+          const uint32_t ph = (it / kWgStages) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22)) { ok = false; break; }
+          const int valid = hi - lo - kb * kWgBlockK;
+          if (valid < kWgBlockK) {
+            // rows [valid, 64) of both A panels: 128 bytes each, 16 bytes per lane-step
+            const int nbytes = (kWgBlockK - valid) * 128;
+            for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl) {
+              uint8_t* base = sA + s * kWgABytes + pnl * kWgPanelBytes + valid * 128;
+              for (int o = lane * 16; o < nbytes; o += 32 * 16)
+                *reinterpret_cast<uint4*>(base + o) = make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
           }
-          fence_proxy_async_smem();
-        }
-        __syncwarp();
-        tc_fence_after_sync();
-        if (lane == 0) {
-          const uint32_t a_addr = smem_u32(sA + s * kWgABytes);
-          const uint32_t b_addr = smem_u32(sB + s * kWgBBytes);
-          const uint64_t adesc = make_smem_desc(a_addr, kWgPanelBytes, 1024);
-          const uint64_t bdesc = make_smem_desc(b_addr, kWgPanelBytes, 1024);
-          const uint32_t d_tmem = tmem_base + buf * kWgBlockN;
+          __syncwarp();
+          tc_fence_after_sync();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_u32(sA + s * kWgABytes);
+            const uint32_t b_addr = smem_u32(sB + s * kWgBBytes);
+            const uint64_t adesc = make_smem_desc(a_addr, kWgPanelBytes, 1024);
+            const uint64_t bdesc = make_smem_desc(b_addr, kWgPanelBytes, 1024);
+            const uint32_t d_tmem = tmem_base + buf * kWgBlockN;
 #pragma unroll
-          for (int k = 0; k < kWgBlockK / 16; ++k) {
-            const uint64_t step = (uint64_t)((k * 16 * 128) >> 4);
-            umma_f16(d_tmem, adesc + step, bdesc + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kWgBlockK / 16; ++k) {
+              const uint64_t step = (uint64_t)((k * 16 * 128) >> 4);
+              umma_f16(d_tmem, adesc + step, bdesc + step, idesc, (done_kb > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(&empty[s]);
+            if (done_kb == total_kb - 1) umma_commit(&tfull[buf]);
           }
-          umma_commit(&empty[s]);
-          if (kb == num_kb - 1) umma_commit(&tfull[buf]);
+          __syncwarp();
         }
-        __syncwarp();
       }
     }
     if (!ok && lane == 0) {
@@ -217,9 +230,12 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
       const int rem = (int)(t - (long long)g * tiles_per_group);
       const int m0 = (rem / n_tiles) * kWgBlockM;
       const int n0 = (rem % n_tiles) * kWgBlockN;
-      int lo, hi;
-      group_range(g, lo, hi);
-      const bool has_rows = hi > lo;
+      bool has_rows = false;
+      for (int seg = 0; seg < p.segments; ++seg) {
+        int lo, hi;
+        group_range(g, seg, lo, hi);
+        has_rows = has_rows || hi > lo;
+      }
       const int m = m0 + q * 32 + lane;
       const int col0 = n0 + half * kCols;
       OutT* orow = out + ((long long)g * p.M + m) * p.N + col0;
@@ -275,11 +291,11 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
 using namespace b200;
 
 extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const void* x, long long ldx,
-                                          const int32_t* offsets, int groups, long long rows_total, int M,
-                                          int N, void* out, int out_is_fp32, int32_t* status,
-                                          void* stream) {
+                                          const int32_t* offsets, int groups, int segments,
+                                          long long rows_total, int M, int N, void* out, int out_is_fp32,
+                                          int32_t* status, void* stream) {
   if (!g || !x || !offsets || !out || !status) return B200MOE_ERR_ARG;
-  if (groups <= 0 || M <= 0 || N <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
+  if (groups <= 0 || segments <= 0 || M <= 0 || N <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
   if (groups > kWgMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
   if ((M % 8) || (N % 8) || (ldg % 8) || (ldx % 8)) return B200MOE_ERR_ALIGN;
   if (((uintptr_t)g & 15) || ((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return B200MOE_ERR_ALIGN;
@@ -313,6 +329,7 @@ extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const vo
   p.M = M;
   p.N = N;
   p.rows_total = (int)rows_total;
+  p.segments = segments;
   p.status = status;
   const long long tiles = (long long)groups * ((M + kWgBlockM - 1) / kWgBlockM) * ((N + kWgBlockN - 1) / kWgBlockN);
   long long grid = tiles < sm_count() ? tiles : sm_count();

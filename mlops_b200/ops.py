@@ -295,7 +295,8 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
     `a_scale` is `[rows, K/128]` (any strides) or `[rows]`/`[rows, 1]` for one scale per row."""
     device = _need_cuda(a_q, a_scale, b_q, b_scale, offsets)
     rows, k = a_q.shape
-    groups = b_q.shape[0]
+    weights = b_q.shape[0]
+    groups = offsets.numel() - 1  # a multiple of `weights`: group g multiplies weight g % weights
     n = b_q.shape[2] if b_mn_major else b_q.shape[1]
     kb = b_q.shape[1] if b_mn_major else b_q.shape[2]
     if kb != k:
@@ -320,7 +321,7 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
             lib.b200moe_grouped_gemm_fp8(
                 a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
                 b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), offsets.data_ptr(),
-                groups, rows, n, k, 1 if b_mn_major else 0, int(block_n),
+                groups, weights, rows, n, k, 1 if b_mn_major else 0, int(block_n),
                 status_block(device).data_ptr(), _stream(),
             ),
             "grouped_gemm_fp8",
@@ -330,10 +331,13 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
 
 
 def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
-    """`[G, M, N]` with `out[e] = g[rows_e].T @ x[rows_e]` (bf16 operands, fp32 sums)."""
+    """`[G, M, N]` with `out[e] = g[rows_e].T @ x[rows_e]` (bf16 operands, fp32 sums).
+    `offsets` has `segments * groups + 1` entries; expert e sums over the ranges
+    `offsets[s*groups+e] .. offsets[s*groups+e+1]`."""
     device = _need_cuda(g, x, offsets)
     rows, m = g.shape
     n = x.shape[1]
+    segments = (offsets.numel() - 1) // groups
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise NativeError("weight gradients are written as bf16 or fp32")
     if rows == 0:
@@ -342,7 +346,7 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
     with _Timed("wgrad_bf16", 2.0 * rows * m * n):
         check(
             lib.b200moe_grouped_wgrad_bf16(
-                g.data_ptr(), g.stride(0), x.data_ptr(), x.stride(0), offsets.data_ptr(), groups, rows,
+                g.data_ptr(), g.stride(0), x.data_ptr(), x.stride(0), offsets.data_ptr(), groups, segments, rows,
                 m, n, out.data_ptr(), 1 if out_dtype == torch.float32 else 0,
                 status_block(device).data_ptr(), _stream(),
             ),

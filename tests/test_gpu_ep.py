@@ -1,0 +1,27 @@
+"""Expert-parallel layer on 2 GPUs against the single-GPU layer (skipped with fewer than two
+devices). Each case is a fresh `torch.distributed.run` job with its own process group, as the
+reference's expert-parallel tests are (tests/expert_parallel/_gate.py:19-197)."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("expert_map,mode", [("contiguous", "softmax_then_topk"), ("strided", "sigmoid_noaux_tc")])
+def test_two_rank_layer_matches_single_gpu(expert_map, mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29613", str(ROOT / "tests" / "ep_worker.py"),
+           expert_map, mode]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+    assert "ep worker ok" in done.stdout

@@ -203,3 +203,42 @@ def test_wgrad(counts, m, n, out_dtype):
             mx, mean = O.rel_errors(out[e].float().cpu(), ref[e])
             assert mx <= (1e-5 if out_dtype == torch.float32 else MAX_REL), mx
             assert mean <= (1e-6 if out_dtype == torch.float32 else MEAN_REL), mean
+
+
+def test_segmented_layout_matches_expert_sorted_layout():
+    """Rows laid out [source][expert] (what an expert-parallel exchange delivers): the GEMM
+    with `weights < groups` and the weight gradient with `segments > 1` must equal the plain
+    expert-sorted computation on the regrouped rows."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(12)
+    experts, sources, n, k = 3, 4, 256, 384
+    counts = torch.randint(0, 90, (sources, experts), generator=g)
+    counts[1, 2] = 0
+    seg_offs = _offsets(counts.reshape(-1).tolist())
+    rows = int(counts.sum())
+    a = torch.randn(rows, k, generator=g)
+    a_q, a_s = O.quantize_rows(a, mode="1x128")
+    b_q, b_s = O.quantize_blocks(torch.randn(experts, n, k, generator=g))
+    out = _run(a_q, a_s, b_q, b_s, seg_offs, False, 256)
+    # reference: per segment against weight (segment index % experts)
+    ref = torch.zeros(rows, n, dtype=torch.float64)
+    offs = seg_offs.tolist()
+    for s in range(sources * experts):
+        lo, hi = offs[s], offs[s + 1]
+        if hi > lo:
+            e = s % experts
+            ref[lo:hi] = O.grouped_block_gemm(a_q[lo:hi], a_s[lo:hi], b_q[e:e + 1], b_s[e:e + 1],
+                                              torch.tensor([0, hi - lo], dtype=torch.int32))
+    mx, mean = O.rel_errors(out.float().cpu(), ref)
+    assert mx <= MAX_REL and mean <= MEAN_REL
+    grad = torch.randn(rows, 128, generator=g).bfloat16()
+    x = torch.randn(rows, 256, generator=g).bfloat16()
+    dw = ops.grouped_wgrad(grad.to(DEV), x.to(DEV), seg_offs.to(DEV), experts, torch.float32)
+    ops.check_status(DEV)
+    for e in range(experts):
+        expected = torch.zeros(128, 256, dtype=torch.float64)
+        for s in range(sources):
+            lo, hi = offs[s * experts + e], offs[s * experts + e + 1]
+            expected += grad[lo:hi].double().t() @ x[lo:hi].double()
+        mx, mean = O.rel_errors(dw[e].cpu(), expected)
+        assert mx <= 1e-5, mx
