@@ -143,6 +143,8 @@ int b200moe_quantize_blocks(const void* w, int src_is_fp32, int experts, int out
  *            b_mn_major != 0: [groups, K, N] with scales [groups, ceil(K/128), ceil(N/128)]
  *            (the stored weight read along its rows: input gradients, no transposed copy)
  *   d        bf16 [rows_total, N], pitch ldd
+ *   addend   optional bf16 [rows_total, N] (pitch ldc) added to the fp32 sums before the one
+ *            rounding (the LoRA term of a projection); NULL for none
  *   block_n  128 or 256: tile width
  * Every 128-wide K block is accumulated on the tensor cores from zero and promoted in
  * fp32 by a_scale * b_scale.  N % 8 == 0, K % 16 == 0 (N % 16 for b_mn_major),
@@ -155,9 +157,26 @@ int b200moe_quantize_blocks(const void* w, int src_is_fp32, int experts, int out
  */
 int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale, long long as_row_stride,
                              long long as_kb_stride, const void* b, const float* b_scale, void* d,
-                             long long ldd, const int32_t* offsets, int groups, int weights,
+                             long long ldd, const void* addend, long long ldc, const int32_t* offsets,
+                             int groups, int weights,
                              long long rows_total, int N, int K, int b_mn_major, int block_n,
                              int32_t* status, void* stream);
+
+/*
+ * Rank-r side products of expert LoRA on expert-sorted rows (rank <= 64, bf16, fp32 sums).
+ * project: t[row, 0:rank] = x[row, 0:K] . W_e, with W [experts, rank, K] (rank_major != 0) or
+ *          [experts, K, rank].  expand: c[row, 0:N] = scale * t[row, 0:rank] . W_e, with
+ *          W [experts, N, rank] (wide_major != 0) or [experts, rank, N].  W_e is the factor of
+ *          the expert that owns the row (offsets as in the GEMMs, experts <= 1024).
+ * Reference: src/mlops/lora/grouped.py:19-110 (`grouped_linear` on the factors),
+ * src/mlops/lora/experts.py:140-167.
+ */
+int b200moe_lora_project(const void* x, long long ldx, const void* w, int rank_major,
+                         const int32_t* offsets, int experts, long long rows, int K, int rank, void* t,
+                         long long ldt, void* stream);
+int b200moe_lora_expand(const void* t, long long ldt, const void* w, int wide_major, const int32_t* offsets,
+                        int experts, long long rows, int N, int rank, float scale, void* c, long long ldc,
+                        void* stream);
 
 /*
  * Grouped weight gradient: out[g] (M x N) = G[rows of g, 0:M]^T @ X[rows of g, 0:N],

@@ -41,9 +41,11 @@ SIGNATURES = {
     "b200moe_quantize_blocks": (I, [P, I, I, I, I, P, P, P]),
     "b200moe_grouped_gemm_fp8": (
         I,
-        [P, LL, P, LL, LL, P, P, P, LL, P, I, I, LL, I, I, I, I, P, P],
+        [P, LL, P, LL, LL, P, P, P, LL, P, LL, P, I, I, LL, I, I, I, I, P, P],
     ),
     "b200moe_grouped_wgrad_bf16": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, P, P]),
+    "b200moe_lora_project": (I, [P, LL, P, I, P, I, LL, I, I, P, LL, P]),
+    "b200moe_lora_expand": (I, [P, LL, P, I, P, I, LL, I, I, F, P, LL, P]),
     "b200moe_combine": (I, [P, LL, LL, P, P, P, LL, P, LL, LL, I, I, P]),
     "b200moe_gather_rows": (I, [P, LL, P, I, LL, I, P, LL, P]),
     "b200moe_gather_scalar": (I, [P, P, LL, P, P]),

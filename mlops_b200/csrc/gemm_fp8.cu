@@ -37,6 +37,8 @@ struct GemmFp8Params {
   long long bs_group_stride, bs_n_stride, bs_k_stride;
   __nv_bfloat16* d;
   long long ldd;
+  const __nv_bfloat16* addend;  // optional [rows, N] term added in fp32 before the rounding
+  long long ldc;
   const int* offsets;
   int groups, N, K, rows_total;
   int weights;  // group g multiplies weight matrix g % weights
@@ -345,6 +347,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int j = 0; j < kCols; j += 8) {
           if (col0 + j + 8 <= p.N) {
+            if (p.addend != nullptr) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(p.addend + (long long)grow * p.ldc + col0 + j);
+              const __nv_bfloat162* cv = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 f = __bfloat1622float2(cv[u]);
+                acc[j + 2 * u] += f.x;
+                acc[j + 2 * u + 1] += f.y;
+              }
+            }
             uint4 v;
             v.x = pack_bf16x2(acc[j + 0], acc[j + 1]);
             v.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
@@ -396,7 +408,7 @@ using namespace b200;
 extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
                                         long long as_row_stride, long long as_kb_stride, const void* b,
                                         const float* b_scale, void* d, long long ldd,
-                                        const int32_t* offsets, int groups, int weights,
+                                        const void* addend, long long ldc, const int32_t* offsets, int groups, int weights,
                                         long long rows_total, int N, int K, int b_mn_major, int block_n,
                                         int32_t* status, void* stream) {
   if (!a || !a_scale || !b || !b_scale || !d || !offsets || !status) return B200MOE_ERR_ARG;
@@ -405,6 +417,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
   if (groups > kMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
   if (block_n != 128 && block_n != 256) return B200MOE_ERR_ARG;
   if ((N % 8) || (K % 16) || (lda % 16) || (ldd % 8)) return B200MOE_ERR_ALIGN;
+  if (addend != nullptr && ((ldc % 8) || ((uintptr_t)addend & 15))) return B200MOE_ERR_ALIGN;
   if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)d & 15)) return B200MOE_ERR_ALIGN;
   if (b_mn_major && (N % 16)) return B200MOE_ERR_ALIGN;
   if (rows_total == 0) return B200MOE_OK;
@@ -427,6 +440,8 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
   p.b_scale = b_scale;
   p.d = reinterpret_cast<__nv_bfloat16*>(d);
   p.ldd = ldd;
+  p.addend = reinterpret_cast<const __nv_bfloat16*>(addend);
+  p.ldc = ldc;
   p.offsets = offsets;
   p.groups = groups;
   p.N = N;

@@ -289,11 +289,12 @@ def quantize_blocks(weight):
 
 
 # ------------------------------------------------------------------------------- GEMMs
-def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, block_n=128, out=None):
+def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, block_n=256, out=None,
+                     addend=None):
     """bf16 `[rows, N]` of the grouped block-FP8 product. `b_q` is `[G, N, K]`
     (`b_mn_major=False`) or `[G, K, N]` read along its rows (`b_mn_major=True`);
     `a_scale` is `[rows, K/128]` (any strides) or `[rows]`/`[rows, 1]` for one scale per row."""
-    device = _need_cuda(a_q, a_scale, b_q, b_scale, offsets)
+    device = _need_cuda(a_q, a_scale, b_q, b_scale, offsets, addend)
     rows, k = a_q.shape
     weights = b_q.shape[0]
     groups = offsets.numel() - 1  # a multiple of `weights`: group g multiplies weight g % weights
@@ -320,7 +321,8 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
         check(
             lib.b200moe_grouped_gemm_fp8(
                 a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
-                b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), offsets.data_ptr(),
+                b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), _ptr(addend),
+                0 if addend is None else addend.stride(0), offsets.data_ptr(),
                 groups, weights, rows, n, k, 1 if b_mn_major else 0, int(block_n),
                 status_block(device).data_ptr(), _stream(),
             ),
@@ -352,6 +354,47 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
             ),
             "grouped_wgrad",
         )
+    _count()
+    return out
+
+
+def lora_project(x, factor, offsets, *, rank_major):
+    """`t [rows, r] = x[row] . factor[expert(row)]`; factor `[E, r, K]` (`rank_major`) or `[E, K, r]`."""
+    device = _need_cuda(x, factor, offsets)
+    rows, k = x.shape
+    experts = factor.shape[0]
+    rank = factor.shape[1] if rank_major else factor.shape[2]
+    factor = factor.contiguous()
+    out = torch.empty((rows, rank), dtype=torch.bfloat16, device=device)
+    if rows == 0:
+        return out
+    check(
+        lib.b200moe_lora_project(x.data_ptr(), x.stride(0), factor.data_ptr(), 1 if rank_major else 0,
+                                 offsets.data_ptr(), experts, rows, k, rank, out.data_ptr(), out.stride(0),
+                                 _stream()),
+        "lora_project",
+    )
+    _count()
+    return out
+
+
+def lora_expand(t, factor, offsets, *, wide_major, scale=1.0):
+    """`c [rows, N] = scale * t[row] . factor[expert(row)]`; factor `[E, N, r]` (`wide_major`) or
+    `[E, r, N]`."""
+    device = _need_cuda(t, factor, offsets)
+    rows, rank = t.shape
+    experts = factor.shape[0]
+    n = factor.shape[1] if wide_major else factor.shape[2]
+    factor = factor.contiguous()
+    out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
+    if rows == 0:
+        return out
+    check(
+        lib.b200moe_lora_expand(t.data_ptr(), t.stride(0), factor.data_ptr(), 1 if wide_major else 0,
+                                offsets.data_ptr(), experts, rows, n, rank, float(scale), out.data_ptr(),
+                                out.stride(0), _stream()),
+        "lora_expand",
+    )
     _count()
     return out
 

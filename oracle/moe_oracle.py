@@ -318,3 +318,75 @@ def rel_errors(actual, expected):
     rms = e.pow(2).mean().sqrt().clamp_min(1e-30)
     diff = (a - e).abs() / torch.maximum(e.abs(), rms)
     return diff.max().item(), diff.mean().item()
+
+
+# ------------------------------------------------------------------------ expert LoRA
+def _factor_rows(rows, factor, offsets, transpose):
+    """Per expert `rows_e @ factor[e]` (or `@ factor[e].T`), float64, zeros for empty experts."""
+    out = torch.zeros((rows.shape[0], factor.shape[1] if transpose else factor.shape[2]), dtype=torch.float64)
+    offs = offsets.tolist()
+    for e in range(factor.shape[0]):
+        lo, hi = offs[e], offs[e + 1]
+        if hi > lo:
+            f = factor[e].double()
+            out[lo:hi] = rows[lo:hi].double() @ (f.t() if transpose else f)
+    return out
+
+
+def forward_lora_block_fp8(h2, residual, logits, w13_q, w13_s, w2_q, w2_s, a13, b13, a2, b2, *, top_k,
+                           routing_mode, scale, router_bias=None, n_group=1, topk_group=1,
+                           routed_scaling=1.0, swiglu_limit=None):
+    """`h13 = x W13^T + s (x A13^T) B13^T -> SwiGLU -> y = a W2^T + s (a A2^T) B2^T` with the
+    base products on block-FP8 operands and the LoRA branch in bf16 (semantics:
+    src/mlops/lora/experts.py:140-167, src/mlops/lora/grouped.py:19-110). Rounding points:
+    the rank-r intermediate and the LoRA term are bf16, the sum is rounded once."""
+    bf = torch.bfloat16
+    experts = w13_q.shape[0]
+    weights, ids = route(logits, top_k, routing_mode, bias=router_bias, n_group=n_group,
+                         topk_group=topk_group, routed_scaling=routed_scaling)
+    order, offsets, slots = sort_assignments(ids, experts)
+    token = torch.div(order.long(), int(top_k), rounding_mode="floor")
+    x_rows = h2[token].to(bf)
+    x_q, x_s = quantize_rows(x_rows)
+    t1 = _factor_rows(x_rows, a13, offsets, True).to(bf)
+    c1 = (scale * _factor_rows(t1, b13, offsets, True)).to(bf)
+    h13 = (grouped_block_gemm(x_q, x_s, w13_q, w13_s, offsets) + c1.double()).to(bf)
+    act = swiglu(h13, swiglu_limit)
+    a_q, a_s = quantize_rows(act)
+    act_b = act.to(bf)
+    t2 = _factor_rows(act_b, a2, offsets, True).to(bf)
+    c2 = (scale * _factor_rows(t2, b2, offsets, True)).to(bf)
+    y = (grouped_block_gemm(a_q, a_s, w2_q, w2_s, offsets) + c2.double()).to(bf)
+    output = combine(y, slots, weights, residual)
+    return dict(weights=weights, ids=ids, order=order, offsets=offsets, slots=slots, x_rows=x_rows, h13=h13,
+                act=act_b, t1=t1, t2=t2, y=y, output=output)
+
+
+def backward_lora_block_fp8(grad_output, fwd, w13_q, w13_s, w2_q, w2_s, a13, b13, a2, b2, *, top_k, scale,
+                            swiglu_limit=None):
+    """VJP of `forward_lora_block_fp8` for the hidden rows (expert part), the route weights and
+    the four factors (frozen base)."""
+    bf = torch.bfloat16
+    experts = w13_q.shape[0]
+    order, offsets, slots, weights = fwd["order"], fwd["offsets"], fwd["slots"], fwd["weights"]
+    token = torch.div(order.long(), int(top_k), rounding_mode="floor")
+    dy_rows = grad_output[token].to(bf)
+    dy_q, dy_s = quantize_rows(dy_rows)
+    t2g = _factor_rows(dy_rows, b2, offsets, False).to(bf)                      # dy B2
+    r_add = (scale * _factor_rows(t2g, a2, offsets, False)).to(bf)              # s dy B2 A2
+    r = (grouped_block_gemm(dy_q, dy_s, w2_q, w2_s, offsets, b_mn_major=True) + r_add.double()).to(bf)
+    score = weights.reshape(-1)[order.long()].float()
+    dscore, grad_h13, act_scaled = dswiglu_routed(fwd["h13"], r, score, swiglu_limit)
+    gh_b = grad_h13.to(bf)
+    gh_q, gh_s = quantize_rows(grad_h13)
+    dt1 = _factor_rows(gh_b, b13, offsets, False).to(bf)                        # gh B13
+    dx_add = (scale * _factor_rows(dt1, a13, offsets, False)).to(bf)
+    grad_rows = (grouped_block_gemm(gh_q, gh_s, w13_q, w13_s, offsets, b_mn_major=True) + dx_add.double()).to(bf)
+    grad_h2 = combine(grad_rows, slots, None, None)
+    w_col = score[:, None]
+    grad_b2 = grouped_wgrad(dy_rows, (fwd["t2"].float() * (w_col * scale)).to(bf), offsets, experts)
+    grad_a2 = grouped_wgrad((t2g.float() * scale).to(bf), act_scaled.to(bf), offsets, experts)
+    grad_b13 = grouped_wgrad(gh_b, (fwd["t1"].float() * scale).to(bf), offsets, experts)
+    grad_a13 = grouped_wgrad((dt1.float() * scale).to(bf), fwd["x_rows"], offsets, experts)
+    return dict(grad_h2=grad_h2, grad_route_weights=dscore[slots.reshape(-1).long()].view_as(weights),
+                grad_a13=grad_a13, grad_b13=grad_b13, grad_a2=grad_a2, grad_b2=grad_b2)

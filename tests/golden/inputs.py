@@ -65,3 +65,22 @@ def ep_case():
     ids = torch.stack([torch.randperm(E - 1)[:K] for _ in range(T)]).to(torch.int32)
     p = torch.rand(T, K)
     return dict(x=x, gate=gate, up=up, down=down, ids=ids, p=p)
+
+
+def lora_case(rank=16):
+    """A small expert-LoRA layer: T=96, D=128, 4 experts, top-2, F=128; factors as in
+    BASELINE config 5 (A ~ N(0, 0.02), B = 0.01 N(0, 1), bf16), alpha = rank (scale 1)."""
+    torch.manual_seed(23)
+    T, D, E, K, F = 96, 128, 4, 2, 128
+    x = torch.randn(T, D).bfloat16()
+    residual = torch.randn(T, D).bfloat16()
+    router = torch.randn(E, D) * 0.1
+    w13 = (torch.randn(E, 2 * F, D) * 0.05).bfloat16()
+    w2 = (torch.randn(E, D, F) * 0.05).bfloat16()
+    a13 = (torch.randn(E, rank, D) * 0.02).bfloat16()
+    b13 = (torch.randn(E, 2 * F, rank) * 0.01).bfloat16()
+    a2 = (torch.randn(E, rank, F) * 0.02).bfloat16()
+    b2 = (torch.randn(E, D, rank) * 0.01).bfloat16()
+    dy = torch.randn(T, D).bfloat16()
+    return dict(x=x, residual=residual, router=router, w13=w13, w2=w2, a13=a13, b13=b13, a2=a2, b2=b2, dy=dy,
+                top_k=K, routing_mode="softmax_then_topk", scale=4.0)

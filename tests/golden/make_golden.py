@@ -132,6 +132,27 @@ def main(reference_src: str) -> None:
     y = expert_computation(ep["x"], ep["ids"], ep["p"], ep["gate"], ep["up"], ep["down"])
     torch.save(dict(checksum=inputs.checksum(*(ep[k] for k in ("x", "gate", "up", "down", "ids", "p"))), y=y),
                HERE / "ep_reference.pt")
+    # --------------------------------- expert LoRA through the reference's builtin composition
+    from mlops.lora.experts import expert_lora
+
+    lc = inputs.lora_case()
+    leaves = {k: lc[k].clone().requires_grad_(True) for k in ("x", "router", "a13", "b13", "a2", "b2")}
+    g13 = BlockFP8Weight.quantize(lc["w13"])
+    g2 = BlockFP8Weight.quantize(lc["w2"])
+    out, aux, counts, psum = expert_lora(
+        leaves["x"], lc["residual"], leaves["router"], g13, g2, leaves["a13"], leaves["b13"], leaves["a2"],
+        leaves["b2"], top_k=lc["top_k"], routing_mode=lc["routing_mode"], scale=lc["scale"],
+        implementation="builtin", compute_precision="bf16")
+    grads = torch.autograd.grad((out.float() * lc["dy"].float()).sum(), list(leaves.values()))
+    base_out, *_ = mlops.moe(lc["x"], lc["residual"], lc["router"], g13, g2, top_k=lc["top_k"],
+                             routing_mode=lc["routing_mode"], compute_precision="bf16")
+    torch.save(
+        dict(checksum=inputs.checksum(*(lc[k] for k in ("x", "residual", "router", "w13", "w2", "a13", "b13",
+                                                         "a2", "b2", "dy"))),
+             output=out.detach(), base_output=base_out.detach(), counts=counts, aux=aux.detach(),
+             **{"grad_" + k: g for k, g in zip(leaves, grads)}),
+        HERE / "lora_builtin.pt",
+    )
     print("fixtures written to", HERE)
 
 

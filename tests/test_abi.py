@@ -39,7 +39,8 @@ def test_argument_validation_needs_no_gpu():
     assert lib.b200moe_route_topk(None, 0, 1, 8, 2, 1, None, 1, 1, 1.0, None, None, None) == -1
     assert lib.b200moe_sort_assignments_workspace_bytes(4096 * 3 + 1, 8) == 4 * 8 * 4
     assert lib.b200moe_sort_assignments_workspace_bytes(-1, 8) == -1
-    assert lib.b200moe_grouped_gemm_fp8(None, 0, None, 0, 0, None, None, None, 0, None, 1, 1, 0, 8, 16, 0, 128,
+    assert lib.b200moe_grouped_gemm_fp8(None, 0, None, 0, 0, None, None, None, 0, None, 0, None, 1, 1, 0, 8, 16, 0,
+                                        128,
                                         None, None) == -1
     assert lib.b200moe_combine(None, 0, 0, None, None, None, 0, None, 0, 0, 8, 1, None) == -1
 

@@ -160,3 +160,37 @@ def test_expert_math_against_ep_reference(golden):
     rel_rms = ((out.double() - fixture["y"].double()).pow(2).mean().sqrt()
                / fixture["y"].double().pow(2).mean().sqrt()).item()
     assert rel_rms < 0.12
+
+
+def test_lora_restatement_against_reference_builtin(golden):
+    """Oracle expert-LoRA (FP8 base, bf16 LoRA branch) vs the reference's builtin composition
+    (bf16 base on the dequantised weights): bound 8e-2 rel-Frobenius, the reference's
+    LoRA fp8-vs-bf16 bound (tests/test_sonicmoe_lora.py:351); counts exact."""
+    fixture = golden("lora_builtin.pt")
+    lc = inputs.lora_case()
+    keys = ("x", "residual", "router", "w13", "w2", "a13", "b13", "a2", "b2", "dy")
+    assert torch.equal(inputs.checksum(*(lc[k] for k in keys)), fixture["checksum"])
+    w13, w2 = O.quantize_blocks(lc["w13"]), O.quantize_blocks(lc["w2"])
+    logits = lc["x"].float() @ lc["router"].t()
+    fwd = O.forward_lora_block_fp8(lc["x"], lc["residual"], logits, *w13, *w2, lc["a13"], lc["b13"], lc["a2"],
+                                   lc["b2"], top_k=lc["top_k"], routing_mode=lc["routing_mode"], scale=lc["scale"])
+    assert torch.equal(torch.bincount(fwd["ids"].reshape(-1).long(), minlength=4), fixture["counts"])
+
+    def frob(a, e):
+        return ((a.double() - e.double()).norm() / e.double().norm()).item()
+
+    # the LoRA branch must be visible: the fixture's output differs from its base-only output
+    assert frob(fixture["base_output"], fixture["output"]) > 1e-3
+    routed = fixture["output"].float() - lc["residual"].float()
+    assert frob(fwd["output"].float() - lc["residual"].float(), routed) < 8e-2
+    bwd = O.backward_lora_block_fp8(lc["dy"], fwd, *w13, *w2, lc["a13"], lc["b13"], lc["a2"], lc["b2"],
+                                    top_k=lc["top_k"], scale=lc["scale"])
+    for name in ("a13", "b13", "a2", "b2"):
+        assert frob(bwd["grad_" + name], fixture["grad_" + name]) < 8e-2, name
+    # zero B factors reduce the layer to the plain one
+    zero13, zero2 = torch.zeros_like(lc["b13"]), torch.zeros_like(lc["b2"])
+    plain = O.forward_block_fp8(lc["x"], lc["residual"], logits, *w13, *w2, top_k=lc["top_k"],
+                                routing_mode=lc["routing_mode"])
+    same = O.forward_lora_block_fp8(lc["x"], lc["residual"], logits, *w13, *w2, lc["a13"], zero13, lc["a2"], zero2,
+                                    top_k=lc["top_k"], routing_mode=lc["routing_mode"], scale=lc["scale"])
+    assert torch.equal(same["output"], plain["output"])
