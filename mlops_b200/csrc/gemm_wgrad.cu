@@ -14,6 +14,8 @@
 #include "common.cuh"
 #include "host_util.h"
 
+#include <stdlib.h>
+
 namespace b200 {
 
 constexpr int kWgMaxGroups = 1024;
@@ -26,8 +28,9 @@ constexpr int kWgPanelBytes = kWgBlockK * 128;            // 64 K-rows x 64 bf16
 constexpr int kWgABytes = (kWgBlockM / 64) * kWgPanelBytes;  // 16 KB
 constexpr int kWgBBytes = (kWgBlockN / 64) * kWgPanelBytes;  // 32 KB
 constexpr int kWgTileBytes = kWgStages * (kWgABytes + kWgBBytes);
-constexpr int kWgSmemBytes = 1024 + kWgTileBytes + 256;
+constexpr int kWgSmemBytes = 1024 + kWgTileBytes + 256 + 4 * 4104;
 constexpr int kWgTmemCols = 2 * kWgBlockN;
+constexpr int kWgMaxOffsets = 4097;  // segments * groups + 1 entries are cached in shared memory
 
 struct WgradParams {
   void* out;  // [groups, M, N]
@@ -70,6 +73,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
   uint64_t* drain = bars + 2 * kWgStages + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kWgStages + 5);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  int* offs_s = reinterpret_cast<int*>(smem + kWgTileBytes + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -99,21 +103,35 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
     tmem_alloc(tmem_slot, kWgTmemCols);
     tmem_relinquish();
   }
+  __syncthreads();  // abort_flag initialised before the table check may set it
+  // The row ranges are read many times by every role: keep them in shared memory.  A malformed
+  // table (negative, decreasing, past the end) is reported and every range becomes empty.
+  {
+    const int entries = p.segments * p.groups + 1;
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+      const int v = p.offsets[i];
+      const int nxt = i + 1 < entries ? p.offsets[i + 1] : v;
+      if (v < 0 || nxt < v || nxt > p.rows_total) {
+        report_error(p.status, ERR_BAD_OFFSETS, 20, i);
+        *abort_flag = 2;  // not an abort: marks the table as unusable
+      }
+      offs_s[i] = v;
+    }
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  const bool table_ok = *abort_flag != 2;
+  __syncthreads();
+  if (threadIdx.x == 0) *abort_flag = 0;
+  __syncthreads();
 
-  // Every role walks the same tile sequence and derives the same K range from `offsets`.
-  // A malformed range (negative, decreasing, past the end) is treated as empty.
+  // Every role walks the same tile sequence and derives the same K ranges from the table.
   auto group_range = [&](int g, int seg, int& lo, int& hi) {
     const int at = seg * p.groups + g;
-    lo = p.offsets[at];
-    hi = p.offsets[at + 1];
-    if (lo < 0 || hi < lo || hi > p.rows_total) {
-      report_error(p.status, ERR_BAD_OFFSETS, 20, at);
-      lo = hi = 0;
-    }
+    lo = offs_s[at];
+    hi = table_ok ? offs_s[at + 1] : lo;
   };
 
   if (warp == 0) {
@@ -286,6 +304,314 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster share one 256 x 256 output tile.  CTA r of the
+// pair owns output rows [r*128, r*128+128) (accumulated in its own TMEM) and loads, per K
+// block, its 128 columns of G and 128 of the 256 columns of X; one tcgen05.mma.cta_group::2
+// issued by the leader CTA multiplies across both SMs, so every operand byte is fetched from
+// L2 and written to shared memory once per pair instead of once per CTA (32 KB instead of
+// 48 KB per CTA and K block).  No load is multicast: each CTA's TMA loads land in its own
+// shared memory and complete on its own barrier; after the K tail of its A tile is zeroed the
+// CTA tells the leader with one (remote) mbarrier arrival (warp 1 of each CTA); warp 3 of the
+// leader waits for both reports and issues the MMAs.  The leader's commits arrive on both
+// CTAs' barriers.
+// ---------------------------------------------------------------------------------------
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = 2 * kWgPanelBytes;  // 128 columns of G x 64 K-rows
+constexpr int kPairBBytes = 2 * kWgPanelBytes;  // 128 columns of X x 64 K-rows
+constexpr int kPairTileBytes = kPairStages * (kPairABytes + kPairBBytes);
+constexpr int kPairSmemBytes = 1024 + kPairTileBytes + 512 + 4 * 4104;
+constexpr int kPairBlockM = 256;  // per pair
+
+template <typename OutT>
+__global__ void __launch_bounds__(kWgThreads, 1)
+grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_x,
+                          const WgradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kPairStages * kPairABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairTileBytes);
+  uint64_t* landed = bars;                         // [stages] this CTA's TMA bytes
+  uint64_t* ready = bars + kPairStages;            // [stages] leader only: both CTAs' tiles usable
+  uint64_t* empty = bars + 2 * kPairStages;        // [stages] stage consumed (leader's commit, both CTAs)
+  uint64_t* tfull = bars + 3 * kPairStages;        // [2] accumulator complete (leader's commit, both CTAs)
+  uint64_t* tempty = bars + 3 * kPairStages + 2;   // [2] leader only: both CTAs drained the buffer
+  uint64_t* drain = bars + 3 * kPairStages + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kPairStages + 5);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  int* offs_s = reinterpret_cast<int*>(smem + kPairTileBytes + 512);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int m_tiles = (p.M + kPairBlockM - 1) / kPairBlockM;
+  const int n_tiles = (p.N + kWgBlockN - 1) / kWgBlockN;
+  const int tiles_per_group = m_tiles * n_tiles;
+  const long long total_tiles = (long long)tiles_per_group * p.groups;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&landed[s], 1);
+      mbar_init(&ready[s], 2);   // one arrival per CTA of the pair
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 16);  // 8 epilogue warps in each CTA
+    mbar_init(&tempty[1], 16);
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_g);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(tmem_slot, kWgTmemCols);
+    tmem_relinquish_pair();
+  }
+  __syncthreads();  // abort_flag initialised before the table check may set it
+  // The row ranges are read many times by every role: keep them in shared memory.  A malformed
+  // table (negative, decreasing, past the end) is reported and every range becomes empty.
+  {
+    const int entries = p.segments * p.groups + 1;
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+      const int v = p.offsets[i];
+      const int nxt = i + 1 < entries ? p.offsets[i + 1] : v;
+      if (v < 0 || nxt < v || nxt > p.rows_total) {
+        report_error(p.status, ERR_BAD_OFFSETS, 20, i);
+        *abort_flag = 2;  // not an abort: marks the table as unusable
+      }
+      offs_s[i] = v;
+    }
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();  // barriers of both CTAs exist before anyone arrives on a remote one
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool table_ok = *abort_flag != 2;
+  __syncthreads();
+  if (threadIdx.x == 0) *abort_flag = 0;
+  __syncthreads();
+
+  auto group_range = [&](int g, int seg, int& lo, int& hi) {
+    const int at = seg * p.groups + g;
+    lo = offs_s[at];
+    hi = table_ok ? offs_s[at + 1] : lo;
+  };
+
+  if (warp == 0) {
+    // ---- TMA producer of this CTA: its half of the G columns and its half of the X columns
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = pair; t < total_tiles && ok; t += num_pairs) {
+        const int g = (int)(t / tiles_per_group);
+        const int rem = (int)(t - (long long)g * tiles_per_group);
+        const int m0 = (rem / n_tiles) * kPairBlockM + (int)rank * 128;
+        const int n0 = (rem % n_tiles) * kWgBlockN + (int)rank * 128;
+        for (int seg = 0; seg < p.segments && ok; ++seg) {
+          int lo, hi;
+          group_range(g, seg, lo, hi);
+          const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+          for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int s = it % kPairStages;
+            const uint32_t ph = (it / kPairStages) & 1;
+            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 31)) { ok = false; break; }
+            mbar_arrive_expect_tx(&landed[s], kPairABytes + kPairBBytes);
+            const int krow = lo + kb * kWgBlockK;
+#pragma unroll
+            for (int pnl = 0; pnl < 2; ++pnl) {
+              tma_load_2d(sA + s * kPairABytes + pnl * kWgPanelBytes, &tmap_g, &landed[s], m0 + pnl * 64, krow);
+              tma_load_2d(sB + s * kPairBBytes + pnl * kWgPanelBytes, &tmap_x, &landed[s], n0 + pnl * 64, krow);
+            }
+          }
+        }
+      }
+      if (!ok) {
+        const uint32_t issued = it;
+        for (int s = 0; s < kPairStages; ++s) {
+          if (issued <= (uint32_t)s) continue;
+          const uint32_t last = ((issued - 1 - s) / kPairStages) * kPairStages + s;
+          const long long start = clock64();
+          while (!mbar_try(&landed[s], (last / kPairStages) & 1) && clock64() - start < 20000000LL) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- every CTA: wait for its tiles, zero the K tail, report to the leader.
+    uint32_t it = 0;
+    bool ok = true;
+    for (long long t = pair; t < total_tiles && ok; t += num_pairs) {
+      const int g = (int)(t / tiles_per_group);
+      for (int seg = 0; seg < p.segments && ok; ++seg) {
+        int lo, hi;
+        group_range(g, seg, lo, hi);
+        const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1;
+          if (!mbar_wait(&landed[s], ph, abort_flag, p.status, 32)) { ok = false; break; }
+          const int valid = hi - lo - kb * kWgBlockK;
+          if (valid < kWgBlockK) {
+            const int nbytes = (kWgBlockK - valid) * 128;
+            for (int pnl = 0; pnl < 2; ++pnl) {
+              uint8_t* base = sA + s * kPairABytes + pnl * kWgPanelBytes + valid * 128;
+              for (int o = lane * 16; o < nbytes; o += 32 * 16)
+                *reinterpret_cast<uint4*>(base + o) = make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+          }
+          __syncwarp();
+          if (lane == 0) {
+            if (valid < kWgBlockK) mbar_arrive_cluster(&ready[s], 0);  // publishes the zeroed rows
+            else mbar_arrive_remote(&ready[s], 0);
+          }
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // ---- leader CTA only: wait for both reports and issue the pair MMAs.
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, 1, 1, kPairBlockM, kWgBlockN);
+      uint32_t it = 0, tb = 0;
+      bool ok = true;
+      for (long long t = pair; t < total_tiles && ok; t += num_pairs) {
+        const int g = (int)(t / tiles_per_group);
+        int total_kb = 0;
+        for (int seg = 0; seg < p.segments; ++seg) {
+          int lo, hi;
+          group_range(g, seg, lo, hi);
+          total_kb += (hi - lo + kWgBlockK - 1) / kWgBlockK;
+        }
+        if (total_kb == 0) continue;
+        const int buf = tb & 1;
+        const uint32_t aph = (tb >> 1) & 1;
+        ++tb;
+        if (!mbar_wait(&tempty[buf], aph ^ 1, abort_flag, p.status, 33)) { ok = false; break; }
+        for (int done_kb = 0; done_kb < total_kb; ++done_kb, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1;
+          if (!mbar_wait(&ready[s], ph, abort_flag, p.status, 34)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t adesc = make_smem_desc(smem_u32(sA + s * kPairABytes), kWgPanelBytes, 1024);
+          const uint64_t bdesc = make_smem_desc(smem_u32(sB + s * kPairBBytes), kWgPanelBytes, 1024);
+          const uint32_t d_tmem = tmem_base + buf * kWgBlockN;
+#pragma unroll
+          for (int k = 0; k < kWgBlockK / 16; ++k) {
+            const uint64_t step = (uint64_t)((k * 16 * 128) >> 4);
+            umma_f16_pair(d_tmem, adesc + step, bdesc + step, idesc, (done_kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[s], 3);
+          if (done_kb == total_kb - 1) umma_commit_pair(&tfull[buf], 3);
+        }
+      }
+      if (!ok) {
+        umma_commit_pair(drain, 1);
+        const long long start = clock64();
+        while (!mbar_try(drain, 0) && clock64() - start < 20000000LL) {}
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;
+    const int half = (warp - 4) >> 2;
+    constexpr int kCols = kWgBlockN / 2;
+    uint32_t tb = 0;
+    bool ok = true;
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    for (long long t = pair; t < total_tiles && ok; t += num_pairs) {
+      const int g = (int)(t / tiles_per_group);
+      const int rem = (int)(t - (long long)g * tiles_per_group);
+      const int m0 = (rem / n_tiles) * kPairBlockM + (int)rank * 128;
+      const int n0 = (rem % n_tiles) * kWgBlockN;
+      bool has_rows = false;
+      for (int seg = 0; seg < p.segments; ++seg) {
+        int lo, hi;
+        group_range(g, seg, lo, hi);
+        has_rows = has_rows || hi > lo;
+      }
+      const int m = m0 + q * 32 + lane;
+      const int col0 = n0 + half * kCols;
+      OutT* orow = out + ((long long)g * p.M + m) * p.N + col0;
+      int buf = 0;
+      if (has_rows) {
+        buf = tb & 1;
+        const uint32_t aph = (tb >> 1) & 1;
+        ++tb;
+        if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 35)) { ok = false; break; }
+        tc_fence_after_sync();
+      }
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kWgBlockN + half * kCols;
+#pragma unroll
+      for (int cc = 0; cc < kCols / 32; ++cc) {
+        uint32_t r[32];
+        if (has_rows) {
+          tmem_ld_32x32(taddr + cc * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + cc * 32 + j + 8 <= p.N) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
+              store8<OutT>(orow + cc * 32 + j, v);
+            }
+          }
+        }
+      }
+      if (has_rows) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(&tempty[buf], 0);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  cluster_sync_all();  // the peer may still be arriving on, or reading from, this CTA
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kWgTmemCols);
+  }
+}
+
+template <typename OutT>
+static int launch_pair(const CUtensorMap& tg, const CUtensorMap& tx, const WgradParams& p, cudaStream_t s) {
+  auto kern = grouped_wgrad_pair_kernel<OutT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
+    return B200MOE_ERR_LAUNCH;
+  const long long tiles = (long long)p.groups * ((p.M + kPairBlockM - 1) / kPairBlockM) *
+                          ((p.N + kWgBlockN - 1) / kWgBlockN);
+  long long pairs = sm_count() / 2;
+  if (tiles < pairs) pairs = tiles;
+  if (pairs < 1) pairs = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kWgThreads);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, tg, tx, p) != cudaSuccess) return B200MOE_ERR_LAUNCH;
+  return launch_status();
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -297,6 +623,7 @@ extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const vo
   if (!g || !x || !offsets || !out || !status) return B200MOE_ERR_ARG;
   if (groups <= 0 || segments <= 0 || M <= 0 || N <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
   if (groups > kWgMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  if ((long long)groups * segments + 1 > kWgMaxOffsets) return B200MOE_ERR_LIMIT;
   if ((M % 8) || (N % 8) || (ldg % 8) || (ldx % 8)) return B200MOE_ERR_ALIGN;
   if (((uintptr_t)g & 15) || ((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return B200MOE_ERR_ALIGN;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -331,6 +658,15 @@ extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const vo
   p.rows_total = (int)rows_total;
   p.segments = segments;
   p.status = status;
+  // Wide outputs go to the CTA-pair kernel (256-row tiles); narrow ones (LoRA factors) and the
+  // B200MOE_WGRAD_SINGLE=1 escape hatch use the single-CTA kernel.
+  static const bool force_single = [] {
+    const char* v = getenv("B200MOE_WGRAD_SINGLE");
+    return v != nullptr && v[0] == '1';
+  }();
+  if (!force_single && M > 128 && N > 128) {
+    return out_is_fp32 ? launch_pair<float>(tg, tx, p, s) : launch_pair<__nv_bfloat16>(tg, tx, p, s);
+  }
   const long long tiles = (long long)groups * ((M + kWgBlockM - 1) / kWgBlockM) * ((N + kWgBlockN - 1) / kWgBlockN);
   long long grid = tiles < sm_count() ? tiles : sm_count();
   if (out_is_fp32) {
