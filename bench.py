@@ -234,13 +234,17 @@ def gpu_arm(args, cfg):
         ep = ep_module.ExpertParallelMoE(
             ep_module.ExpertParallelConfig(hidden=D, experts=E, intermediate=F, top_k=K, routing_mode=cfg["mode"],
                                            n_group=cfg["n_group"], topk_group=cfg["topk_group"],
-                                           routed_scaling=cfg["scaling"]),
+                                           routed_scaling=cfg["scaling"], expert_map="strided"),
             dist.group.WORLD, router_weight=router, router_bias=bias, w13=w13, w2=w2, shared=shared,
             device=device)
 
+    rows_received = []
+
     def step(x_in, dy_in):
         if ep is not None:
-            return ep.forward_backward(x_in, residual, dy_in)
+            result = ep.forward_backward(x_in, residual, dy_in)
+            rows_received.append(ep.last_recv_rows)
+            return result
         base, shared_h13 = residual, None
         if shared is not None:
             y_shared, shared_h13 = layer.shared_expert_forward(x_in, *shared)
@@ -303,6 +307,12 @@ def gpu_arm(args, cfg):
     h2d = x_host.numel() * 2 + dy_host.numel() * 2
     d2h = host_result.numel() * 4
 
+    per_rank_rows = None
+    if distributed:
+        mine = torch.tensor([rows_received[-1]], device=device, dtype=torch.int64)
+        gathered = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        per_rank_rows = [int(t.item()) for t in gathered]
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
@@ -326,7 +336,8 @@ def gpu_arm(args, cfg):
         "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": cfg["name"], "tokens_per_gpu": T, "hidden": D, "experts": E, "intermediate": F,
                    "top_k": K, "routing": cfg["mode"], "shared_expert": bool(cfg["shared"]),
-                   "expert_parallel": world, "weights": "block-FP8 e4m3 128x128, random N(0,0.02)",
+                   "expert_parallel": world, "expert_map": "strided" if distributed else "local",
+                   "rows_per_rank": per_rank_rows, "weights": "block-FP8 e4m3 128x128, random N(0,0.02)",
                    "activations": "e4m3 1x128 blocks", "weight_grads": "bf16 operands, fp32 sums, bf16 out",
                    "l2": "inputs exceed L2 (no flush needed)" if T * D * 2 > (126 << 20) else "inputs fit L2"},
         "tflops_per_gpu": (routed_flops + shared_flops) / (ms_per_step * 1e-3) / 1e12,

@@ -53,8 +53,9 @@ struct GemmCfg {
   static constexpr int kTmemCols = 2 * BLOCK_N;
   static constexpr int kTileBytes = kStages * (kABytes + kBBytes);
   static constexpr int kBarBytes = 256;
-  static constexpr int kSchedBytes = 2 * (kMaxGroups + 1) * 4;
-  static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes;
+  static constexpr int kSchedBytes = (2 * (kMaxGroups + 1) * 4 + 15) / 16 * 16;
+  static constexpr int kStoreBytes = 8 * 32 * 80;  // per-warp transpose buffers of the epilogue
+  static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + kStoreBytes;
 };
 
 struct TileCoord {
@@ -258,6 +259,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     B200_REG_INC();
     constexpr int kCols = BLOCK_N / 2;  // columns owned by one thread
     constexpr int kChunks = kCols / 32;
+    constexpr int kStageRowBytes = 80;  // 64 bytes of data, padded against bank conflicts
+    constexpr int kStageWarpBytes = 32 * kStageRowBytes;
+    uint8_t* stage_base = smem + Cfg::kTileBytes + Cfg::kBarBytes + Cfg::kSchedBytes;
     const int q = warp & 3;             // TMEM lane quarter this warp may read
     const int half = (warp - 4) >> 2;   // which half of the tile's columns
     const int row_in_tile = q * 32 + lane;
@@ -342,27 +346,52 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       cur_tile = nxt_tile;
       if (!ok) break;
-      if (row_in_tile < c.rows_valid) {
-        __nv_bfloat16* drow = p.d + (long long)grow * p.ldd + col0;
+      // Store: the warp holds 32 rows x kCols columns, one row per lane.  Written directly, a
+      // store instruction would touch 32 different rows with 16 bytes each; instead each 32-column
+      // slab goes through a small per-warp shared-memory buffer and leaves as 8 rows x 64
+      // contiguous bytes per instruction (whole 32-byte sectors).
+      {
+        uint8_t* stage = stage_base + (warp - 4) * kStageWarpBytes;
+        const int warp_row0 = c.grow - lane;  // global row of lane 0
+        const int rows_here = c.rows_valid - q * 32;  // rows of this warp that belong to the group
 #pragma unroll
-        for (int j = 0; j < kCols; j += 8) {
-          if (col0 + j + 8 <= p.N) {
-            if (p.addend != nullptr) {
-              const uint4 raw = *reinterpret_cast<const uint4*>(p.addend + (long long)grow * p.ldc + col0 + j);
-              const __nv_bfloat162* cv = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        for (int cc = 0; cc < kChunks; ++cc) {
+          if (p.addend != nullptr && lane < rows_here) {
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const float2 f = __bfloat1622float2(cv[u]);
-                acc[j + 2 * u] += f.x;
-                acc[j + 2 * u + 1] += f.y;
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + cc * 32 + j + 8 <= p.N) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(p.addend + (long long)grow * p.ldc + col0 +
+                                                                  cc * 32 + j);
+                const __nv_bfloat162* cv = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const float2 f = __bfloat1622float2(cv[u]);
+                  acc[cc * 32 + j + 2 * u] += f.x;
+                  acc[cc * 32 + j + 2 * u + 1] += f.y;
+                }
               }
             }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
             uint4 v;
-            v.x = pack_bf16x2(acc[j + 0], acc[j + 1]);
-            v.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
-            v.z = pack_bf16x2(acc[j + 4], acc[j + 5]);
-            v.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
-            *reinterpret_cast<uint4*>(drow + j) = v;
+            v.x = pack_bf16x2(acc[cc * 32 + j + 0], acc[cc * 32 + j + 1]);
+            v.y = pack_bf16x2(acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
+            v.z = pack_bf16x2(acc[cc * 32 + j + 4], acc[cc * 32 + j + 5]);
+            v.w = pack_bf16x2(acc[cc * 32 + j + 6], acc[cc * 32 + j + 7]);
+            *reinterpret_cast<uint4*>(stage + lane * kStageRowBytes + j * 2) = v;
+          }
+          __syncwarp();
+          const int piece = lane & 3;          // 16-byte piece of the 64-byte row slab
+          const int col = col0 + cc * 32 + piece * 8;
+#pragma unroll
+          for (int pass = 0; pass < 4; ++pass) {
+            const int r = pass * 8 + (lane >> 2);
+            if (r < rows_here && col + 8 <= p.N) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + r * kStageRowBytes + piece * 16);
+              *reinterpret_cast<uint4*>(p.d + (long long)(warp_row0 + r) * p.ldd + col) = v;
+            }
           }
         }
       }

@@ -140,6 +140,9 @@ class ExpertParallelMoE:
         self.keys = placement(config, self.world, self.device)
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.bytes_moved = 0
+        self.last_recv_rows = 0
+        self.profile = False  # when set, phase boundaries are marked with CUDA events
+        self._marks = []
 
     # ------------------------------------------------------------------ reference API
     def expert_parameters(self):
@@ -167,12 +170,26 @@ class ExpertParallelMoE:
                     expert_map=self.config.expert_map, transport="nccl all_to_all_single, bf16 rows",
                     bytes_moved=self.bytes_moved)
 
+    def _mark(self, name):
+        if self.profile:
+            event = torch.cuda.Event(enable_timing=True)
+            event.record()
+            self._marks.append((name, event))
+
+    def phase_times(self):
+        """`[(phase, milliseconds)]` between consecutive marks of the profiled calls so far
+        (synchronises); clears the marks."""
+        torch.cuda.synchronize()
+        marks, self._marks = self._marks, []
+        return [(b[0], a[1].elapsed_time(b[1])) for a, b in zip(marks, marks[1:])]
+
     # ----------------------------------------------------------------------- forward
     def forward(self, x, residual=None, expert_ids=None, routing_weights=None):
         from . import layer, ops
 
         cfg = self.config
         with torch.no_grad():
+            self._mark("start")
             flat = x.reshape(-1, x.shape[-1]).contiguous()
             tokens = flat.shape[0]
             base = torch.zeros_like(flat) if residual is None else residual.reshape_as(flat).contiguous()
@@ -186,10 +203,14 @@ class ExpertParallelMoE:
                 weights = routing_weights.float().contiguous()
             keys = ids if cfg.expert_map == "contiguous" else self.keys[ids.long()]
             order, _offsets, slots, key_counts = ops.sort_assignments(keys, cfg.experts)
+            self._mark("route+sort")
             plan = make_plan(key_counts, self.group)
+            self.last_recv_rows = plan.recv_rows
+            self._mark("plan")
 
             rows = ops.dispatch(flat, order, cfg.top_k)
             row_weights = weights.reshape(-1)[order.long()].contiguous()
+            self._mark("gather rows")
             recv_x, work_x = exchange(rows, plan, self.group, async_op=True)
             recv_w, work_w = exchange(row_weights, plan, self.group, async_op=True)
             self.bytes_moved += rows.numel() * 2
@@ -206,12 +227,15 @@ class ExpertParallelMoE:
                     tensor.record_stream(torch.cuda.current_stream())
             work_x.wait()
             work_w.wait()
+            self._mark("dispatch a2a (+shared fwd)")
 
             x_q, x_s = ops.quantize_rows(recv_x)
             h13 = ops.grouped_gemm_fp8(x_q, x_s, *self.w13, plan.segment_offsets)
             a_q, a_s, _ = ops.swiglu_quantize(h13, limit=cfg.swiglu_limit)
             y = ops.grouped_gemm_fp8(a_q, a_s, *self.w2, plan.segment_offsets)
+            self._mark("expert fwd")
             y_back, _ = exchange(y, plan, self.group, back=True)
+            self._mark("combine a2a")
             self.bytes_moved += y.numel() * 2
             if self.shared is not None:
                 torch.cuda.current_stream().wait_stream(self.side_stream)
@@ -221,6 +245,7 @@ class ExpertParallelMoE:
             counts = key_counts if cfg.expert_map == "contiguous" else key_counts[self.keys.long()]
             aux, counts, psum = layer.routing_statistics(
                 logits, ids, counts, routing_mode=cfg.routing_mode, lengths=(tokens,), experts=cfg.experts)
+        self._mark("combine+stats")
         saved = dict(flat=flat, logits=logits, weights=weights, ids=ids, order=order, slots=slots, plan=plan,
                      recv_x=recv_x, recv_w=recv_w, h13=h13, shared_h13=shared_h13, counts=counts,
                      shape=x.shape)
@@ -235,8 +260,10 @@ class ExpertParallelMoE:
         plan = saved["plan"]
         with torch.no_grad():
             flat = saved["flat"]
+            self._mark("bwd start")
             dy = grad_output.reshape_as(flat).contiguous()
             dy_rows = ops.dispatch(dy, saved["order"], cfg.top_k)
+            self._mark("gather dy rows")
             recv_dy, work = exchange(dy_rows, plan, self.group, async_op=True)
             self.bytes_moved += dy_rows.numel() * 2
             shared_grads = (None, None, None)
@@ -251,6 +278,7 @@ class ExpertParallelMoE:
                     if tensor is not None:
                         tensor.record_stream(torch.cuda.current_stream())
             work.wait()
+            self._mark("dy dispatch a2a (+shared bwd)")
 
             identity = torch.arange(plan.recv_rows, dtype=torch.int32, device=flat.device)
             dy_q, dy_s = ops.quantize_rows(recv_dy)
@@ -259,6 +287,7 @@ class ExpertParallelMoE:
                 saved["h13"], r, saved["recv_w"], identity, limit=cfg.swiglu_limit, quantized=True,
                 rounded=need_experts, scaled_activation=need_experts)
             grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, *self.w13, plan.segment_offsets, b_mn_major=True)
+            self._mark("expert dgrad")
             back_rows, work_rows = exchange(grad_rows, plan, self.group, back=True, async_op=True)
             back_score, work_score = exchange(dscore, plan, self.group, back=True, async_op=True)
             self.bytes_moved += grad_rows.numel() * 2
@@ -268,8 +297,10 @@ class ExpertParallelMoE:
                                             self.weight_grad_dtype)
                 grad_w13 = ops.grouped_wgrad(gh_b, saved["recv_x"], plan.segment_offsets, self.local_experts,
                                              self.weight_grad_dtype)
+            self._mark("expert wgrad (issued)")
             work_rows.wait()
             work_score.wait()
+            self._mark("dx return a2a (+wgrad)")
             grad_x = ops.dispatch_backward(back_rows, saved["slots"])
             grad_route_weights = ops.gather_scalar(back_score, saved["slots"])
             grad_logits = layer.routing_gradient(
@@ -282,6 +313,7 @@ class ExpertParallelMoE:
             if self.shared is not None:
                 torch.cuda.current_stream().wait_stream(self.side_stream)
                 grad_x.add_(shared_grads[0])
+        self._mark("scatter+router grads")
         return dict(grad_x=grad_x.reshape(saved["shape"]), grad_router=grad_router, grad_w13=grad_w13,
                     grad_w2=grad_w2, grad_shared_w13=shared_grads[1], grad_shared_w2=shared_grads[2])
 
