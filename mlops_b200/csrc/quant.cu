@@ -36,13 +36,33 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
   }
 }
 
+// E4M3 bytes of clamp(v / scale, +-448) with the division rounded to nearest, i.e. exactly
+// what `x / scale` followed by the cast gives on a CPU.  Fast path: multiply by the rounded
+// reciprocal; the true quotient lies within 2^-22 (relative) of that product, and the cast is
+// monotonic, so when both ends of the interval [q(1-2^-21), q(1+2^-21)] cast to the same
+// byte that byte is the exact answer.  Otherwise (a value within an ulp of an E4M3 rounding
+// boundary, about one lane in ten thousand) the eight values take the exact division.
 __device__ __forceinline__ uint2 quantize8(const float (&v)[8], float scale) {
+  const float inv = __frcp_rn(scale);
   uint32_t w[2] = {0, 0};
+  bool exact = true;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float q = __fdiv_rn(v[i], scale);
-    q = fminf(fmaxf(q, -448.0f), 448.0f);
-    w[i >> 2] |= (uint32_t)to_e4m3(q) << (8 * (i & 3));
+  for (int i = 0; i < 8; i += 2) {
+    const float q0 = v[i] * inv, q1 = v[i + 1] * inv;
+    const float e0 = q0 * 4.76837158203125e-7f, e1 = q1 * 4.76837158203125e-7f;  // 2^-21
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q0 + e0, q1 + e1), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0 - e0, q1 - e1), __NV_SATFINITE, __NV_E4M3);
+    exact = exact && (hi == lo);
+    w[i >> 2] |= (hi & 0xffffu) << (8 * (i & 3));
+  }
+  if (!exact) {
+    w[0] = w[1] = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float q = __fdiv_rn(v[i], scale);
+      q = fminf(fmaxf(q, -448.0f), 448.0f);
+      w[i >> 2] |= (uint32_t)to_e4m3(q) << (8 * (i & 3));
+    }
   }
   return make_uint2(w[0], w[1]);
 }
@@ -68,20 +88,26 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const i
   const __nv_bfloat16* xr = x + src * ldx;
   uint8_t* qr = q + r * ldq;
   if (mode == 0) {
-    for (int c0 = 0; c0 < D; c0 += 256) {
-      const int c = c0 + lane * 8;
-      float v[8];
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (c < D) raw = *reinterpret_cast<const uint4*>(xr + c);
-      unpack8(raw, v);
-      float amax = 0.f;
+    // two 256-column steps per iteration: both loads are in flight before either is used
+    for (int c0 = 0; c0 < D; c0 += 512) {
+      const int ca = c0 + lane * 8, cb = ca + 256;
+      uint4 raw_a = make_uint4(0, 0, 0, 0), raw_b = make_uint4(0, 0, 0, 0);
+      if (ca < D) raw_a = *reinterpret_cast<const uint4*>(xr + ca);
+      if (cb < D) raw_b = *reinterpret_cast<const uint4*>(xr + cb);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      amax = halfwarp_max(amax);
-      const float scale = fmaxf(amax * kInv448, 1e-12f);
-      if (c < D) {
-        *reinterpret_cast<uint2*>(qr + c) = quantize8(v, scale);
-        if ((lane & 15) == 0) scales[r * s_row + (long long)(c >> 7) * s_kb] = scale;
+      for (int h = 0; h < 2; ++h) {
+        const int c = h == 0 ? ca : cb;
+        float v[8];
+        unpack8(h == 0 ? raw_a : raw_b, v);
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = halfwarp_max(amax);
+        const float scale = fmaxf(amax * kInv448, 1e-12f);
+        if (c < D) {
+          *reinterpret_cast<uint2*>(qr + c) = quantize8(v, scale);
+          if ((lane & 15) == 0) scales[r * s_row + (long long)(c >> 7) * s_kb] = scale;
+        }
       }
     }
   } else {
@@ -133,7 +159,7 @@ swiglu_quant_kernel(const __nv_bfloat16* __restrict__ h13, long long ldh, long l
         gi = fminf(gi, limit);
         ui = fminf(fmaxf(ui, -limit), limit);
       }
-      const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gi));
+      const float sig = __frcp_rn(1.0f + expf(-gi));
       a[i] = gi * sig * ui;
       amax = fmaxf(amax, fabsf(a[i]));
     }
@@ -193,7 +219,7 @@ dswiglu_routed_kernel(const __nv_bfloat16* __restrict__ h13, long long ldh,
         gi = fminf(gi, limit);
         ui = fminf(fmaxf(ui, -limit), limit);
       }
-      const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gi));
+      const float sig = __frcp_rn(1.0f + expf(-gi));
       const float silu = gi * sig;
       const float act = silu * ui;
       dot = fmaf(rv[i], act, dot);
