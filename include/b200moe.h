@@ -163,6 +163,15 @@ int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
                              int32_t* status, void* stream);
 
 /*
+ * Process-wide cap on the CTAs the persistent tensor-core kernels launch (they launch one CTA
+ * per SM and leave no room for another kernel on an SM they occupy).  A caller that overlaps
+ * them with communication kernels keeps a few SMs free: ctas = SM count - reserved; 0 restores
+ * "every SM".  The reference's expert-parallel runtime reserves SMs for its transport the same
+ * way (src/mlops/expert_parallel/quack/config.py, `num_sms`).
+ */
+int b200moe_set_cta_limit(int ctas);
+
+/*
  * Rank-r side products of expert LoRA on expert-sorted rows (rank <= 64, bf16, fp32 sums).
  * project: t[row, 0:rank] = x[row, 0:K] . W_e, with W [experts, rank, K] (rank_major != 0) or
  *          [experts, K, rank].  expand: c[row, 0:N] = scale * t[row, 0:rank] . W_e, with

@@ -508,3 +508,9 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
   }
   return b_mn_major ? launch_gemm<256, true>(ta, tb, p, s) : launch_gemm<256, false>(ta, tb, p, s);
 }
+
+extern "C" int b200moe_set_cta_limit(int ctas) {
+  if (ctas < 0) return B200MOE_ERR_ARG;
+  set_cta_limit(ctas);
+  return B200MOE_OK;
+}

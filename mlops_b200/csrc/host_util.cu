@@ -18,7 +18,16 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+static int g_cta_limit = 0;  // 0 = every SM
+
 int sm_count() {
+  const int n = sm_count_device();
+  return (g_cta_limit > 0 && g_cta_limit < n) ? g_cta_limit : n;
+}
+
+void set_cta_limit(int n) { g_cta_limit = n > 0 ? n : 0; }
+
+int sm_count_device() {
   static int cached[64];
   static bool have[64];
   int dev = 0;

@@ -26,7 +26,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_tiled();
-int sm_count();  // SM count of the current device (cached per device)
+int sm_count_device();      // SM count of the current device (cached per device)
+int sm_count();             // CTAs a persistent kernel may launch: the SM count, or the limit below
+void set_cta_limit(int n);  // n > 0: persistent kernels launch at most n CTAs; 0: no limit
 
 // Encodes a row-major tensor of `rank` dims.  dims[0] is the innermost (contiguous)
 // extent in elements; strides_bytes[i] is the byte pitch of dims[i+1].

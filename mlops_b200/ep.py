@@ -85,27 +85,40 @@ class ExchangePlan:
     send_rows: int
 
 
-def make_plan(send_counts: torch.Tensor, group) -> ExchangePlan:
-    """`send_counts [E]`: rows per placement key held by this rank (any integer dtype, on the
-    group's device). One all-to-all of the counts, one host read of the split sizes."""
+def make_plans(send_counts: torch.Tensor, group) -> list[ExchangePlan]:
+    """`send_counts [C, E]`: rows per placement key of each of C token chunks held by this rank
+    (any integer dtype, on the group's device). One all-to-all of all the counts and one host
+    read of the split sizes give one plan per chunk."""
     world = dist.get_world_size(group)
-    local = send_counts.numel() // world
-    mine = send_counts.to(torch.int64).view(world, local).contiguous()
+    chunks, experts = send_counts.shape
+    local = experts // world
+    mine = send_counts.to(torch.int64).view(chunks, world, local).permute(1, 0, 2).contiguous()  # [G, C, El]
     theirs = torch.empty_like(mine)
     dist.all_to_all_single(theirs, mine, group=group)
-    sizes = torch.stack([mine.sum(1), theirs.sum(1)]).cpu()  # the one device-to-host copy
-    send_splits, recv_splits = sizes[0].tolist(), sizes[1].tolist()
-    offsets = torch.zeros(world * local + 1, dtype=torch.int32, device=send_counts.device)
-    offsets[1:] = theirs.reshape(-1).cumsum(0).to(torch.int32)
-    return ExchangePlan(send_splits, recv_splits, offsets, int(sum(recv_splits)), int(sum(send_splits)))
+    sizes = torch.stack([mine.sum(2), theirs.sum(2)]).cpu()  # the one device-to-host copy: [2, G, C]
+    plans = []
+    for c in range(chunks):
+        send_splits, recv_splits = sizes[0, :, c].tolist(), sizes[1, :, c].tolist()
+        offsets = torch.zeros(world * local + 1, dtype=torch.int32, device=send_counts.device)
+        offsets[1:] = theirs[:, c, :].reshape(-1).cumsum(0).to(torch.int32)
+        plans.append(ExchangePlan(send_splits, recv_splits, offsets, int(sum(recv_splits)), int(sum(send_splits))))
+    return plans
 
 
-def exchange(rows: torch.Tensor, plan: ExchangePlan, group, *, back: bool = False, async_op: bool = False):
+def make_plan(send_counts: torch.Tensor, group) -> ExchangePlan:
+    """The single-chunk form of `make_plans`: `send_counts [E]`."""
+    return make_plans(send_counts.reshape(1, -1), group)[0]
+
+
+def exchange(rows: torch.Tensor, plan: ExchangePlan, group, *, back: bool = False, async_op: bool = False,
+             out: torch.Tensor | None = None):
     """Dispatch (`back=False`: send my sorted rows, receive the rows of my experts) or return
-    (`back=True`: the inverse). Returns `(received, work)`; `work` is None unless `async_op`."""
+    (`back=True`: the inverse). Returns `(received, work)`; `work` is None unless `async_op`.
+    `out` (optional) receives the rows instead of a fresh tensor."""
     send, recv = (plan.recv_splits, plan.send_splits) if back else (plan.send_splits, plan.recv_splits)
     total = plan.send_rows if back else plan.recv_rows
-    received = torch.empty((total, *rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    received = out if out is not None else torch.empty((total, *rows.shape[1:]), dtype=rows.dtype,
+                                                       device=rows.device)
     payload, target = rows, received
     if rows.dtype == torch.float8_e4m3fn:  # collectives move bytes
         payload, target = rows.view(torch.uint8), received.view(torch.uint8)
@@ -124,7 +137,7 @@ class ExpertParallelMoE:
     with local expert gradients and UN-reduced replicated gradients."""
 
     def __init__(self, config: ExpertParallelConfig, ep_group, *, router_weight, w13, w2, router_bias=None,
-                 shared=None, device=None, weight_grad_dtype=torch.bfloat16):
+                 shared=None, device=None, weight_grad_dtype=torch.bfloat16, chunks=2, comm_sms=16):
         self.config = config
         self.group = ep_group
         self.world = dist.get_world_size(ep_group)
@@ -137,6 +150,14 @@ class ExpertParallelMoE:
         self.router_weight, self.router_bias = router_weight, router_bias
         self.w13, self.w2, self.shared = w13, w2, shared
         self.weight_grad_dtype = weight_grad_dtype
+        self.chunks = int(chunks)
+        self.comm_sms = int(comm_sms) if self.world > 1 else 0
+        if self.comm_sms and self.device.type == "cuda":
+            # the persistent GEMMs leave these SMs to the all-to-all kernels they overlap with
+            from . import ops
+
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            ops.set_cta_limit(max(sms - self.comm_sms, 2) // 2 * 2)
         self.keys = placement(config, self.world, self.device)
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.bytes_moved = 0
@@ -168,6 +189,7 @@ class ExpertParallelMoE:
     def report(self):
         return dict(world=self.world, rank=self.rank, local_experts=self.local_experts,
                     expert_map=self.config.expert_map, transport="nccl all_to_all_single, bf16 rows",
+                    chunks=self.chunks,
                     bytes_moved=self.bytes_moved)
 
     def _mark(self, name):
@@ -185,13 +207,15 @@ class ExpertParallelMoE:
 
     # ----------------------------------------------------------------------- forward
     def forward(self, x, residual=None, expert_ids=None, routing_weights=None):
+        """Tokens are processed in `self.chunks` contiguous chunks: the dispatch of chunk c+1
+        and the return of chunk c are in flight while chunk c's expert GEMMs run."""
         from . import layer, ops
 
         cfg = self.config
         with torch.no_grad():
             self._mark("start")
             flat = x.reshape(-1, x.shape[-1]).contiguous()
-            tokens = flat.shape[0]
+            tokens, width = flat.shape
             base = torch.zeros_like(flat) if residual is None else residual.reshape_as(flat).contiguous()
             logits = layer.router_logits(flat, self.router_weight)
             if expert_ids is None:
@@ -202,21 +226,38 @@ class ExpertParallelMoE:
                 ids = expert_ids.to(torch.int32).contiguous()
                 weights = routing_weights.float().contiguous()
             keys = ids if cfg.expert_map == "contiguous" else self.keys[ids.long()]
-            order, _offsets, slots, key_counts = ops.sort_assignments(keys, cfg.experts)
+            chunks = max(1, min(self.chunks, tokens))
+            bounds = [tokens * c // chunks for c in range(chunks + 1)]
+            parts = []
+            for c in range(chunks):
+                lo, hi = bounds[c], bounds[c + 1]
+                order, _offsets, slots, key_counts = ops.sort_assignments(keys[lo:hi], cfg.experts)
+                parts.append(dict(lo=lo, hi=hi, order=order, slots=slots, key_counts=key_counts))
             self._mark("route+sort")
-            plan = make_plan(key_counts, self.group)
-            self.last_recv_rows = plan.recv_rows
+            plans = make_plans(torch.stack([part["key_counts"] for part in parts]), self.group)
             self._mark("plan")
+            total = sum(plan.recv_rows for plan in plans)
+            self.last_recv_rows = total
+            starts = [0]
+            for plan in plans:
+                starts.append(starts[-1] + plan.recv_rows)
+            recv_x = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
+            recv_w = torch.empty(total, dtype=torch.float32, device=flat.device)
+            h13 = torch.empty((total, 2 * cfg.intermediate), dtype=torch.bfloat16, device=flat.device)
 
-            rows = ops.dispatch(flat, order, cfg.top_k)
-            row_weights = weights.reshape(-1)[order.long()].contiguous()
-            self._mark("gather rows")
-            recv_x, work_x = exchange(rows, plan, self.group, async_op=True)
-            recv_w, work_w = exchange(row_weights, plan, self.group, async_op=True)
-            self.bytes_moved += rows.numel() * 2
+            def send(c):
+                part = parts[c]
+                rows = ops.dispatch(flat[part["lo"]:part["hi"]], part["order"], cfg.top_k)
+                row_weights = weights[part["lo"]:part["hi"]].reshape(-1)[part["order"].long()].contiguous()
+                _, wx = exchange(rows, plans[c], self.group, async_op=True, out=recv_x[starts[c]:starts[c + 1]])
+                _, ww = exchange(row_weights, plans[c], self.group, async_op=True,
+                                 out=recv_w[starts[c]:starts[c + 1]])
+                self.bytes_moved += rows.numel() * 2
+                return rows, row_weights, wx, ww
 
+            in_flight = send(0)
             shared_h13 = None
-            if self.shared is not None:  # overlaps the dispatch
+            if self.shared is not None:  # overlaps the first dispatch
                 side = self.side_stream
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
@@ -225,31 +266,40 @@ class ExpertParallelMoE:
                     base = base + y_shared
                 for tensor in (base, shared_h13):  # produced on the side stream, consumed on this one
                     tensor.record_stream(torch.cuda.current_stream())
-            work_x.wait()
-            work_w.wait()
-            self._mark("dispatch a2a (+shared fwd)")
-
-            x_q, x_s = ops.quantize_rows(recv_x)
-            h13 = ops.grouped_gemm_fp8(x_q, x_s, *self.w13, plan.segment_offsets)
-            a_q, a_s, _ = ops.swiglu_quantize(h13, limit=cfg.swiglu_limit)
-            y = ops.grouped_gemm_fp8(a_q, a_s, *self.w2, plan.segment_offsets)
-            self._mark("expert fwd")
-            y_back, _ = exchange(y, plan, self.group, back=True)
-            self._mark("combine a2a")
-            self.bytes_moved += y.numel() * 2
+            returns = []
+            for c in range(chunks):
+                nxt = send(c + 1) if c + 1 < chunks else None
+                in_flight[2].wait()
+                in_flight[3].wait()
+                in_flight = nxt
+                self._mark("dispatch wait")
+                rows = slice(starts[c], starts[c + 1])
+                x_q, x_s = ops.quantize_rows(recv_x[rows])
+                ops.grouped_gemm_fp8(x_q, x_s, *self.w13, plans[c].segment_offsets, out=h13[rows])
+                a_q, a_s, _ = ops.swiglu_quantize(h13[rows], limit=cfg.swiglu_limit)
+                y = ops.grouped_gemm_fp8(a_q, a_s, *self.w2, plans[c].segment_offsets)
+                self._mark("expert fwd")
+                y_back, work = exchange(y, plans[c], self.group, back=True, async_op=True)
+                self.bytes_moved += y.numel() * 2
+                returns.append((y, y_back, work))
             if self.shared is not None:
                 torch.cuda.current_stream().wait_stream(self.side_stream)
-            output = ops.combine(y_back, slots, weights, base).reshape(x.shape)
-
+            output = torch.empty_like(flat)
+            for c, (y, y_back, work) in enumerate(returns):
+                work.wait()
+                part = parts[c]
+                output[part["lo"]:part["hi"]] = ops.combine(
+                    y_back, part["slots"], weights[part["lo"]:part["hi"]], base[part["lo"]:part["hi"]])
+            self._mark("combine a2a wait + combine")
+            key_counts = torch.stack([part["key_counts"] for part in parts]).sum(0)
             # the sort counted by placement key; statistics want expert order
             counts = key_counts if cfg.expert_map == "contiguous" else key_counts[self.keys.long()]
             aux, counts, psum = layer.routing_statistics(
                 logits, ids, counts, routing_mode=cfg.routing_mode, lengths=(tokens,), experts=cfg.experts)
-        self._mark("combine+stats")
-        saved = dict(flat=flat, logits=logits, weights=weights, ids=ids, order=order, slots=slots, plan=plan,
-                     recv_x=recv_x, recv_w=recv_w, h13=h13, shared_h13=shared_h13, counts=counts,
-                     shape=x.shape)
-        return output, aux, counts, psum, saved
+        self._mark("stats")
+        saved = dict(flat=flat, logits=logits, weights=weights, ids=ids, parts=parts, plans=plans, starts=starts,
+                     recv_x=recv_x, recv_w=recv_w, h13=h13, shared_h13=shared_h13, counts=counts, shape=x.shape)
+        return output.reshape(x.shape), aux, counts, psum, saved
 
     # ---------------------------------------------------------------------- backward
     def backward(self, saved, grad_output, grad_aux=None, grad_probability_sum=None, *, need_router=True,
@@ -257,17 +307,26 @@ class ExpertParallelMoE:
         from . import layer, ops
 
         cfg = self.config
-        plan = saved["plan"]
+        plans, parts, starts = saved["plans"], saved["parts"], saved["starts"]
+        chunks = len(plans)
         with torch.no_grad():
-            flat = saved["flat"]
             self._mark("bwd start")
+            flat = saved["flat"]
+            tokens, width = flat.shape
+            total = starts[-1]
             dy = grad_output.reshape_as(flat).contiguous()
-            dy_rows = ops.dispatch(dy, saved["order"], cfg.top_k)
-            self._mark("gather dy rows")
-            recv_dy, work = exchange(dy_rows, plan, self.group, async_op=True)
-            self.bytes_moved += dy_rows.numel() * 2
+            recv_dy = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
+
+            def send(c):
+                part = parts[c]
+                rows = ops.dispatch(dy[part["lo"]:part["hi"]], part["order"], cfg.top_k)
+                _, work = exchange(rows, plans[c], self.group, async_op=True, out=recv_dy[starts[c]:starts[c + 1]])
+                self.bytes_moved += rows.numel() * 2
+                return rows, work
+
+            in_flight = send(0)
             shared_grads = (None, None, None)
-            if self.shared is not None:  # overlaps the dispatch of dy
+            if self.shared is not None:  # overlaps the first dispatch of dy
                 side = self.side_stream
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
@@ -277,35 +336,53 @@ class ExpertParallelMoE:
                 for tensor in shared_grads:
                     if tensor is not None:
                         tensor.record_stream(torch.cuda.current_stream())
-            work.wait()
-            self._mark("dy dispatch a2a (+shared bwd)")
-
-            identity = torch.arange(plan.recv_rows, dtype=torch.int32, device=flat.device)
-            dy_q, dy_s = ops.quantize_rows(recv_dy)
-            r = ops.grouped_gemm_fp8(dy_q, dy_s, *self.w2, plan.segment_offsets, b_mn_major=True)
-            dscore, gh_q, gh_s, gh_b, act_scaled = ops.dswiglu_routed(
-                saved["h13"], r, saved["recv_w"], identity, limit=cfg.swiglu_limit, quantized=True,
-                rounded=need_experts, scaled_activation=need_experts)
-            grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, *self.w13, plan.segment_offsets, b_mn_major=True)
-            self._mark("expert dgrad")
-            back_rows, work_rows = exchange(grad_rows, plan, self.group, back=True, async_op=True)
-            back_score, work_score = exchange(dscore, plan, self.group, back=True, async_op=True)
-            self.bytes_moved += grad_rows.numel() * 2
+            gh_b = act_scaled = None
+            if need_experts:
+                gh_b = torch.empty((total, 2 * cfg.intermediate), dtype=torch.bfloat16, device=flat.device)
+                act_scaled = torch.empty((total, cfg.intermediate), dtype=torch.bfloat16, device=flat.device)
+            returns = []
+            for c in range(chunks):
+                nxt = send(c + 1) if c + 1 < chunks else None
+                in_flight[1].wait()
+                in_flight = nxt
+                self._mark("dy dispatch wait")
+                rows = slice(starts[c], starts[c + 1])
+                count = starts[c + 1] - starts[c]
+                identity = torch.arange(count, dtype=torch.int32, device=flat.device)
+                dy_q, dy_s = ops.quantize_rows(recv_dy[rows])
+                r = ops.grouped_gemm_fp8(dy_q, dy_s, *self.w2, plans[c].segment_offsets, b_mn_major=True)
+                dscore, gh_q, gh_s, _, _ = ops.dswiglu_routed(
+                    saved["h13"][rows], r, saved["recv_w"][rows], identity, limit=cfg.swiglu_limit, quantized=True,
+                    rounded=need_experts, scaled_activation=need_experts,
+                    rounded_out=None if gh_b is None else gh_b[rows],
+                    scaled_out=None if act_scaled is None else act_scaled[rows])
+                grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, *self.w13, plans[c].segment_offsets, b_mn_major=True)
+                self._mark("expert dgrad")
+                back_rows, work_rows = exchange(grad_rows, plans[c], self.group, back=True, async_op=True)
+                back_score, work_score = exchange(dscore, plans[c], self.group, back=True, async_op=True)
+                self.bytes_moved += grad_rows.numel() * 2
+                returns.append((grad_rows, dscore, back_rows, back_score, work_rows, work_score))
             grad_w13 = grad_w2 = None
-            if need_experts:  # local weight gradients overlap the return of dx rows
-                grad_w2 = ops.grouped_wgrad(recv_dy, act_scaled, plan.segment_offsets, self.local_experts,
+            if need_experts:  # local weight gradients over every chunk; overlaps the last return
+                all_offsets = torch.cat(
+                    [plans[c].segment_offsets[: -1 if c + 1 < chunks else None] + starts[c] for c in range(chunks)])
+                grad_w2 = ops.grouped_wgrad(recv_dy, act_scaled, all_offsets, self.local_experts,
                                             self.weight_grad_dtype)
-                grad_w13 = ops.grouped_wgrad(gh_b, saved["recv_x"], plan.segment_offsets, self.local_experts,
+                grad_w13 = ops.grouped_wgrad(gh_b, saved["recv_x"], all_offsets, self.local_experts,
                                              self.weight_grad_dtype)
             self._mark("expert wgrad (issued)")
-            work_rows.wait()
-            work_score.wait()
-            self._mark("dx return a2a (+wgrad)")
-            grad_x = ops.dispatch_backward(back_rows, saved["slots"])
-            grad_route_weights = ops.gather_scalar(back_score, saved["slots"])
+            grad_x = torch.empty_like(flat)
+            grad_route_weights = torch.empty_like(saved["weights"])
+            for c, (_rows, _score, back_rows, back_score, work_rows, work_score) in enumerate(returns):
+                work_rows.wait()
+                work_score.wait()
+                part = parts[c]
+                grad_x[part["lo"]:part["hi"]] = ops.dispatch_backward(back_rows, part["slots"])
+                grad_route_weights[part["lo"]:part["hi"]] = ops.gather_scalar(back_score, part["slots"])
+            self._mark("dx return wait + scatter")
             grad_logits = layer.routing_gradient(
                 grad_aux, grad_probability_sum, grad_route_weights, saved["weights"], saved["ids"],
-                saved["logits"], saved["counts"], routing_mode=cfg.routing_mode, lengths=(flat.shape[0],))
+                saved["logits"], saved["counts"], routing_mode=cfg.routing_mode, lengths=(tokens,))
             grad_router = None
             if need_router:
                 grad_router = layer._router_weight_gradient(grad_logits, flat, self.router_weight.dtype)
@@ -313,7 +390,7 @@ class ExpertParallelMoE:
             if self.shared is not None:
                 torch.cuda.current_stream().wait_stream(self.side_stream)
                 grad_x.add_(shared_grads[0])
-        self._mark("scatter+router grads")
+        self._mark("router grads")
         return dict(grad_x=grad_x.reshape(saved["shape"]), grad_router=grad_router, grad_w13=grad_w13,
                     grad_w2=grad_w2, grad_shared_w13=shared_grads[1], grad_shared_w2=shared_grads[2])
 
@@ -323,4 +400,8 @@ class ExpertParallelMoE:
         return output, grads["grad_x"], aux, counts
 
     def close(self):
+        if self.comm_sms and self.device.type == "cuda":
+            from . import ops
+
+            ops.set_cta_limit(0)
         self.side_stream = None

@@ -50,6 +50,12 @@ class _Timed:
         return False
 
 
+def set_cta_limit(ctas: int) -> None:
+    """Cap the CTAs of the persistent GEMM kernels (0 = every SM), so that communication
+    kernels running beside them find free SMs."""
+    check(lib.b200moe_set_cta_limit(int(ctas)), "set_cta_limit")
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -230,7 +236,7 @@ def swiglu_quantize(h13, *, limit=None, quantized=True, rounded=False):
 
 
 def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, rounded=False,
-                   scaled_activation=False):
+                   scaled_activation=False, rounded_out=None, scaled_out=None):
     """One pass over h13 and r: returns (dscore [rows] fp32, grad_h13_q, grad_h13_scales,
     grad_h13_bf16, act_scaled)."""
     _need_cuda(h13, r, route_weights, order)
@@ -243,9 +249,9 @@ def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, 
         gq = torch.empty((rows, two_f), dtype=FP8, device=device)
         gs = _scale_buffer(rows, (two_f + 127) // 128, device)
     if rounded:
-        gb = torch.empty((rows, two_f), dtype=torch.bfloat16, device=device)
+        gb = torch.empty((rows, two_f), dtype=torch.bfloat16, device=device) if rounded_out is None else rounded_out
     if scaled_activation:
-        a_s = torch.empty((rows, width), dtype=torch.bfloat16, device=device)
+        a_s = torch.empty((rows, width), dtype=torch.bfloat16, device=device) if scaled_out is None else scaled_out
     weights_flat = route_weights.reshape(-1)
     if rows == 0:
         return dscore, gq, gs, gb, a_s
@@ -253,8 +259,8 @@ def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, 
         lib.b200moe_dswiglu_routed(
             h13.data_ptr(), h13.stride(0), r.data_ptr(), r.stride(0), weights_flat.data_ptr(),
             order.data_ptr(), rows, width, dscore.data_ptr(), _ptr(gq), two_f, _ptr(gs),
-            0 if gs is None else gs.stride(0), 0 if gs is None else gs.stride(1), _ptr(gb), two_f,
-            _ptr(a_s), width, 0.0 if limit is None else float(limit), 0 if limit is None else 1,
+            0 if gs is None else gs.stride(0), 0 if gs is None else gs.stride(1), _ptr(gb),
+            two_f if gb is None else gb.stride(0), _ptr(a_s), width if a_s is None else a_s.stride(0), 0.0 if limit is None else float(limit), 0 if limit is None else 1,
             _stream(),
         ),
         "dswiglu_routed",

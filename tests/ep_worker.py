@@ -52,7 +52,8 @@ def main():
     module = ep.ExpertParallelMoE(config, dist.group.WORLD, router_weight=router, router_bias=bias,
                                   w13=(w13[0][pick].contiguous(), w13[1][pick].contiguous()),
                                   w2=(w2[0][pick].contiguous(), w2[1][pick].contiguous()), shared=shared,
-                                  device=device, weight_grad_dtype=torch.float32)
+                                  device=device, weight_grad_dtype=torch.float32,
+                                  chunks=3 if expert_map == "strided" else 1)
     output, aux, counts, psum, saved = module.forward(x, residual)
     grads = module.backward(saved, dy)
     torch.cuda.synchronize()
