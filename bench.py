@@ -15,6 +15,8 @@ Workloads (shapes only; weights are random, data synthetic, seeded):
       T=32768 tokens per GPU (the configuration the headline metric is quoted on)
   c4p the same layer at profiling size (32 experts, T=4096: the same 1024 rows per expert,
       a few GB on the device) for ncu captures
+  c5  Qwen3-30B-A3B-shaped with rank-16 LoRA on a frozen base and Zipf(1.2) expert popularity:
+      D=2048, 128 experts, F=768, softmax top-8, T=65536 (single GPU only)
   c3  Mixtral-8x7B-shaped: D=4096, 8 experts, F=14336, softmax top-2, T=16384
   c1  the small CPU-runnable case: D=256, 8 experts, F=512, softmax top-2, T=512
 """
@@ -43,6 +45,9 @@ WORKLOADS = {
                 mode="sigmoid_noaux_tc", n_group=8, topk_group=4, scaling=2.5, shared=True),
     "c3": dict(name="mixtral_8x7b_shaped_moe_layer", T=16384, D=4096, E=8, F=14336, K=2,
                mode="softmax_then_topk", n_group=1, topk_group=1, scaling=1.0, shared=False),
+    "c5": dict(name="qwen3_30b_a3b_shaped_moe_layer_lora_zipf", T=65536, D=2048, E=128, F=768, K=8,
+               mode="softmax_then_topk", n_group=1, topk_group=1, scaling=1.0, shared=False, lora_rank=16,
+               zipf=1.2),
     "c1": dict(name="small_moe_layer", T=512, D=256, E=8, F=512, K=2,
                mode="softmax_then_topk", n_group=1, topk_group=1, scaling=1.0, shared=False),
 }
@@ -231,6 +236,27 @@ def gpu_arm(args, cfg):
                   (torch.randn(D, F, device=device, generator=gw) * 0.02).bfloat16())
     del g
 
+    lora = None
+    if cfg.get("lora_rank"):
+        if distributed:
+            raise SystemExit("the LoRA workload runs on one GPU (expert-parallel LoRA is not built)")
+        from mlops_b200.lora import expert_lora
+        from mlops_b200.weights import BlockFP8Weight
+
+        r = cfg["lora_rank"]
+        # skew lives in the data: x[:, 0] = 1 and Wr[:, 0] = log p_e shift the logits by log p_e
+        popularity = torch.arange(1, E + 1, device=device).float().pow(-cfg["zipf"])
+        router[:, 0] = torch.log(popularity / popularity.sum())
+        x[:, 0] = 1.0
+        x_host[:, 0] = 1.0
+        factors = [(torch.randn(E, r, D, device=device, generator=gw) * 0.02).bfloat16(),
+                   (torch.randn(E, 2 * F, r, device=device, generator=gw) * 0.01).bfloat16(),
+                   (torch.randn(E, r, F, device=device, generator=gw) * 0.02).bfloat16(),
+                   (torch.randn(E, D, r, device=device, generator=gw) * 0.01).bfloat16()]
+        for f in factors:
+            f.requires_grad_(True)
+        lora = dict(factors=factors, w13=BlockFP8Weight(*w13), w2=BlockFP8Weight(*w2))
+
     route_kwargs = dict(top_k=K, routing_mode=cfg["mode"], router_bias=bias, n_group=cfg["n_group"],
                         topk_group=cfg["topk_group"], routed_scaling=cfg["scaling"])
     ep = None
@@ -251,6 +277,12 @@ def gpu_arm(args, cfg):
             result = ep.forward_backward(x_in, residual, dy_in)
             rows_received.append(ep.last_recv_rows)
             return result
+        if lora is not None:
+            x_leaf = x_in.detach().requires_grad_(True)
+            out, aux, counts, _ = expert_lora(x_leaf, residual, router, lora["w13"], lora["w2"], *lora["factors"],
+                                              top_k=K, routing_mode=cfg["mode"], scale=1.0)
+            grads = torch.autograd.grad(out, [x_leaf, *lora["factors"]], dy_in)
+            return out.detach(), grads[0], aux.detach(), counts
         base, shared_h13 = residual, None
         if shared is not None:
             y_shared, shared_h13 = layer.shared_expert_forward(x_in, *shared)
@@ -332,7 +364,7 @@ def gpu_arm(args, cfg):
     achieved = fp8_flops / (fp8_ms * 1e-3) / 1e12 if fp8_ms > 0 else 0.0
     peak_fp8 = 2.0 * peaks["bf16_tflops_sustained"]
     rows = T * K
-    routed_flops = 18.0 * D * F * rows
+    routed_flops = (12.0 if lora is not None else 18.0) * D * F * rows  # a frozen base has no base wgrad
     shared_flops = 18.0 * D * F * T if cfg["shared"] else 0.0
     tokens_total = T * world
     line = {
@@ -370,9 +402,11 @@ def gpu_arm(args, cfg):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture; filled
-# from profiles/ once a capture of the workload exists.
-TRAFFIC_BYTES_PER_LAUNCH: dict[str, float] = {}
+# DRAM bytes (read + write) per launch of the dominant kernel, averaged over its four launches
+# of a step, from the ncu capture summarised in profiles/grouped_gemm_fp8_c4p.md (6.19 GB over
+# four launches at 32768 rows x 32 experts). Traffic is operands once + output once, so the
+# full-size figure scales with rows and experts (x8).
+TRAFFIC_BYTES_PER_LAUNCH: dict[str, float] = {"c4p": 6.19e9 / 4, "c4": 8 * 6.19e9 / 4}
 
 
 def main():

@@ -163,6 +163,25 @@ int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
                              int32_t* status, void* stream);
 
 /*
+ * The up projection with its SwiGLU fused into the GEMM epilogue: one kernel writes
+ *   h13   bf16 [rows_total, 2F] (pitch ldh): gate columns then up columns, the residual the
+ *         backward pass reads, and
+ *   act_q E4M3 [rows_total, F] (byte pitch ldq) = silu(gate) * up (from the bf16 values of h13,
+ *         fp32 math, GLM clamp when `limited`), with one fp32 scale per row and 128 columns at
+ *         act_scale[row*acts_row_stride + block*acts_block_stride].
+ * b is w13 [weights, 2F, K] (gate rows then up rows) with its 128x128 scales; the other
+ * arguments are those of b200moe_grouped_gemm_fp8.  F % 128 == 0.
+ * Reference: src/mlops/kernels/quack_moe/block_fp8_gemm.py:1484 (`block_fp8_gemm_swiglu`),
+ * epilogue :1195-1206; dispatch src/mlops/providers/sonicmoe/block_fp8.py:114-125.
+ */
+int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, const float* a_scale,
+                                    long long as_row_stride, long long as_kb_stride, const void* b,
+                                    const float* b_scale, void* h13, long long ldh, void* act_q, long long ldq,
+                                    float* act_scale, long long acts_row_stride, long long acts_block_stride,
+                                    const int32_t* offsets, int groups, int weights, long long rows_total,
+                                    int F, int K, float limit, int limited, int32_t* status, void* stream);
+
+/*
  * Process-wide cap on the CTAs the persistent tensor-core kernels launch (they launch one CTA
  * per SM and leave no room for another kernel on an SM they occupy).  A caller that overlaps
  * them with communication kernels keeps a few SMs free: ctas = SM count - reserved; 0 restores

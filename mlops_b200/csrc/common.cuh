@@ -367,4 +367,37 @@ __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
+constexpr float kInv448 = 1.0f / 448.0f;
+
+// E4M3 bytes of clamp(v / scale, +-448) with the division rounded to nearest, i.e. exactly
+// what `x / scale` followed by the cast gives on a CPU.  Fast path: multiply by the rounded
+// reciprocal; the true quotient lies within 2^-22 (relative) of that product, and the cast is
+// monotonic, so when both ends of the interval [q(1-2^-21), q(1+2^-21)] cast to the same
+// byte that byte is the exact answer.  Otherwise (a value within an ulp of an E4M3 rounding
+// boundary, about one lane in ten thousand) the eight values take the exact division.
+__device__ __forceinline__ uint2 quantize8(const float (&v)[8], float scale) {
+  const float inv = __frcp_rn(scale);
+  uint32_t w[2] = {0, 0};
+  bool exact = true;
+#pragma unroll
+  for (int i = 0; i < 8; i += 2) {
+    const float q0 = v[i] * inv, q1 = v[i + 1] * inv;
+    const float e0 = q0 * 4.76837158203125e-7f, e1 = q1 * 4.76837158203125e-7f;  // 2^-21
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q0 + e0, q1 + e1), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0 - e0, q1 - e1), __NV_SATFINITE, __NV_E4M3);
+    exact = exact && (hi == lo);
+    w[i >> 2] |= (hi & 0xffffu) << (8 * (i & 3));
+  }
+  if (!exact) {
+    w[0] = w[1] = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float q = __fdiv_rn(v[i], scale);
+      q = fminf(fmaxf(q, -448.0f), 448.0f);
+      w[i >> 2] |= (uint32_t)to_e4m3(q) << (8 * (i & 3));
+    }
+  }
+  return make_uint2(w[0], w[1]);
+}
+
 }  // namespace b200

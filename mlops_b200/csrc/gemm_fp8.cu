@@ -42,6 +42,13 @@ struct GemmFp8Params {
   const int* offsets;
   int groups, N, K, rows_total;
   int weights;  // group g multiplies weight matrix g % weights
+  // fused SwiGLU epilogue (EPI == 1): N = 2F, tiles pair 128 gate with 128 up columns
+  uint8_t* act_q;
+  long long ldq;
+  float* act_scale;
+  long long acts_row_stride, acts_kb_stride;
+  float limit;
+  int limited;
   int* status;
 };
 
@@ -55,7 +62,7 @@ struct GemmCfg {
   static constexpr int kBarBytes = 256;
   static constexpr int kSchedBytes = (2 * (kMaxGroups + 1) * 4 + 15) / 16 * 16;
   static constexpr int kStoreBytes = 8 * 32 * 80;  // per-warp transpose buffers of the epilogue
-  static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + kStoreBytes;
+  static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + kStoreBytes + 1024;
 };
 
 struct TileCoord {
@@ -79,7 +86,7 @@ __device__ __forceinline__ TileCoord locate_m_tile(int mt, const int* m_tile_sta
   return c;
 }
 
-template <int BLOCK_N, bool B_MN_MAJOR>
+template <int BLOCK_N, bool B_MN_MAJOR, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const __grid_constant__ CUtensorMap tmap_b, const GemmFp8Params p) {
@@ -96,7 +103,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* tfull = bars + 2 * kStages;     // [2]
   uint64_t* tempty = bars + 2 * kStages + 2;  // [2]
   uint64_t* drain = bars + 2 * kStages + 4;   // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
+  uint64_t* amax_bar = bars + 2 * kStages + 5;  // [4] row-quarter pairs of the fused SwiGLU epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 9);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* total_m_tiles_s = abort_flag + 1;
   int* m_tile_start = reinterpret_cast<int*>(smem + Cfg::kTileBytes + Cfg::kBarBytes);  // [groups+1]
@@ -106,7 +114,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   const int groups = p.groups;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
-  const int num_n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+  // EPI == 1: a tile is 128 gate columns and the 128 up columns that go with them
+  const int half_n = p.N / 2;
+  const int num_n_tiles = EPI == 1 ? half_n / 128 : (p.N + BLOCK_N - 1) / BLOCK_N;
+  constexpr int kTileStep = EPI == 1 ? 128 : BLOCK_N;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -118,6 +129,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_init(&tempty[0], 8);
     mbar_init(&tempty[1], 8);
     mbar_init(drain, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&amax_bar[i], 64);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -183,7 +195,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int mt = t / num_n_tiles;
-        const int n0 = (t - mt * num_n_tiles) * BLOCK_N;
+        const int n0 = (t - mt * num_n_tiles) * kTileStep;
         const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
@@ -191,7 +203,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[s], Cfg::kABytes + Cfg::kBBytes);
           tma_load_2d(sA + s * Cfg::kABytes, &tmap_a, &full[s], kb * kBlockK, c.m0);
-          if (!B_MN_MAJOR) {
+          if (EPI == 1) {
+            tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], kb * kBlockK, n0, c.group % p.weights);
+            tma_load_3d(sB + s * Cfg::kBBytes + 128 * kBlockK, &tmap_b, &full[s], kb * kBlockK, half_n + n0,
+                        c.group % p.weights);
+          } else if (!B_MN_MAJOR) {
             tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], kb * kBlockK, n0, c.group % p.weights);
           } else {
 #pragma unroll
@@ -267,43 +283,52 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int row_in_tile = q * 32 + lane;
     float acc[kCols];
     uint32_t ab = 0;
+    uint32_t amax_phase = 0;
     bool ok = true;
+    float* amax_s = reinterpret_cast<float*>(stage_base + Cfg::kStoreBytes);  // [2][128]
 
     // Everything the epilogue needs to know about one tile.
     struct EpiTile {
-      int rows_valid, grow, col0;
+      int rows_valid, grow, col0, col1;  // col1: first up column of this thread (EPI == 1)
       const float* as_ptr;
       const float* bs_ptr;
+      const float* bs_ptr_up;
     };
     auto describe = [&](int t) {
       EpiTile e;
       const int mt = t / num_n_tiles;
-      const int n0 = (t - mt * num_n_tiles) * BLOCK_N;
+      const int n0 = (t - mt * num_n_tiles) * kTileStep;
       const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
       e.rows_valid = c.rows_valid;
       e.grow = c.m0 + row_in_tile;
-      e.col0 = n0 + half * kCols;
+      e.col0 = EPI == 1 ? n0 + half * 64 : n0 + half * kCols;
+      e.col1 = half_n + e.col0;
       e.as_ptr = p.a_scale + (long long)min(e.grow, p.rows_total - 1) * p.as_row_stride;
       e.bs_ptr = p.b_scale + (long long)(c.group % p.weights) * p.bs_group_stride +
                  (long long)min(e.col0 / 128, (p.N - 1) / 128) * p.bs_n_stride;
+      e.bs_ptr_up = p.b_scale + (long long)(c.group % p.weights) * p.bs_group_stride +
+                    (long long)min(e.col1 / 128, (p.N - 1) / 128) * p.bs_n_stride;
       return e;
     };
     // The two scales of a K block come from global memory.  They are fetched one batch of
     // kScaleBatch K blocks ahead -- across the tile boundary too -- so their latency never
     // sits between two K blocks.
     float sa_cur[kScaleBatch], sb_cur[kScaleBatch], sa_nxt[kScaleBatch], sb_nxt[kScaleBatch];
-    auto fetch = [&](const EpiTile& e, int kb0, float (&sa)[kScaleBatch], float (&sb)[kScaleBatch]) {
+    float su_cur[EPI == 1 ? kScaleBatch : 1], su_nxt[EPI == 1 ? kScaleBatch : 1];  // up-column block scales
+    auto fetch = [&](const EpiTile& e, int kb0, float (&sa)[kScaleBatch], float (&sb)[kScaleBatch],
+                     float (&su)[EPI == 1 ? kScaleBatch : 1]) {
 #pragma unroll
       for (int u = 0; u < kScaleBatch; ++u) {
         const int kk = min(kb0 + u, num_kb - 1);
         sa[u] = e.as_ptr[(long long)kk * p.as_kb_stride];
         sb[u] = e.bs_ptr[(long long)kk * p.bs_k_stride];
+        if constexpr (EPI == 1) su[u] = e.bs_ptr_up[(long long)kk * p.bs_k_stride];
       }
     };
     EpiTile cur_tile, nxt_tile;
     if ((int)blockIdx.x < total_tiles) {
       cur_tile = describe(blockIdx.x);
-      fetch(cur_tile, 0, sa_cur, sb_cur);
+      fetch(cur_tile, 0, sa_cur, sb_cur, su_cur);
     }
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const bool has_next = t + (int)gridDim.x < total_tiles;
@@ -314,25 +339,30 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
       for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kScaleBatch) {
-        if (kb0 + kScaleBatch < num_kb) fetch(c, kb0 + kScaleBatch, sa_nxt, sb_nxt);
-        else if (has_next) fetch(nxt_tile, 0, sa_nxt, sb_nxt);
+        if (kb0 + kScaleBatch < num_kb) fetch(c, kb0 + kScaleBatch, sa_nxt, sb_nxt, su_nxt);
+        else if (has_next) fetch(nxt_tile, 0, sa_nxt, sb_nxt, su_nxt);
 #pragma unroll
         for (int u = 0; u < kScaleBatch; ++u) {
           if (kb0 + u >= num_kb) break;
           const float s = sa_cur[u] * sb_cur[u];
+          const float s_up = EPI == 1 ? sa_cur[u] * su_cur[u] : s;
           const int buf = ab & 1;
           const uint32_t aph = (ab >> 1) & 1;
           ++ab;
           if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N + half * kCols;
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N +
+                                 (EPI == 1 ? half * 64 : half * kCols);
 #pragma unroll
           for (int cc = 0; cc < kChunks; ++cc) {
             uint32_t r[32];
-            tmem_ld_32x32(taddr + cc * 32, r);
+            // EPI == 1: chunks 0,1 are this thread's 64 gate columns, chunks 2,3 its 64 up columns
+            const int tcol = EPI == 1 ? (cc & 1) * 32 + (cc >> 1) * 128 : cc * 32;
+            const float sc = (EPI == 1 && cc >= 2) ? s_up : s;
+            tmem_ld_32x32(taddr + tcol, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(s, __uint_as_float(r[j]), acc[cc * 32 + j]);
+            for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(sc, __uint_as_float(r[j]), acc[cc * 32 + j]);
           }
           tc_fence_before_sync();
           __syncwarp();
@@ -342,6 +372,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int u = 0; u < kScaleBatch; ++u) {
           sa_cur[u] = sa_nxt[u];
           sb_cur[u] = sb_nxt[u];
+          if constexpr (EPI == 1) su_cur[u] = su_nxt[u];
         }
       }
       cur_tile = nxt_tile;
@@ -384,7 +415,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           __syncwarp();
           const int piece = lane & 3;          // 16-byte piece of the 64-byte row slab
-          const int col = col0 + cc * 32 + piece * 8;
+          const int chunk_col = EPI == 1 ? ((cc >> 1) ? c.col1 : c.col0) + (cc & 1) * 32 : col0 + cc * 32;
+          const int col = chunk_col + piece * 8;
 #pragma unroll
           for (int pass = 0; pass < 4; ++pass) {
             const int r = pass * 8 + (lane >> 2);
@@ -392,6 +424,47 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const uint4 v = *reinterpret_cast<const uint4*>(stage + r * kStageRowBytes + piece * 16);
               *reinterpret_cast<uint4*>(p.d + (long long)(warp_row0 + r) * p.ldd + col) = v;
             }
+          }
+        }
+        if constexpr (EPI == 1) {
+          // act = silu(gate) * up from the bf16 values just stored (what a separate pass over
+          // h13 would read), one E4M3 scale per row and 128 columns: the other half of the
+          // block lives in the partner warp (same rows, other 64 columns), so the two exchange
+          // their maxima through shared memory with a bounded mbarrier wait.
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            float gi = __bfloat162float(__float2bfloat16_rn(acc[j]));
+            float ui = __bfloat162float(__float2bfloat16_rn(acc[64 + j]));
+            if (p.limited) {
+              gi = fminf(gi, p.limit);
+              ui = fminf(fmaxf(ui, -p.limit), p.limit);
+            }
+            const float sig = __frcp_rn(1.0f + expf(-gi));
+            acc[j] = gi * sig * ui;
+            amax = fmaxf(amax, fabsf(acc[j]));
+          }
+          amax_s[half * 128 + row_in_tile] = amax;
+          mbar_arrive(&amax_bar[q]);
+          if (!mbar_wait(&amax_bar[q], amax_phase, abort_flag, p.status, 5)) { ok = false; break; }
+          amax_phase ^= 1;
+          amax = fmaxf(amax, amax_s[(half ^ 1) * 128 + row_in_tile]);
+          const float scale = fmaxf(amax * kInv448, 1e-12f);
+          if (lane < rows_here) {
+            uint8_t* arow = p.act_q + (long long)grow * p.ldq + c.col0;
+#pragma unroll
+            for (int j = 0; j < 64; j += 16) {
+              float v0[8], v1[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                v0[i] = acc[j + i];
+                v1[i] = acc[j + 8 + i];
+              }
+              const uint2 lo8 = quantize8(v0, scale), hi8 = quantize8(v1, scale);
+              *reinterpret_cast<uint4*>(arow + j) = make_uint4(lo8.x, lo8.y, hi8.x, hi8.y);
+            }
+            if (half == 0)
+              p.act_scale[(long long)grow * p.acts_row_stride + (long long)(c.col0 >> 7) * p.acts_kb_stride] = scale;
           }
         }
       }
@@ -412,16 +485,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <int BLOCK_N, bool B_MN>
+template <int BLOCK_N, bool B_MN, int EPI = 0>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp8Params& p,
                        cudaStream_t stream) {
   using Cfg = GemmCfg<BLOCK_N>;
-  auto kern = grouped_gemm_fp8_kernel<BLOCK_N, B_MN>;
+  auto kern = grouped_gemm_fp8_kernel<BLOCK_N, B_MN, EPI>;
   // Function attributes are per device; setting one is a cheap host-side call.
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
     return B200MOE_ERR_LAUNCH;
   const long long m_tiles_bound = (p.rows_total + kBlockM - 1) / kBlockM + p.groups;
-  const long long n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const long long n_tiles = EPI == 1 ? p.N / 256 : (p.N + BLOCK_N - 1) / BLOCK_N;
   long long grid = m_tiles_bound * n_tiles;
   const int sms = sm_count();
   if (grid > sms) grid = sms;
@@ -477,6 +550,12 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
   p.K = K;
   p.rows_total = (int)rows_total;
   p.weights = weights;
+  p.act_q = nullptr;
+  p.ldq = 0;
+  p.act_scale = nullptr;
+  p.acts_row_stride = p.acts_kb_stride = 0;
+  p.limit = 0.f;
+  p.limited = 0;
   p.status = status;
   if (!b_mn_major) {
     // B is [groups, N, K], K contiguous; scales [groups, ceil(N/128), ceil(K/128)].
@@ -507,6 +586,74 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
     return b_mn_major ? launch_gemm<128, true>(ta, tb, p, s) : launch_gemm<128, false>(ta, tb, p, s);
   }
   return b_mn_major ? launch_gemm<256, true>(ta, tb, p, s) : launch_gemm<256, false>(ta, tb, p, s);
+}
+
+// Up projection with the SwiGLU epilogue fused: h13 (bf16, gate columns then up columns, the
+// residual the backward pass needs) and act = silu(gate) * up as E4M3 with 1x128 scales, in
+// one kernel.  b is w13 [weights, 2F, K] (gate rows then up rows).
+extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, const float* a_scale,
+                                               long long as_row_stride, long long as_kb_stride, const void* b,
+                                               const float* b_scale, void* h13, long long ldh, void* act_q,
+                                               long long ldq, float* act_scale, long long acts_row_stride,
+                                               long long acts_block_stride, const int32_t* offsets, int groups,
+                                               int weights, long long rows_total, int F, int K, float limit,
+                                               int limited, int32_t* status, void* stream) {
+  if (!a || !a_scale || !b || !b_scale || !h13 || !act_q || !act_scale || !offsets || !status)
+    return B200MOE_ERR_ARG;
+  if (groups <= 0 || F <= 0 || K <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
+  if (weights <= 0 || groups % weights != 0) return B200MOE_ERR_ARG;
+  if (groups > kMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  if ((F % 128) || (K % 16) || (lda % 16) || (ldh % 8) || (ldq % 16)) return B200MOE_ERR_ALIGN;
+  if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)h13 & 15) || ((uintptr_t)act_q & 15))
+    return B200MOE_ERR_ALIGN;
+  if (rows_total == 0) return B200MOE_OK;
+  const int N = 2 * F;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_total};
+    uint64_t strides[1] = {(uint64_t)lda};
+    uint32_t box[2] = {128, 128};
+    int r = encode_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)weights};
+    uint64_t strides[2] = {(uint64_t)K, (uint64_t)K * (uint64_t)N};
+    uint32_t box[3] = {128, 128, 1};  // 128 gate rows and 128 up rows are two loads per stage
+    int r = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+  }
+  const int kblocks = (K + 127) / 128;
+  const int nblocks = N / 128;
+  GemmFp8Params p;
+  p.a_scale = a_scale;
+  p.as_row_stride = as_row_stride;
+  p.as_kb_stride = as_kb_stride;
+  p.b_scale = b_scale;
+  p.bs_group_stride = (long long)nblocks * kblocks;
+  p.bs_n_stride = kblocks;
+  p.bs_k_stride = 1;
+  p.d = reinterpret_cast<__nv_bfloat16*>(h13);
+  p.ldd = ldh;
+  p.addend = nullptr;
+  p.ldc = 0;
+  p.offsets = offsets;
+  p.groups = groups;
+  p.N = N;
+  p.K = K;
+  p.rows_total = (int)rows_total;
+  p.weights = weights;
+  p.act_q = reinterpret_cast<uint8_t*>(act_q);
+  p.ldq = ldq;
+  p.act_scale = act_scale;
+  p.acts_row_stride = acts_row_stride;
+  p.acts_kb_stride = acts_block_stride;
+  p.limit = limit;
+  p.limited = limited;
+  p.status = status;
+  return launch_gemm<256, false, 1>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_set_cta_limit(int ctas) {

@@ -338,6 +338,40 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
     return out
 
 
+def grouped_gemm_fp8_swiglu(a_q, a_scale, w13_q, w13_scale, offsets, *, limit=None, out=None):
+    """Up projection with the SwiGLU epilogue fused. Returns `(h13 bf16 [rows, 2F], act_q E4M3
+    [rows, F], act_scale [rows, F/128])`: the same three tensors as `grouped_gemm_fp8` followed
+    by `swiglu_quantize`, from one kernel."""
+    device = _need_cuda(a_q, a_scale, w13_q, w13_scale, offsets)
+    rows, k = a_q.shape
+    weights, two_f, kb = w13_q.shape
+    if kb != k or two_f % 256:
+        raise NativeError("w13 must be [E, 2F, K] with F a multiple of 128")
+    width = two_f // 2
+    groups = offsets.numel() - 1
+    if a_scale.dim() == 1:
+        a_scale = a_scale.unsqueeze(1)
+    as_kb = 0 if a_scale.shape[1] == 1 else a_scale.stride(1)
+    h13 = torch.empty((rows, two_f), dtype=torch.bfloat16, device=device) if out is None else out
+    act_q = torch.empty((rows, width), dtype=FP8, device=device)
+    scales = _scale_buffer(rows, width // 128, device)
+    if rows == 0:
+        return h13, act_q, scales
+    with _Timed("fp8", 2.0 * rows * two_f * k):
+        check(
+            lib.b200moe_grouped_gemm_fp8_swiglu(
+                a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb, w13_q.data_ptr(),
+                w13_scale.data_ptr(), h13.data_ptr(), h13.stride(0), act_q.data_ptr(), act_q.stride(0),
+                scales.data_ptr(), scales.stride(0), scales.stride(1), offsets.data_ptr(), groups, weights, rows,
+                width, k, 0.0 if limit is None else float(limit), 0 if limit is None else 1,
+                status_block(device).data_ptr(), _stream(),
+            ),
+            "grouped_gemm_fp8_swiglu",
+        )
+    _count()
+    return h13, act_q, scales
+
+
 def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
     """`[G, M, N]` with `out[e] = g[rows_e].T @ x[rows_e]` (bf16 operands, fp32 sums).
     `offsets` has `segments * groups + 1` entries; expert e sums over the ranges

@@ -242,3 +242,23 @@ def test_segmented_layout_matches_expert_sorted_layout():
             expected += grad[lo:hi].double().t() @ x[lo:hi].double()
         mx, mean = O.rel_errors(dw[e].cpu(), expected)
         assert mx <= 1e-5, mx
+
+
+@pytest.mark.parametrize("limit", [None, 0.75])
+@pytest.mark.parametrize("counts,inner,k", [([0, 70, 131, 15, 260], 256, 384), ([300, 212], 128, 7168), ([40], 384, 128)])
+def test_fused_swiglu_epilogue_equals_the_two_kernel_form(counts, inner, k, limit):
+    """Up GEMM with the SwiGLU + quantisation epilogue: h13, E4M3 activation bytes and scales
+    must equal `grouped_gemm_fp8` followed by `swiglu_quantize` bit for bit."""
+    ops = _ops()
+    a_q, a_s, b_q, b_s, offs = _case(counts, 2 * inner, k, seed=inner + k, mn_major=False)
+    dev = [t.to(DEV) for t in (a_q, a_s.t().contiguous().t(), b_q, b_s, offs)]
+    dev[1] = a_s.t().contiguous().to(DEV).t()
+    h13 = ops.grouped_gemm_fp8(dev[0], dev[1], dev[2], dev[3], dev[4])
+    act_q, act_s, _ = ops.swiglu_quantize(h13, limit=limit)
+    rows = sum(counts)
+    fused = torch.full((rows, 2 * inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    h13_f, act_q_f, act_s_f = ops.grouped_gemm_fp8_swiglu(dev[0], dev[1], dev[2], dev[3], dev[4], limit=limit, out=fused)
+    ops.check_status(DEV)
+    assert torch.equal(h13_f, h13)
+    assert torch.equal(act_s_f, act_s)
+    assert torch.equal(act_q_f.view(torch.uint8), act_q.view(torch.uint8))

@@ -151,3 +151,16 @@ def test_frozen_gradients_skip_their_gemms_and_leave_the_rest_bit_identical():
     for a, b in zip(full, again):
         assert torch.equal(a, b)  # bitwise repeatable
     ops.check_status(DEV)
+
+
+def test_fused_swiglu_layer_is_bit_identical():
+    layer, ops = _layer()
+    c1 = inputs.config1()
+    w13 = tuple(t.to(DEV) for t in O.quantize_blocks(c1["w13"]))
+    w2 = tuple(t.to(DEV) for t in O.quantize_blocks(c1["w2"]))
+    x, router = c1["x"].to(DEV), c1["router"].to(DEV)
+    plain = layer.forward_routed(x, torch.zeros_like(x), router, w13, w2, top_k=2, routing_mode="softmax_then_topk")
+    fused = layer.forward_routed(x, torch.zeros_like(x), router, w13, w2, top_k=2, routing_mode="softmax_then_topk",
+                                 fuse_swiglu=True)
+    assert torch.equal(plain[0], fused[0]) and torch.equal(plain[10], fused[10])
+    ops.check_status(DEV)
