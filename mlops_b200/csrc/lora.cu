@@ -74,30 +74,36 @@ lora_project_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __
         }
       }
       __syncthreads();
+      // All rows of the warp load their 16 bytes first (independent loads in flight), then each
+      // factor slice read from shared memory is used for every row.
+      for (int k = lane * 8; k < kc; k += 256) {
+        uint4 raw[kRowsPerWarp];
 #pragma unroll
-      for (int i = 0; i < kRowsPerWarp; ++i) {
-        const int row = row0 + warp * kRowsPerWarp + i;
-        if (row < lo || row >= hi) continue;  // warp-uniform
-        for (int k = lane * 8; k < kc; k += 256) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(x + (long long)row * ldx + k0 + k);
-          const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(&raw);
-          float xf[8];
+        for (int i = 0; i < kRowsPerWarp; ++i) {
+          const int row = row0 + warp * kRowsPerWarp + i;
+          raw[i] = (row >= lo && row < hi) ? *reinterpret_cast<const uint4*>(x + (long long)row * ldx + k0 + k)
+                                           : make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float2 f = __bfloat1622float2(xv[u]);
-            xf[2 * u] = f.x;
-            xf[2 * u + 1] = f.y;
-          }
+        for (int j = 0; j < RMAX; ++j) {
+          if (j < r) {
+            const uint4 wraw = *reinterpret_cast<const uint4*>(sw + j * kPitch + k);
+            const __nv_bfloat162* wv = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+            float wf[8];
 #pragma unroll
-          for (int j = 0; j < RMAX; ++j) {
-            if (j < r) {
-              const uint4 wraw = *reinterpret_cast<const uint4*>(sw + j * kPitch + k);
-              const __nv_bfloat162* wv = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+            for (int u = 0; u < 4; ++u) {
+              const float2 f = __bfloat1622float2(wv[u]);
+              wf[2 * u] = f.x;
+              wf[2 * u + 1] = f.y;
+            }
+#pragma unroll
+            for (int i = 0; i < kRowsPerWarp; ++i) {
+              const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
 #pragma unroll
               for (int u = 0; u < 4; ++u) {
-                const float2 f = __bfloat1622float2(wv[u]);
-                acc[i][j] = fmaf(xf[2 * u], f.x, acc[i][j]);
-                acc[i][j] = fmaf(xf[2 * u + 1], f.y, acc[i][j]);
+                const float2 f = __bfloat1622float2(xv[u]);
+                acc[i][j] = fmaf(f.x, wf[2 * u], acc[i][j]);
+                acc[i][j] = fmaf(f.y, wf[2 * u + 1], acc[i][j]);
               }
             }
           }

@@ -47,6 +47,10 @@ class _ExpertLoRA(torch.autograd.Function):
         b13p, _ = _pad_rank(b13.detach(), 2)
         a2p, _ = _pad_rank(a2.detach(), 1)
         b2p, _ = _pad_rank(b2.detach(), 2)
+        # the B factors are also kept rank-major ([E, r, wide]): every rank-r kernel then stages
+        # its factor with 16-byte loads (a few MB, transposed once per call)
+        b13t = b13p.transpose(1, 2).contiguous()
+        b2t = b2p.transpose(1, 2).contiguous()
         logits = layer.router_logits(flat, router_weight)
         weights, ids = ops.route_topk(
             logits, top_k, options["routing_mode"], bias=router_bias, n_group=options["n_group"],
@@ -56,16 +60,16 @@ class _ExpertLoRA(torch.autograd.Function):
         x_rows = ops.dispatch(flat, order, top_k)
         x_q, x_s = ops.quantize_rows(x_rows)
         t1 = ops.lora_project(x_rows, a13p, offsets, rank_major=True)
-        c1 = ops.lora_expand(t1, b13p, offsets, wide_major=True, scale=scale)
+        c1 = ops.lora_expand(t1, b13t, offsets, wide_major=False, scale=scale)
         h13 = ops.grouped_gemm_fp8(x_q, x_s, *w13, offsets, addend=c1)
         a_q, a_s, act = ops.swiglu_quantize(h13, limit=limit, quantized=True, rounded=True)
         t2 = ops.lora_project(act, a2p, offsets, rank_major=True)
-        c2 = ops.lora_expand(t2, b2p, offsets, wide_major=True, scale=scale)
+        c2 = ops.lora_expand(t2, b2t, offsets, wide_major=False, scale=scale)
         y = ops.grouped_gemm_fp8(a_q, a_s, *w2, offsets, addend=c2)
         output = ops.combine(y, slots, weights, residual_flat).reshape(hidden.shape)
         aux, counts, probability_sum = layer.routing_statistics(
             logits, ids, counts, routing_mode=options["routing_mode"], lengths=options["lengths"], experts=experts)
-        ctx.save_for_backward(flat, router_weight, *w13, *w2, a13p, b13p, a2p, b2p, logits, weights, ids, order,
+        ctx.save_for_backward(flat, router_weight, *w13, *w2, a13p, b13t, a2p, b2t, logits, weights, ids, order,
                               offsets, slots, h13, t1, t2)
         ctx.options, ctx.rank, ctx.shape = options, rank, hidden.shape
         ctx.logical = (gate_up.dtype, down.dtype)
@@ -88,7 +92,7 @@ class _ExpertLoRA(torch.autograd.Function):
 
         dy_rows = ops.dispatch(dy, order, top_k)
         dy_q, dy_s = ops.quantize_rows(dy_rows)
-        t2g = ops.lora_project(dy_rows, b2, offsets, rank_major=False)          # dy B2      [R, r]
+        t2g = ops.lora_project(dy_rows, b2, offsets, rank_major=True)           # dy B2      [R, r]
         r_add = ops.lora_expand(t2g, a2, offsets, wide_major=False, scale=scale)  # s dy B2 A2 [R, F]
         r = ops.grouped_gemm_fp8(dy_q, dy_s, w2_d, w2_s, offsets, b_mn_major=True, addend=r_add)
         dscore, gh_q, gh_s, gh_b, act_scaled = ops.dswiglu_routed(
@@ -96,7 +100,7 @@ class _ExpertLoRA(torch.autograd.Function):
         grad_route_weights = ops.gather_scalar(dscore, slots)
 
         x_rows = ops.dispatch(flat, order, top_k)
-        dt1 = ops.lora_project(gh_b, b13, offsets, rank_major=False)            # gh B13     [R, r]
+        dt1 = ops.lora_project(gh_b, b13, offsets, rank_major=True)             # gh B13     [R, r]
         grad_a13 = grad_b13 = grad_a2 = grad_b2 = None
         if need_factors:
             row_weight = weights.reshape(-1)[order.long()].float()[:, None]
