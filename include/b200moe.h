@@ -88,14 +88,16 @@ int b200moe_sort_assignments_static(const int32_t* ids, long long assignments, i
  * gather[r] / gather_div (gather may be NULL: row r).  q is [rows, width] bytes with
  * byte pitch ldq; scale of (row r, block b) is written to
  * scales[r * scale_row_stride + b * scale_block_stride] (block b = columns 128b..128b+127;
- * mode B200MOE_SCALE_ROW writes only b = 0).  width % 8 == 0.
+ * mode B200MOE_SCALE_ROW writes only b = 0).  width % 8 == 0.  `copy` (optional, 1x128 mode)
+ * also receives the gathered rows unquantised (bf16 [rows, width], pitch ldc): the operand of
+ * a weight gradient, from the same pass over the source.
  * Reference: src/mlops/kernels/quack_moe/quantize_rows.py:140-207 (`quantize_rows_fp8`,
  * per-row); the 1x128 mode applies the same equations per block.
  */
 int b200moe_quantize_rows(const void* x, long long ldx, const int32_t* gather, int gather_div,
                           long long rows, int width, void* q, long long ldq, float* scales,
-                          long long scale_row_stride, long long scale_block_stride, int mode,
-                          void* stream);
+                          long long scale_row_stride, long long scale_block_stride, int mode, void* copy,
+                          long long ldc, void* stream);
 
 /*
  * SwiGLU of h13 = [gate | up] (bf16 [rows, 2*width]) computed in fp32 and rounded once

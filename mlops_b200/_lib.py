@@ -32,7 +32,7 @@ SIGNATURES = {
     "b200moe_sort_assignments_workspace_bytes": (LL, [LL, I]),
     "b200moe_sort_assignments": (I, [P, LL, I, P, P, P, P, P, P, P]),
     "b200moe_sort_assignments_static": (I, [P, LL, I, P, P, P, P, P, P]),
-    "b200moe_quantize_rows": (I, [P, LL, P, I, LL, I, P, LL, P, LL, LL, I, P]),
+    "b200moe_quantize_rows": (I, [P, LL, P, I, LL, I, P, LL, P, LL, LL, I, P, LL, P]),
     "b200moe_swiglu_quantize": (I, [P, LL, LL, I, P, LL, P, LL, LL, P, LL, F, I, P]),
     "b200moe_dswiglu_routed": (
         I,

@@ -469,10 +469,9 @@ grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __gr
             fence_proxy_async_smem();
           }
           __syncwarp();
-          if (lane == 0) {
-            if (valid < kWgBlockK) mbar_arrive_cluster(&ready[s], 0);  // publishes the zeroed rows
-            else mbar_arrive_remote(&ready[s], 0);
-          }
+          // The zeroed rows were made visible to the async proxy by the fence above; the
+          // arrival itself needs no cluster-scope release (which costs about a microsecond).
+          if (lane == 0) mbar_arrive_remote(&ready[s], 0);
         }
       }
     }

@@ -48,7 +48,8 @@ __device__ __forceinline__ uint4 pack8_bf16(const float (&v)[8]) {
 __global__ void __launch_bounds__(kRowWarps * 32)
 quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ gather,
                      int gather_div, long long rows, int D, uint8_t* __restrict__ q, long long ldq,
-                     float* __restrict__ scales, long long s_row, long long s_kb, int mode) {
+                     float* __restrict__ scales, long long s_row, long long s_kb, int mode,
+                     __nv_bfloat16* __restrict__ copy, long long ldc) {
   const int lane = threadIdx.x & 31;
   const long long r = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (r >= rows) return;
@@ -75,6 +76,7 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const i
         if (c < D) {
           *reinterpret_cast<uint2*>(qr + c) = quantize8(v, scale);
           if ((lane & 15) == 0) scales[r * s_row + (long long)(c >> 7) * s_kb] = scale;
+          if (copy != nullptr) *reinterpret_cast<uint4*>(copy + r * ldc + c) = h == 0 ? raw_a : raw_b;
         }
       }
     }
@@ -282,15 +284,17 @@ static inline unsigned row_grid(long long rows) { return (unsigned)((rows + kRow
 extern "C" int b200moe_quantize_rows(const void* x, long long ldx, const int32_t* gather, int gather_div,
                                      long long rows, int width, void* q, long long ldq, float* scales,
                                      long long scale_row_stride, long long scale_block_stride, int mode,
-                                     void* stream) {
+                                     void* copy, long long ldc, void* stream) {
   if (!x || !q || !scales || rows < 0 || width <= 0 || (mode != 0 && mode != 1)) return B200MOE_ERR_ARG;
+  if (copy != nullptr && (mode != 0 || (ldc % 8) || ((uintptr_t)copy & 15))) return B200MOE_ERR_ARG;
   if (gather != nullptr && gather_div <= 0) return B200MOE_ERR_ARG;
   if ((width % 8) || (ldx % 8) || (ldq % 8) || ((uintptr_t)x & 15) || ((uintptr_t)q & 7))
     return B200MOE_ERR_ALIGN;
   if (rows == 0) return B200MOE_OK;
   quantize_rows_kernel<<<row_grid(rows), kRowWarps * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ldx, gather, gather_div > 0 ? gather_div : 1, rows, width,
-      reinterpret_cast<uint8_t*>(q), ldq, scales, scale_row_stride, scale_block_stride, mode);
+      reinterpret_cast<uint8_t*>(q), ldq, scales, scale_row_stride, scale_block_stride, mode,
+      reinterpret_cast<__nv_bfloat16*>(copy), ldc);
   return launch_status();
 }
 

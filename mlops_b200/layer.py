@@ -249,7 +249,12 @@ def backward_routed(
         normalized = _normalized_lengths(lengths, h2_flat.shape[0])
         counts = (offsets[1:] - offsets[:-1]).long()
 
-        dy_q, dy_s = ops.quantize_rows(grad_flat, gather=order, gather_div=int(top_k))
+        # one pass over dy: E4M3 rows for the input gradient and, when the down weight's gradient
+        # is wanted, the same rows in bf16 as its operand
+        if need_w2:
+            dy_q, dy_s, dy_rows = ops.quantize_rows(grad_flat, gather=order, gather_div=int(top_k), with_copy=True)
+        else:
+            dy_q, dy_s = ops.quantize_rows(grad_flat, gather=order, gather_div=int(top_k))
         r = ops.grouped_gemm_fp8(dy_q, dy_s, w2_data, w2_scale, offsets, b_mn_major=True, block_n=block_n)
         dscore, gh_q, gh_s, gh_b, act_scaled = ops.dswiglu_routed(
             h13, r, route_weights, order, limit=swiglu_limit, quantized=True, rounded=need_w13,
@@ -257,7 +262,6 @@ def backward_routed(
         )
         grad_route_weights = ops.gather_scalar(dscore, slots)
         if need_w2:
-            dy_rows = ops.dispatch(grad_flat, order, int(top_k))
             grad_w2 = ops.grouped_wgrad(dy_rows, act_scaled, offsets, experts, wdtype)
             del dy_rows, act_scaled
         else:

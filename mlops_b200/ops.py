@@ -182,9 +182,10 @@ def _scale_buffer(rows, blocks, device):
     return torch.empty((blocks, max(rows, 1)), dtype=torch.float32, device=device)[:, :rows].t()
 
 
-def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128"):
+def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False):
     """E4M3 rows and fp32 scales of bf16 `x [T, D]`; output row r reads input row
-    `gather[r] // gather_div`. Returns (q [R, D] float8_e4m3fn, scales [R, blocks])."""
+    `gather[r] // gather_div`. Returns (q [R, D] float8_e4m3fn, scales [R, blocks]); with
+    `with_copy` also the gathered bf16 rows themselves, written by the same pass."""
     _need_cuda(x, gather)
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
         raise NativeError("x must be bf16 [rows, width] with unit inner stride")
@@ -193,18 +194,19 @@ def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128"):
     q = torch.empty((rows, width), dtype=FP8, device=x.device)
     blocks = (width + 127) // 128 if mode == "1x128" else 1
     scales = _scale_buffer(rows, blocks, x.device)
+    copy = torch.empty((rows, width), dtype=torch.bfloat16, device=x.device) if with_copy else None
     if rows == 0:
-        return q, scales
+        return (q, scales, copy) if with_copy else (q, scales)
     check(
         lib.b200moe_quantize_rows(
             x.data_ptr(), x.stride(0), _ptr(gather), int(gather_div), rows, width, q.data_ptr(),
             q.stride(0), scales.data_ptr(), scales.stride(0), scales.stride(1),
-            0 if mode == "1x128" else 1, _stream(),
+            0 if mode == "1x128" else 1, _ptr(copy), width, _stream(),
         ),
         "quantize_rows",
     )
     _count()
-    return q, scales
+    return (q, scales, copy) if with_copy else (q, scales)
 
 
 def swiglu_quantize(h13, *, limit=None, quantized=True, rounded=False):

@@ -87,8 +87,9 @@ def test_frozen_inputs_get_none_and_the_rest_is_bit_identical():
     out3, *_ = provider.apply(x, torch.zeros_like(x), router, w13, w2, top_k=2, routing_mode="softmax_then_topk")
     launches = ops.LAUNCHES
     torch.autograd.grad(out3, [x, router, w13, w2], dy)
-    # two weight-gradient GEMMs and their two row gathers are not launched when frozen
-    assert (ops.LAUNCHES - launches) - frozen_backward == 4
+    # frozen: the two weight-gradient GEMMs and the gather of their x operand are not launched
+    # (the dy operand is a by-product of the quantiser's pass, not a launch of its own)
+    assert (ops.LAUNCHES - launches) - frozen_backward == 3
 
 
 def test_activation_checkpoint_is_bit_identical():
