@@ -210,8 +210,9 @@ def gpu_arm(args, cfg):
     if distributed:
         import torch.distributed as dist
 
-        # the all-to-all kernels run beside the GEMMs on the 16 SMs the layer keeps free
-        os.environ.setdefault("NCCL_MAX_CTAS", "16")
+        # the all-to-all kernels run beside the GEMMs on the SMs the layer keeps free (32 by default)
+        comm_sms = int(os.environ.get("B200MOE_EP_COMM_SMS", "32"))
+        os.environ.setdefault("NCCL_MAX_CTAS", str(comm_sms))
         dist.init_process_group("nccl", device_id=device)
     T, D, E, F, K = cfg["T"], cfg["D"], cfg["E"], cfg["F"], cfg["K"]
     experts_local = E // world
@@ -268,7 +269,7 @@ def gpu_arm(args, cfg):
                                            n_group=cfg["n_group"], topk_group=cfg["topk_group"],
                                            routed_scaling=cfg["scaling"], expert_map="strided"),
             dist.group.WORLD, router_weight=router, router_bias=bias, w13=w13, w2=w2, shared=shared,
-            device=device)
+            device=device, chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "2")), comm_sms=comm_sms)
 
     rows_received = []
 

@@ -137,7 +137,7 @@ class ExpertParallelMoE:
     with local expert gradients and UN-reduced replicated gradients."""
 
     def __init__(self, config: ExpertParallelConfig, ep_group, *, router_weight, w13, w2, router_bias=None,
-                 shared=None, device=None, weight_grad_dtype=torch.bfloat16, chunks=2, comm_sms=16):
+                 shared=None, device=None, weight_grad_dtype=torch.bfloat16, chunks=2, comm_sms=32):
         self.config = config
         self.group = ep_group
         self.world = dist.get_world_size(ep_group)
