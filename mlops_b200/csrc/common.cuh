@@ -64,6 +64,14 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrival without release ordering.  The default (release) form makes the hardware wait for
+// the thread's outstanding global loads before the arrival becomes visible -- hundreds of
+// cycles when a prefetch is in flight.  Use it where what the waiter consumes is not ordinary
+// memory written by this thread: a TMEM buffer whose reads were already completed by
+// tcgen05.wait::ld and ordered by tcgen05.fence::before_thread_sync.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
@@ -78,6 +86,32 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
+}
+
+// Non-blocking probe of the phase (try_wait may put the thread to sleep for a while; a role
+// that sits on the critical path of a handshake polls with this instead).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Hardware (named) barriers of the CTA: ids 1..15, id 0 is __syncthreads.  `threads` is the
+// total number of threads that take part in one completion (a multiple of 32); every thread of
+// a participating warp must execute the instruction.  An arrival does not block.  Unlike an
+// mbarrier these do not go through shared memory, whose queue is long while the tensor cores
+// and the TMA unit stream operands through it.
+__device__ __forceinline__ void named_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // ---- CTA pairs (thread-block clusters of two) -----------------------------------------
@@ -133,13 +167,17 @@ __device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity)
 #endif
 
 // Bounded wait.  Returns false when the limit ran out or when another role of
-// this CTA already raised the abort flag; the caller must then unwind.
+// this CTA already raised the abort flag; the caller must then unwind.  try_wait itself
+// suspends the thread for a hardware-defined time, so the abort flag and the clock are
+// looked at only every few rounds: a spinning role must not compete with the tensor cores
+// and the TMA unit for shared-memory bandwidth.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int where) {
   if (mbar_try(bar, parity)) return true;
   const long long start = clock64();
-  while (true) {
+  for (uint32_t round = 1;; ++round) {
     if (mbar_try(bar, parity)) return true;
+    if ((round & 7u) != 0) continue;
     if (*abort_flag) return false;
     if (clock64() - start > B200_WAIT_LIMIT_CYCLES) {
       *abort_flag = 1;
@@ -147,6 +185,33 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       return false;
     }
   }
+}
+
+// Bounded wait that polls without sleeping: for single threads whose wake-up latency is on
+// the critical path (the UMMA issuers, lane 0 of an epilogue warp).
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int where) {
+  if (mbar_test(bar, parity)) return true;
+  const long long start = clock64();
+  for (uint32_t round = 1;; ++round) {
+    if (mbar_test(bar, parity)) return true;
+    if ((round & 63u) != 0) continue;
+    if (*abort_flag) return false;
+    if (clock64() - start > B200_WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      report_error(status, ERR_WAIT_TIMEOUT, where, (int)parity);
+      return false;
+    }
+  }
+}
+
+// The same for a whole warp: lane 0 waits and tells the others, so a warp costs the barrier
+// one poller instead of thirty-two.  The warp must be converged.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int where) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_spin(bar, parity, abort_flag, status, where) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -234,6 +299,10 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_smem_addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_smem_addr)
                : "memory");
 }
 // ---- the same for a CTA pair (cta_group::2): allocation by one warp of EACH CTA, one MMA

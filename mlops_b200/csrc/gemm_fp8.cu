@@ -11,9 +11,13 @@
 //
 // One persistent CTA per SM, 12 warps:
 //   warp 0      TMA producer (A tile 128x128 bytes, B tile BLOCK_N x 128 bytes per stage)
-//   warp 1      UMMA issuer (one elected thread), 4 x (128 x BLOCK_N x 32) per K block
+//   warps 1, 3  UMMA issuers (one thread each), 4 x (128 x BLOCK_N x 32) per K block.  Even K
+//               blocks (accumulator buffer 0) belong to warp 1, odd ones (buffer 1) to warp 3:
+//               the two streams are independent, so while one thread is between K blocks
+//               (commits, two barrier checks: a few hundred cycles) the tensor cores still
+//               have the other thread's instructions queued
 //   warp 2      TMEM allocation / release
-//   warp 3      builds the tile table (group -> first M tile) in shared memory
+//   warp 3      first builds the tile table (group -> first M tile) in shared memory
 //   warps 4-11  epilogue: tcgen05.ld of a K block's partial, scale, accumulate; at the
 //               end of the K loop convert to bf16 and store the rows that belong to the
 //               group (rows past the group's end were multiplied but are not written).
@@ -29,6 +33,8 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 128;  // bytes == elements for E4M3
 constexpr int kGemmThreads = 384;
 constexpr int kScaleBatch = 4;  // K blocks of scales fetched ahead by the epilogue
+constexpr uint32_t kAccBarrier = 1;  // hardware barriers 1, 2: accumulator buffer 0, 1 drained
+constexpr uint32_t kAccBarrierThreads = (8 + 1) * 32;  // eight epilogue warps and the buffer's issuer
 
 struct GemmFp8Params {
   const float* a_scale;
@@ -101,10 +107,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* full = bars;                    // [kStages]
   uint64_t* empty = bars + kStages;         // [kStages]
   uint64_t* tfull = bars + 2 * kStages;     // [2]
-  uint64_t* tempty = bars + 2 * kStages + 2;  // [2]
-  uint64_t* drain = bars + 2 * kStages + 4;   // [1]
-  uint64_t* amax_bar = bars + 2 * kStages + 5;  // [4] row-quarter pairs of the fused SwiGLU epilogue
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 9);
+  // (bars + 2*kStages + 2, +3 unused: an accumulator buffer is handed back to its issuer on a
+  // hardware barrier, id 1 + buffer, by the eight epilogue warps)
+  uint64_t* drain = bars + 2 * kStages + 4;   // [2] one per issuer
+  uint64_t* amax_bar = bars + 2 * kStages + 6;  // [4] row-quarter pairs of the fused SwiGLU epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 10);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* total_m_tiles_s = abort_flag + 1;
   int* m_tile_start = reinterpret_cast<int*>(smem + Cfg::kTileBytes + Cfg::kBarBytes);  // [groups+1]
@@ -126,9 +133,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     mbar_init(&tfull[0], 1);
     mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], 8);
-    mbar_init(&tempty[1], 8);
-    mbar_init(drain, 1);
+    mbar_init(&drain[0], 1);
+    mbar_init(&drain[1], 1);
     for (int i = 0; i < 4; ++i) mbar_init(&amax_bar[i], 64);
     *abort_flag = 0;
     fence_mbar_init();
@@ -230,45 +236,60 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ UMMA issuer -------------------------------
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ UMMA issuers ------------------------------
     B200_REG_DEC();
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(0, 0, 0, B_MN_MAJOR ? 1 : 0, kBlockM, BLOCK_N);
-      uint32_t it = 0, ab = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < num_kb; ++kb, ++it, ++ab) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          const int buf = ab & 1;
-          const uint32_t aph = (ab >> 1) & 1;
-          if (!mbar_wait(&tempty[buf], aph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
-          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(sA + s * Cfg::kABytes);
-          const uint32_t b_addr = smem_u32(sB + s * Cfg::kBBytes);
-          const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
-          const uint64_t bdesc = B_MN_MAJOR ? make_smem_desc(b_addr, 128 * kBlockK, 1024)
-                                            : make_smem_desc(b_addr, 16, 1024);
-          const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-#pragma unroll
-          for (int k = 0; k < kBlockK / 32; ++k) {
-            // K-major: 32 bytes further along the 128-byte swizzled row.
-            // MN-major: 32 K-rows of 128 bytes further.
-            const uint64_t a_k = adesc + (uint64_t)((k * 32) >> 4);
-            const uint64_t b_k = bdesc + (uint64_t)(B_MN_MAJOR ? ((k * 32 * 128) >> 4) : ((k * 32) >> 4));
-            umma_f8(d_tmem, a_k, b_k, idesc, k > 0 ? 1u : 0u);
-          }
-          umma_commit(&empty[s]);
-          umma_commit(&tfull[buf]);
+    // The whole warp walks the loop (the hardware barrier counts warps); lane 0 issues.
+    constexpr uint32_t idesc = make_idesc(0, 0, 0, B_MN_MAJOR ? 1 : 0, kBlockM, BLOCK_N);
+    const uint32_t mine = warp == 1 ? 0u : 1u;  // parity of the K blocks (and the buffer) of this warp
+    uint32_t it = 0;  // K blocks since the kernel started: stage it % kStages, buffer it & 1
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((it & 1u) != mine) continue;
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        // the operands first: they have usually landed long ago, so this check is off the
+        // path from the epilogue's release to the next multiplication
+        if (!mbar_wait_warp(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
+        // Everything the multiplications need is computed before the barrier: once the buffer
+        // is free, the fewer instructions lane 0 still has to get through the scheduler (next
+        // to epilogue warps that issue a multiply-add every cycle), the better.
+        const uint64_t adesc = make_smem_desc(smem_u32(sA + s * Cfg::kABytes), 16, 1024);
+        const uint32_t b_addr = smem_u32(sB + s * Cfg::kBBytes);
+        const uint64_t bdesc = B_MN_MAJOR ? make_smem_desc(b_addr, 128 * kBlockK, 1024)
+                                          : make_smem_desc(b_addr, 16, 1024);
+        // K-major: 32 bytes further along the 128-byte swizzled row per MMA.
+        // MN-major: 32 K-rows of 128 bytes further.
+        constexpr uint64_t kStepA = (uint64_t)(32 >> 4);
+        constexpr uint64_t kStepB = (uint64_t)(B_MN_MAJOR ? ((32 * 128) >> 4) : (32 >> 4));
+        const uint32_t d_tmem = tmem_base + mine * BLOCK_N;
+        const uint32_t empty_bar = smem_u32(&empty[s]), tfull_bar = smem_u32(&tfull[mine]);
+        if (it >= 2) {
+          // the buffer holds an earlier K block: its eight readers hand it back here.  An
+          // epilogue warp that unwinds arrives once more, so this cannot wait forever.
+          named_sync(kAccBarrier + mine, kAccBarrierThreads);
         }
+        if (lane == 0) {
+          tc_fence_after_sync();
+          umma_f8(d_tmem, adesc, bdesc, idesc, 0u);
+          umma_f8(d_tmem, adesc + kStepA, bdesc + kStepB, idesc, 1u);
+          umma_f8(d_tmem, adesc + 2 * kStepA, bdesc + 2 * kStepB, idesc, 1u);
+          umma_f8(d_tmem, adesc + 3 * kStepA, bdesc + 3 * kStepB, idesc, 1u);
+          umma_commit_addr(empty_bar);
+          umma_commit_addr(tfull_bar);
+        }
+        // one lane reads the flag so that the warp leaves the loop together (a warp that split
+        // here would come back to the hardware barrier with lanes missing)
+        int aborted = lane == 0 ? *abort_flag : 0;
+        aborted = __shfl_sync(0xffffffffu, aborted, 0);
+        if (aborted) { ok = false; break; }
       }
-      if (!ok) {
-        umma_commit(drain);
-        const long long start = clock64();
-        while (!mbar_try(drain, 0) && clock64() - start < 20000000LL) {}
-      }
+    }
+    if (!ok && lane == 0) {
+      umma_commit(&drain[mine]);
+      const long long start = clock64();
+      while (!mbar_try(&drain[mine], 0) && clock64() - start < 20000000LL) {}
     }
   } else if (warp >= 4) {
     // ------------------------------- epilogue --------------------------------
@@ -349,24 +370,46 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int buf = ab & 1;
           const uint32_t aph = (ab >> 1) & 1;
           ++ab;
-          if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
+          if (!mbar_wait_warp(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N +
                                  (EPI == 1 ? half * 64 : half * kCols);
-#pragma unroll
-          for (int cc = 0; cc < kChunks; ++cc) {
-            uint32_t r[32];
-            // EPI == 1: chunks 0,1 are this thread's 64 gate columns, chunks 2,3 its 64 up columns
-            const int tcol = EPI == 1 ? (cc & 1) * 32 + (cc >> 1) * 128 : cc * 32;
+          // EPI == 1: chunks 0,1 are this thread's 64 gate columns, chunks 2,3 its 64 up columns.
+          // Two tcgen05.ld are kept in flight.
+          auto tcol = [&](int cc) { return EPI == 1 ? (cc & 1) * 32 + (cc >> 1) * 128 : cc * 32; };
+          auto promote = [&](const uint32_t (&r)[32], int cc) {
             const float sc = (EPI == 1 && cc >= 2) ? s_up : s;
-            tmem_ld_32x32(taddr + tcol, r);
-            tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(sc, __uint_as_float(r[j]), acc[cc * 32 + j]);
+          };
+          auto release = [&]() {
+            tc_fence_before_sync();
+            __syncwarp();
+            named_arrive(kAccBarrier + buf, kAccBarrierThreads);
+          };
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32(taddr + tcol(0), ra);
+          tmem_ld_32x32(taddr + tcol(1), rb);
+          tmem_ld_wait();
+          if constexpr (kChunks == 2) {
+            release();
+            promote(ra, 0);
+            promote(rb, 1);
+          } else {
+            static_assert(kChunks == 4, "tile widths are 128 or 256");
+            promote(ra, 0);
+            tmem_ld_32x32(taddr + tcol(2), ra);
+            promote(rb, 1);
+            tmem_ld_32x32(taddr + tcol(3), rb);
+            tmem_ld_wait();
+            // The buffer is handed back only after the last multiply-adds: released earlier,
+            // the 64 FMAs that follow (one per cycle, from both epilogue warps of a
+            // sub-partition) keep the issuer warp from being scheduled, and the next
+            // multiplication starts later than if the release had simply waited for them.
+            promote(ra, 2);
+            promote(rb, 3);
+            release();
           }
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty[buf]);
         }
 #pragma unroll
         for (int u = 0; u < kScaleBatch; ++u) {
@@ -446,7 +489,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           amax_s[half * 128 + row_in_tile] = amax;
           mbar_arrive(&amax_bar[q]);
-          if (!mbar_wait(&amax_bar[q], amax_phase, abort_flag, p.status, 5)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(&amax_bar[q], amax_phase, abort_flag, p.status, 5))) {
+            ok = false;
+            break;
+          }
           amax_phase ^= 1;
           amax = fmaxf(amax, amax_s[(half ^ 1) * 128 + row_in_tile]);
           const float scale = fmaxf(amax * kInv448, 1e-12f);
@@ -468,6 +514,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+    }
+    if (!ok) {
+      // Unwinding: an issuer may be waiting on a hardware barrier for this warp.
+      named_arrive(kAccBarrier + 0, kAccBarrierThreads);
+      named_arrive(kAccBarrier + 1, kAccBarrierThreads);
     }
   }
 

@@ -190,7 +190,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
       const int buf = tb & 1;
       const uint32_t aph = (tb >> 1) & 1;
       ++tb;
-      if (!mbar_wait(&tempty[buf], aph ^ 1, abort_flag, p.status, 23)) { ok = false; break; }
+      if (!mbar_wait_warp(&tempty[buf], aph ^ 1, abort_flag, p.status, 23)) { ok = false; break; }
       int done_kb = 0;
       for (int seg = 0; seg < p.segments && ok; ++seg) {
         int lo, hi;
@@ -199,7 +199,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
         for (int kb = 0; kb < num_kb; ++kb, ++it, ++done_kb) {
           const int s = it % kWgStages;
           const uint32_t ph = (it / kWgStages) & 1;
-          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22)) { ok = false; break; }
+          if (!mbar_wait_warp(&full[s], ph, abort_flag, p.status, 22)) { ok = false; break; }
           const int valid = hi - lo - kb * kWgBlockK;
           if (valid < kWgBlockK) {
             // rows [valid, 64) of both A panels: 128 bytes each, 16 bytes per lane-step
@@ -262,7 +262,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
         buf = tb & 1;
         const uint32_t aph = (tb >> 1) & 1;
         ++tb;
-        if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 24)) { ok = false; break; }
+        if (!mbar_wait_warp(&tfull[buf], aph, abort_flag, p.status, 24)) { ok = false; break; }
         tc_fence_after_sync();
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kWgBlockN + half * kCols;
@@ -457,7 +457,7 @@ grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __gr
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kPairStages;
           const uint32_t ph = (it / kPairStages) & 1;
-          if (!mbar_wait(&landed[s], ph, abort_flag, p.status, 32)) { ok = false; break; }
+          if (!mbar_wait_warp(&landed[s], ph, abort_flag, p.status, 32)) { ok = false; break; }
           const int valid = hi - lo - kb * kWgBlockK;
           if (valid < kWgBlockK) {
             const int nbytes = (kWgBlockK - valid) * 128;
@@ -543,7 +543,7 @@ grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __gr
         buf = tb & 1;
         const uint32_t aph = (tb >> 1) & 1;
         ++tb;
-        if (!mbar_wait(&tfull[buf], aph, abort_flag, p.status, 35)) { ok = false; break; }
+        if (!mbar_wait_warp(&tfull[buf], aph, abort_flag, p.status, 35)) { ok = false; break; }
         tc_fence_after_sync();
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kWgBlockN + half * kCols;
