@@ -210,6 +210,14 @@ __device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                int* status, int where) {
   int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, where) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// ... and with the non-sleeping poll, for waits that sit on a per-K-block handshake.  (A long
+// wait should sleep: on a power-capped part a spinning lane costs clock frequency.)
+__device__ __forceinline__ bool mbar_spin_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int where) {
+  int ok = 1;
   if ((threadIdx.x & 31) == 0) ok = mbar_spin(bar, parity, abort_flag, status, where) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }

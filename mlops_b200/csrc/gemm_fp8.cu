@@ -251,7 +251,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t ph = (it / kStages) & 1;
         // the operands first: they have usually landed long ago, so this check is off the
         // path from the epilogue's release to the next multiplication
-        if (!mbar_wait_warp(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
+        if (!mbar_spin_warp(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
         // Everything the multiplications need is computed before the barrier: once the buffer
         // is free, the fewer instructions lane 0 still has to get through the scheduler (next
         // to epilogue warps that issue a multiply-add every cycle), the better.
@@ -370,7 +370,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int buf = ab & 1;
           const uint32_t aph = (ab >> 1) & 1;
           ++ab;
-          if (!mbar_wait_warp(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
+          if (!mbar_spin_warp(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N +
                                  (EPI == 1 ? half * 64 : half * kCols);
