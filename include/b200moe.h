@@ -184,6 +184,31 @@ int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, const float* a
                                     int F, int K, float limit, int limited, int32_t* status, void* stream);
 
 /*
+ * The down projection with the un-permute / combine fused into its store: instead of bf16
+ * expert-order rows the kernel adds, with 16-byte fp32 atomics,
+ *   out_f32[row_token[r], 0:N] += row_weight[r] * bf16(product[r, 0:N])
+ * (the product rounded to bf16 first, as the stored expert output would be).  out_f32
+ * [tokens, N] (pitch ldo floats, a multiple of 4) must hold each token's starting value (zero);
+ * row_token / row_weight give, per expert-order row, its token and route weight.  The other
+ * arguments are those of b200moe_grouped_gemm_fp8 (tile width 256).  The K contributions of a
+ * token arrive in no fixed order: results are not bitwise repeatable, which is why the
+ * two-kernel form (b200moe_grouped_gemm_fp8 + b200moe_combine) is the default.
+ * b200moe_finish_combine then writes out[t] = bf16(sums[t] + residual[t]) (residual may be NULL).
+ * Reference: src/mlops/kernels/moe_dispatch.py:168-196 (`combine`) after
+ * src/mlops/kernels/block_fp8.py:249-341; the fused form is the one
+ * src/mlops/providers/sonicmoe names `down projection + scatter`.
+ */
+int b200moe_grouped_gemm_fp8_combine(const void* a, long long lda, const float* a_scale,
+                                     long long as_row_stride, long long as_kb_stride, const void* b,
+                                     const float* b_scale, float* out_f32, long long ldo,
+                                     const int32_t* row_token, const float* row_weight, const void* addend,
+                                     long long ldc, const int32_t* offsets, int groups, int weights,
+                                     long long rows_total, int N, int K, int b_mn_major, int32_t* status,
+                                     void* stream);
+int b200moe_finish_combine(const float* sums, long long lds, const void* residual, long long ldr, void* out,
+                           long long ldo, long long tokens, int width, void* stream);
+
+/*
  * Process-wide cap on the CTAs the persistent tensor-core kernels launch (they launch one CTA
  * per SM and leave no room for another kernel on an SM they occupy).  A caller that overlaps
  * them with communication kernels keeps a few SMs free: ctas = SM count - reserved; 0 restores

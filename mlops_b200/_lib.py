@@ -47,6 +47,11 @@ SIGNATURES = {
         I,
         [P, LL, P, LL, LL, P, P, P, LL, P, LL, P, LL, LL, P, I, I, LL, I, I, F, I, P, P],
     ),
+    "b200moe_grouped_gemm_fp8_combine": (
+        I,
+        [P, LL, P, LL, LL, P, P, P, LL, P, P, P, LL, P, I, I, LL, I, I, I, P, P],
+    ),
+    "b200moe_finish_combine": (I, [P, LL, P, LL, P, LL, LL, I, P]),
     "b200moe_grouped_wgrad_bf16": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, P, P]),
     "b200moe_set_cta_limit": (I, [I]),
     "b200moe_lora_project": (I, [P, LL, P, I, P, I, LL, I, I, P, LL, P]),

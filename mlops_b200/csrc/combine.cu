@@ -73,6 +73,39 @@ __global__ void gather_scalar_kernel(const float* __restrict__ values, const int
   if (i < n) out[i] = values[slots[i]];
 }
 
+// out[t] = bf16(sums[t] + residual[t]): the rounding that ends a combine whose route-weighted
+// sum was formed in fp32 by the down projection's fused store.
+__global__ void __launch_bounds__(256)
+finish_combine_kernel(const float* __restrict__ sums, long long lds, const __nv_bfloat16* __restrict__ residual,
+                      long long ldr, __nv_bfloat16* __restrict__ out, long long ldo, long long tokens, int D) {
+  const int per_row = D / 8;
+  const long long total = tokens * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8;
+    const float4 lo = *reinterpret_cast<const float4*>(sums + t * lds + c);
+    const float4 hi = *reinterpret_cast<const float4*>(sums + t * lds + c + 4);
+    float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    if (residual != nullptr) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(residual + t * ldr + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        v[2 * k] += f.x;
+        v[2 * k + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]);
+    o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]);
+    o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(out + t * ldo + c) = o;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -111,5 +144,21 @@ extern "C" int b200moe_gather_scalar(const float* values, const int32_t* slots, 
   if (n == 0) return B200MOE_OK;
   gather_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       values, slots, n, out);
+  return launch_status();
+}
+
+extern "C" int b200moe_finish_combine(const float* sums, long long lds, const void* residual, long long ldr,
+                                      void* out, long long ldo, long long tokens, int width, void* stream) {
+  if (!sums || !out || tokens < 0 || width <= 0) return B200MOE_ERR_ARG;
+  if ((width % 8) || (lds % 4) || (ldo % 8) || (residual && (ldr % 8))) return B200MOE_ERR_ALIGN;
+  if (((uintptr_t)sums & 15) || ((uintptr_t)out & 15) || ((uintptr_t)residual & 15)) return B200MOE_ERR_ALIGN;
+  if (tokens == 0) return B200MOE_OK;
+  const long long work = tokens * (width / 8);
+  long long blocks = (work + 255) / 256;
+  const long long cap = (long long)sm_count_device() * 8;
+  if (blocks > cap) blocks = cap;
+  finish_combine_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      sums, lds, reinterpret_cast<const __nv_bfloat16*>(residual), ldr, reinterpret_cast<__nv_bfloat16*>(out), ldo,
+      tokens, width);
   return launch_status();
 }

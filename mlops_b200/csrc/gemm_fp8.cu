@@ -10,7 +10,9 @@
 // src/mlops/kernels/block_fp8.py:217-223, kernels/quack_moe/block_fp8_gemm.py:1087-1136).
 //
 // One persistent CTA per SM, 12 warps:
-//   warp 0      TMA producer (A tile 128x128 bytes, B tile BLOCK_N x 128 bytes per stage)
+//   warp 0      TMA producer (A tile 128x128 bytes, B tile BLOCK_N x 128 bytes per stage);
+//               also draws the CTA's tiles from a global counter and publishes them to the
+//               other roles (dynamic scheduling: see `tile_at` in the kernel)
 //   warps 1, 3  UMMA issuers (one thread each), 4 x (128 x BLOCK_N x 32) per K block.  Even K
 //               blocks (accumulator buffer 0) belong to warp 1, odd ones (buffer 1) to warp 3:
 //               the two streams are independent, so while one thread is between K blocks
@@ -26,6 +28,8 @@
 #include "common.cuh"
 #include "host_util.h"
 
+#include <atomic>
+
 namespace b200 {
 
 constexpr int kMaxGroups = 1024;
@@ -35,6 +39,12 @@ constexpr int kGemmThreads = 384;
 constexpr int kScaleBatch = 4;  // K blocks of scales fetched ahead by the epilogue
 constexpr uint32_t kAccBarrier = 1;  // hardware barriers 1, 2: accumulator buffer 0, 1 drained
 constexpr uint32_t kAccBarrierThreads = (8 + 1) * 32;  // eight epilogue warps and the buffer's issuer
+
+// Tile counters of the dynamic scheduler: [slot][0] next tile, [slot][1] CTAs that have finished.
+// A launch takes the next slot (host side, round robin); the last CTA to finish zeroes its slot,
+// so a slot is ready again long before 64 further launches have gone by.
+constexpr int kSchedSlots = 64;
+__device__ int g_tile_counter[kSchedSlots][2];
 
 struct GemmFp8Params {
   const float* a_scale;
@@ -55,6 +65,12 @@ struct GemmFp8Params {
   long long acts_row_stride, acts_kb_stride;
   float limit;
   int limited;
+  // fused combine epilogue (EPI == 2): out_f32[row_token[r], :] += row_weight[r] * bf16(D[r, :])
+  float* out_f32;
+  long long ldo;
+  const int* row_token;
+  const float* row_weight;
+  int sched_slot;
   int* status;
 };
 
@@ -65,7 +81,7 @@ struct GemmCfg {
   static constexpr int kBBytes = BLOCK_N * kBlockK;
   static constexpr int kTmemCols = 2 * BLOCK_N;
   static constexpr int kTileBytes = kStages * (kABytes + kBBytes);
-  static constexpr int kBarBytes = 256;
+  static constexpr int kBarBytes = 384;
   static constexpr int kSchedBytes = (2 * (kMaxGroups + 1) * 4 + 15) / 16 * 16;
   static constexpr int kStoreBytes = 8 * 32 * 80;  // per-warp transpose buffers of the epilogue
   static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + kStoreBytes + 1024;
@@ -111,9 +127,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // hardware barrier, id 1 + buffer, by the eight epilogue warps)
   uint64_t* drain = bars + 2 * kStages + 4;   // [2] one per issuer
   uint64_t* amax_bar = bars + 2 * kStages + 6;  // [4] row-quarter pairs of the fused SwiGLU epilogue
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 10);
+  uint64_t* sched_full = bars + 2 * kStages + 10;   // [4] ring of tile ids: slot published
+  uint64_t* sched_empty = bars + 2 * kStages + 14;  // [4] ... and read by every consumer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 18);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* total_m_tiles_s = abort_flag + 1;
+  int* sched_tile = total_m_tiles_s + 1;  // [4]
   int* m_tile_start = reinterpret_cast<int*>(smem + Cfg::kTileBytes + Cfg::kBarBytes);  // [groups+1]
   int* offs = m_tile_start + (kMaxGroups + 1);                                          // [groups+1]
 
@@ -136,6 +155,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_init(&drain[0], 1);
     mbar_init(&drain[1], 1);
     for (int i = 0; i < 4; ++i) mbar_init(&amax_bar[i], 64);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&sched_full[i], 1);
+      mbar_init(&sched_empty[i], 10);  // two issuer warps and eight epilogue warps
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -187,6 +210,22 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = (*total_m_tiles_s) * num_n_tiles;
 
+  // Tiles are handed out by a global counter, not by stride: a CTA that becomes resident late
+  // (its SM was busy with another kernel, e.g. a collective) simply takes fewer tiles, and no
+  // tile waits for a CTA that has not started.  The producer draws the numbers and publishes
+  // them, one tile ahead, in a four-slot ring in shared memory; -1 ends the sequence.
+  // `tile_at(i)`: the i-th tile of this CTA (warp-wide call; lane 0 waits); `done_with(i)`
+  // lets the slot be reused.  -2: the wait gave up.
+  auto tile_at = [&](uint32_t i) -> int {
+    int t = -2;
+    if (lane == 0 && mbar_spin(&sched_full[i & 3], (i >> 2) & 1, abort_flag, p.status, 7))
+      t = *reinterpret_cast<volatile int*>(&sched_tile[i & 3]);
+    return __shfl_sync(0xffffffffu, t, 0);
+  };
+  auto done_with = [&](uint32_t i) {
+    if (lane == 0) mbar_arrive(&sched_empty[i & 3]);
+  };
+
   // The wide tile keeps 128 fp32 sums per epilogue thread: registers move from the
   // producer warpgroup (warps 0-3) to the two epilogue warpgroups.  Each role adjusts
   // its own limit at the top of its branch so the branches never merge in between.
@@ -197,12 +236,29 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------ TMA producer ------------------------------
     B200_REG_DEC();
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, published = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      auto draw = [&]() {
+        const int t = atomicAdd(&g_tile_counter[p.sched_slot][0], 1);
+        return t < total_tiles ? t : -1;
+      };
+      auto publish = [&](int t) {
+        const uint32_t slot = published & 3;
+        if (!mbar_wait(&sched_empty[slot], ((published >> 2) & 1) ^ 1, abort_flag, p.status, 8)) return false;
+        sched_tile[slot] = t;
+        mbar_arrive(&sched_full[slot]);  // a release: the id is visible to whoever sees the phase
+        ++published;
+        return true;
+      };
+      int t = draw();
+      ok = publish(t);
+      while (ok && t >= 0) {
+        const int t_next = draw();
+        if (!publish(t_next)) { ok = false; break; }  // the epilogue looks one tile ahead
         const int mt = t / num_n_tiles;
         const int n0 = (t - mt * num_n_tiles) * kTileStep;
         const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
+        t = t_next;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -244,7 +300,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t mine = warp == 1 ? 0u : 1u;  // parity of the K blocks (and the buffer) of this warp
     uint32_t it = 0;  // K blocks since the kernel started: stage it % kStages, buffer it & 1
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (uint32_t tile_i = 0; ok; ++tile_i) {
+      const int t = tile_at(tile_i);  // only whether there is another tile matters here
+      if (t == -2) ok = false;         // the wait gave up
+      else done_with(tile_i);
+      if (t < 0) break;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((it & 1u) != mine) continue;
         const int s = it % kStages;
@@ -347,13 +407,19 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     };
     EpiTile cur_tile, nxt_tile;
-    if ((int)blockIdx.x < total_tiles) {
-      cur_tile = describe(blockIdx.x);
+    int t_cur = tile_at(0);
+    if (t_cur == -2) ok = false;
+    if (t_cur >= 0) {
+      cur_tile = describe(t_cur);
       fetch(cur_tile, 0, sa_cur, sb_cur, su_cur);
     }
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const bool has_next = t + (int)gridDim.x < total_tiles;
-      if (has_next) nxt_tile = describe(t + gridDim.x);
+    for (uint32_t tile_i = 0; t_cur >= 0 && ok; ++tile_i) {
+      const int t_nxt = tile_at(tile_i + 1);  // published together with the current one
+      if (t_nxt == -2) { ok = false; break; }
+      const bool has_next = t_nxt >= 0;
+      if (has_next) nxt_tile = describe(t_nxt);
+      done_with(tile_i);
+      t_cur = t_nxt;
       const EpiTile c = cur_tile;
       const int grow = c.grow;
       const int col0 = c.col0;
@@ -446,6 +512,42 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
+          if constexpr (EPI == 2) {
+            // Combine fused into the store: the row, rounded to bf16 as the stored expert
+            // output would be, times its route weight, is added to the token's fp32 row
+            // with 16-byte atomics (4 rows x 64 contiguous bytes per instruction after the
+            // same shared-memory transpose as the plain store).  The K experts of a token
+            // arrive in no fixed order, so the sum is not bitwise repeatable: the plain
+            // store plus `combine_kernel` is.
+            const int tok = lane < rows_here ? p.row_token[grow] : 0;
+            const float wgt = lane < rows_here ? p.row_weight[grow] : 0.f;
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                float4 v;
+                v.x = wgt * __bfloat162float(__float2bfloat16_rn(acc[cc * 32 + sub * 16 + j + 0]));
+                v.y = wgt * __bfloat162float(__float2bfloat16_rn(acc[cc * 32 + sub * 16 + j + 1]));
+                v.z = wgt * __bfloat162float(__float2bfloat16_rn(acc[cc * 32 + sub * 16 + j + 2]));
+                v.w = wgt * __bfloat162float(__float2bfloat16_rn(acc[cc * 32 + sub * 16 + j + 3]));
+                *reinterpret_cast<float4*>(stage + lane * kStageRowBytes + j * 4) = v;
+              }
+              __syncwarp();
+              const int piece = lane & 3;  // 16-byte piece of the 64-byte row slab
+              const int col = col0 + cc * 32 + sub * 16 + piece * 4;
+#pragma unroll
+              for (int pass = 0; pass < 4; ++pass) {
+                const int r = pass * 8 + (lane >> 2);
+                const int tok_r = __shfl_sync(0xffffffffu, tok, r);
+                if (r < rows_here && col + 4 <= p.N) {
+                  const float4 v = *reinterpret_cast<const float4*>(stage + r * kStageRowBytes + piece * 16);
+                  atomicAdd(reinterpret_cast<float4*>(p.out_f32 + (long long)tok_r * p.ldo + col), v);
+                }
+              }
+            }
+            continue;
+          }
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -534,6 +636,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  // The thread that drew this CTA's tiles reports the CTA finished; the last one in the grid
+  // leaves the slot zeroed for a later launch.
+  if (threadIdx.x == 0) {
+    const int finished = atomicAdd(&g_tile_counter[p.sched_slot][1], 1);
+    if (finished == (int)gridDim.x - 1) {
+      g_tile_counter[p.sched_slot][0] = 0;
+      g_tile_counter[p.sched_slot][1] = 0;
+    }
+  }
 }
 
 template <int BLOCK_N, bool B_MN, int EPI = 0>
@@ -550,7 +661,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmF
   const int sms = sm_count();
   if (grid > sms) grid = sms;
   if (grid < 1) grid = 1;
-  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  static std::atomic<unsigned> next_slot{0};
+  GemmFp8Params q = p;
+  q.sched_slot = (int)(next_slot.fetch_add(1) % (unsigned)kSchedSlots);
+  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, q);
   return launch_status();
 }
 
@@ -558,13 +672,18 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmF
 
 using namespace b200;
 
-extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
-                                        long long as_row_stride, long long as_kb_stride, const void* b,
-                                        const float* b_scale, void* d, long long ldd,
-                                        const void* addend, long long ldc, const int32_t* offsets, int groups, int weights,
-                                        long long rows_total, int N, int K, int b_mn_major, int block_n,
-                                        int32_t* status, void* stream) {
-  if (!a || !a_scale || !b || !b_scale || !d || !offsets || !status) return B200MOE_ERR_ARG;
+// Shared by the plain product (d != NULL) and the one with the combine fused into its store
+// (out_f32 != NULL).
+static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_scale, long long as_row_stride,
+                                 long long as_kb_stride, const void* b, const float* b_scale, void* d,
+                                 long long ldd, float* out_f32, long long ldo, const int32_t* row_token,
+                                 const float* row_weight, const void* addend, long long ldc,
+                                 const int32_t* offsets, int groups, int weights, long long rows_total, int N,
+                                 int K, int b_mn_major, int block_n, int32_t* status, void* stream) {
+  const bool fused = out_f32 != nullptr;
+  if (!a || !a_scale || !b || !b_scale || !offsets || !status) return B200MOE_ERR_ARG;
+  if (fused ? (!row_token || !row_weight || d != nullptr) : !d) return B200MOE_ERR_ARG;
+  if (fused && (block_n != 256 || (ldo % 4) || ((uintptr_t)out_f32 & 15) || (N % 4))) return B200MOE_ERR_ALIGN;
   if (groups <= 0 || N <= 0 || K <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
   if (weights <= 0 || groups % weights != 0) return B200MOE_ERR_ARG;
   if (groups > kMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
@@ -607,6 +726,10 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
   p.acts_row_stride = p.acts_kb_stride = 0;
   p.limit = 0.f;
   p.limited = 0;
+  p.out_f32 = out_f32;
+  p.ldo = ldo;
+  p.row_token = row_token;
+  p.row_weight = row_weight;
   p.status = status;
   if (!b_mn_major) {
     // B is [groups, N, K], K contiguous; scales [groups, ceil(N/128), ceil(K/128)].
@@ -633,10 +756,39 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
     p.bs_k_stride = nblocks;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (fused) return b_mn_major ? launch_gemm<256, true, 2>(ta, tb, p, s) : launch_gemm<256, false, 2>(ta, tb, p, s);
   if (block_n == 128) {
     return b_mn_major ? launch_gemm<128, true>(ta, tb, p, s) : launch_gemm<128, false>(ta, tb, p, s);
   }
   return b_mn_major ? launch_gemm<256, true>(ta, tb, p, s) : launch_gemm<256, false>(ta, tb, p, s);
+}
+
+extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
+                                        long long as_row_stride, long long as_kb_stride, const void* b,
+                                        const float* b_scale, void* d, long long ldd,
+                                        const void* addend, long long ldc, const int32_t* offsets, int groups, int weights,
+                                        long long rows_total, int N, int K, int b_mn_major, int block_n,
+                                        int32_t* status, void* stream) {
+  if (!d) return B200MOE_ERR_ARG;
+  return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, d, ldd, nullptr, 0,
+                               nullptr, nullptr, addend, ldc, offsets, groups, weights, rows_total, N, K,
+                               b_mn_major, block_n, status, stream);
+}
+
+// The down projection with the un-permute / combine fused into its store:
+//   out_f32[row_token[r], :] += row_weight[r] * bf16(sum_k ... [r, :])   (16-byte fp32 atomics)
+// out_f32 must hold the starting value of every token row (zero, or the residual).
+extern "C" int b200moe_grouped_gemm_fp8_combine(const void* a, long long lda, const float* a_scale,
+                                                long long as_row_stride, long long as_kb_stride, const void* b,
+                                                const float* b_scale, float* out_f32, long long ldo,
+                                                const int32_t* row_token, const float* row_weight,
+                                                const void* addend, long long ldc, const int32_t* offsets,
+                                                int groups, int weights, long long rows_total, int N, int K,
+                                                int b_mn_major, int32_t* status, void* stream) {
+  if (!out_f32) return B200MOE_ERR_ARG;
+  return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, nullptr, 0, out_f32, ldo,
+                               row_token, row_weight, addend, ldc, offsets, groups, weights, rows_total, N, K,
+                               b_mn_major, 256, status, stream);
 }
 
 // Up projection with the SwiGLU epilogue fused: h13 (bf16, gate columns then up columns, the
@@ -703,6 +855,10 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.acts_kb_stride = acts_block_stride;
   p.limit = limit;
   p.limited = limited;
+  p.out_f32 = nullptr;
+  p.ldo = 0;
+  p.row_token = nullptr;
+  p.row_weight = nullptr;
   p.status = status;
   return launch_gemm<256, false, 1>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -160,6 +160,7 @@ def forward_routed(
     block_n: int = BLOCK_N_DEFAULT,
     route: tuple[torch.Tensor, torch.Tensor] | None = None,
     fuse_swiglu: bool = False,
+    fuse_combine: bool = False,
 ) -> tuple[torch.Tensor, ...]:
     """Returns `(output, aux, counts, probability_sum, logits, route_weights, route_ids,
     order, offsets, slots, h13)`.
@@ -170,7 +171,10 @@ def forward_routed(
     statistics are still computed). `fuse_swiglu` runs SwiGLU and the activation quantiser in
     the up GEMM's epilogue (bit-identical results; measured 7% slower than the two-kernel form
     at DeepSeek-V3 shapes because the longer tile epilogue stalls the MMA pipeline, hence off
-    by default)."""
+    by default). `fuse_combine` forms the route-weighted sum in the down GEMM's store with fp32
+    atomics instead of writing expert-order rows for `combine`: not bitwise repeatable, and
+    slower for top-8 routing (a token row is read-modify-written eight times in HBM), so it is
+    off by default as well."""
     w13_data, w13_scale = w13
     w2_data, w2_scale = w2
     experts = w13_data.shape[0]
@@ -197,8 +201,13 @@ def forward_routed(
         else:
             h13 = ops.grouped_gemm_fp8(x_q, x_s, w13_data, w13_scale, offsets, block_n=block_n)
             a_q, a_s, _ = ops.swiglu_quantize(h13, limit=swiglu_limit)
-        expert_output = ops.grouped_gemm_fp8(a_q, a_s, w2_data, w2_scale, offsets, block_n=block_n)
-        output = ops.combine(expert_output, slots, route_weights, residual_flat).reshape(original_shape)
+        if fuse_combine:
+            output = ops.grouped_gemm_fp8_combine(
+                a_q, a_s, w2_data, w2_scale, offsets, order, route_weights, h2_flat.shape[0],
+                residual=residual_flat).reshape(original_shape)
+        else:
+            expert_output = ops.grouped_gemm_fp8(a_q, a_s, w2_data, w2_scale, offsets, block_n=block_n)
+            output = ops.combine(expert_output, slots, route_weights, residual_flat).reshape(original_shape)
         aux, counts, probability_sum = routing_statistics(
             logits, route_ids, counts, routing_mode=str(routing_mode), lengths=normalized, experts=experts
         )

@@ -340,6 +340,58 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
     return out
 
 
+def grouped_gemm_fp8_combine(a_q, a_scale, b_q, b_scale, offsets, order, route_weights, tokens, *,
+                             residual=None, addend=None):
+    """Down projection with the combine fused into its store: returns bf16 `[tokens, N]` =
+    `residual + sum over the token's assignments of weight * bf16(product row)`. The sum is
+    formed with fp32 atomics in arrival order, so it is not bitwise repeatable (the unfused
+    `grouped_gemm_fp8` + `combine` is). `order [rows]` is the sort's permutation (assignment
+    index of every expert-order row), `route_weights [tokens, K]` fp32."""
+    device = _need_cuda(a_q, a_scale, b_q, b_scale, offsets, order, route_weights, residual, addend)
+    rows, k = a_q.shape
+    weights = b_q.shape[0]
+    groups = offsets.numel() - 1
+    n = b_q.shape[1]
+    if b_q.shape[2] != k:
+        raise NativeError(f"contraction sizes differ: A has {k}, B has {b_q.shape[2]}")
+    if not b_q.is_contiguous() or not b_scale.is_contiguous():
+        raise NativeError("weights and their scales must be contiguous")
+    if a_scale.dim() == 1:
+        a_scale = a_scale.unsqueeze(1)
+    kblocks = (k + 127) // 128
+    as_kb = 0 if a_scale.shape[1] == 1 else a_scale.stride(1)
+    if a_scale.shape[1] not in (1, kblocks):
+        raise NativeError("a_scale must have 1 or ceil(K/128) columns")
+    top_k = route_weights.shape[1]
+    row_token = torch.div(order, top_k, rounding_mode="floor").to(torch.int32)
+    row_weight = route_weights.reshape(-1).float()[order.long()].contiguous()
+    sums = torch.zeros((tokens, n), dtype=torch.float32, device=device)
+    out = torch.empty((tokens, n), dtype=torch.bfloat16, device=device)
+    if rows:
+        with _Timed("fp8", 2.0 * rows * n * k):
+            check(
+                lib.b200moe_grouped_gemm_fp8_combine(
+                    a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
+                    b_q.data_ptr(), b_scale.data_ptr(), sums.data_ptr(), sums.stride(0),
+                    row_token.data_ptr(), row_weight.data_ptr(), _ptr(addend),
+                    0 if addend is None else addend.stride(0), offsets.data_ptr(), groups, weights, rows, n, k,
+                    0, status_block(device).data_ptr(), _stream(),
+                ),
+                "grouped_gemm_fp8_combine",
+            )
+        _count()
+    if tokens:
+        check(
+            lib.b200moe_finish_combine(
+                sums.data_ptr(), sums.stride(0), _ptr(residual), 0 if residual is None else residual.stride(0),
+                out.data_ptr(), out.stride(0), tokens, n, _stream(),
+            ),
+            "finish_combine",
+        )
+        _count()
+    return out
+
+
 def grouped_gemm_fp8_swiglu(a_q, a_scale, w13_q, w13_scale, offsets, *, limit=None, out=None):
     """Up projection with the SwiGLU epilogue fused. Returns `(h13 bf16 [rows, 2F], act_q E4M3
     [rows, F], act_scale [rows, F/128])`: the same three tensors as `grouped_gemm_fp8` followed

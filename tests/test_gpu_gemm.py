@@ -262,3 +262,36 @@ def test_fused_swiglu_epilogue_equals_the_two_kernel_form(counts, inner, k, limi
     assert torch.equal(h13_f, h13)
     assert torch.equal(act_s_f, act_s)
     assert torch.equal(act_q_f.view(torch.uint8), act_q.view(torch.uint8))
+
+
+@pytest.mark.parametrize("counts,n,k,top_k", [([0, 70, 131, 15, 260], 256, 384, 2), ([300, 212], 384, 512, 4),
+                                               ([64, 64, 64, 64], 7168, 256, 8)])
+def test_fused_combine_store_matches_gemm_then_combine(counts, n, k, top_k):
+    """Down GEMM with the combine fused into its store against `grouped_gemm_fp8` followed by
+    `combine`. The fused sum is formed with fp32 atomics in arrival order, so the two results are
+    bf16 roundings of fp32 sums whose order differs; the parity metric is checked as well."""
+    ops = _ops()
+    a_q, a_s, b_q, b_s, offs = _case(counts, n, k, seed=n + k + top_k, mn_major=False)
+    dev = [t.to(DEV) for t in (a_q, a_s, b_q, b_s, offs)]
+    rows = sum(counts)
+    tokens = rows // top_k
+    g = torch.Generator().manual_seed(7)
+    order = torch.randperm(tokens * top_k, generator=g)[:rows].to(torch.int32)  # row -> assignment
+    slots = torch.full((tokens * top_k,), 0, dtype=torch.int32)
+    slots[order.long()] = torch.arange(rows, dtype=torch.int32)
+    route_weights = torch.rand(tokens, top_k, generator=g) + 0.1
+    residual = torch.randn(tokens, n, generator=g).bfloat16()
+    assert rows == tokens * top_k  # every assignment has a row in these cases
+    y = ops.grouped_gemm_fp8(*dev)
+    expected = ops.combine(y, slots.reshape(tokens, top_k).to(DEV), route_weights.to(DEV), residual.to(DEV))
+    fused = ops.grouped_gemm_fp8_combine(*dev, order.to(DEV), route_weights.to(DEV), tokens,
+                                         residual=residual.to(DEV))
+    ops.check_status(DEV)
+    # one bf16 rounding of fp32 sums that differ only in order: at most one ulp of the sum of
+    # the terms' magnitudes
+    magnitude = ops.combine(y.abs(), slots.reshape(tokens, top_k).to(DEV), route_weights.to(DEV),
+                            residual.abs().to(DEV)).float()
+    diff = (fused.float() - expected.float()).abs()
+    assert (diff <= magnitude * 2.0 ** -7 + 1e-6).all(), diff.max().item()
+    mx, mean = O.rel_errors(fused.cpu(), expected.double().cpu())
+    assert mx <= MAX_REL and mean <= MEAN_REL

@@ -164,3 +164,22 @@ def test_fused_swiglu_layer_is_bit_identical():
                                  fuse_swiglu=True)
     assert torch.equal(plain[0], fused[0]) and torch.equal(plain[10], fused[10])
     ops.check_status(DEV)
+
+
+def test_fused_combine_layer_matches_within_one_rounding():
+    """`fuse_combine=True` changes only the order of the fp32 sum behind the output's one bf16
+    rounding; everything saved for the backward pass is unchanged."""
+    layer, ops = _layer()
+    c1 = inputs.config1()
+    w13 = tuple(t.to(DEV) for t in O.quantize_blocks(c1["w13"]))
+    w2 = tuple(t.to(DEV) for t in O.quantize_blocks(c1["w2"]))
+    x, router = c1["x"].to(DEV), c1["router"].to(DEV)
+    residual = torch.randn(x.shape, generator=torch.Generator().manual_seed(3)).bfloat16().to(DEV)
+    plain = layer.forward_routed(x, residual, router, w13, w2, top_k=2, routing_mode="softmax_then_topk")
+    fused = layer.forward_routed(x, residual, router, w13, w2, top_k=2, routing_mode="softmax_then_topk",
+                                 fuse_combine=True)
+    ops.check_status(DEV)
+    mx, mean = O.rel_errors(fused[0].cpu(), plain[0].double().cpu())
+    assert mx <= 2.0 ** -6 and mean <= 1e-4, (mx, mean)
+    for a, b in zip(plain[1:], fused[1:]):
+        assert torch.equal(a, b)
