@@ -210,7 +210,8 @@ def gpu_arm(args, cfg):
     if distributed:
         import torch.distributed as dist
 
-        # the all-to-all kernels run beside the GEMMs on the SMs the layer keeps free (32 by default)
+        # the all-to-all kernels run beside the GEMMs on at most this many SMs; the FP8 GEMMs draw
+        # their tiles dynamically and take whatever SMs are left
         comm_sms = int(os.environ.get("B200MOE_EP_COMM_SMS", "32"))
         os.environ.setdefault("NCCL_MAX_CTAS", str(comm_sms))
         dist.init_process_group("nccl", device_id=device)
@@ -269,7 +270,8 @@ def gpu_arm(args, cfg):
                                            n_group=cfg["n_group"], topk_group=cfg["topk_group"],
                                            routed_scaling=cfg["scaling"], expert_map="strided"),
             dist.group.WORLD, router_weight=router, router_bias=bias, w13=w13, w2=w2, shared=shared,
-            device=device, chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "2")), comm_sms=comm_sms)
+            device=device, chunks=int(os.environ["B200MOE_EP_CHUNKS"]) if "B200MOE_EP_CHUNKS" in os.environ else None,
+            comm_sms=int(os.environ.get("B200MOE_EP_LIMIT_SMS", "0")))
 
     rows_received = []
 

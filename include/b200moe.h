@@ -165,6 +165,21 @@ int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
                              int32_t* status, void* stream);
 
 /*
+ * b200moe_grouped_gemm_fp8 with a scattered store: d[row_map[r], 0:N] = product[r, 0:N]
+ * (row_map: int32 [rows_total], a permutation of the rows that belong to a group).  The
+ * expert-parallel layer multiplies received rows in expert order and gives them back in the
+ * [source rank][expert] order the return exchange wants, without a pass of its own.
+ * No counterpart in the reference (its transport returns rows through MoonEP's own buffers,
+ * src/mlops/expert_parallel/quack/layer.py).
+ */
+int b200moe_grouped_gemm_fp8_scatter(const void* a, long long lda, const float* a_scale,
+                                     long long as_row_stride, long long as_kb_stride, const void* b,
+                                     const float* b_scale, void* d, long long ldd, const int32_t* row_map,
+                                     const void* addend, long long ldc, const int32_t* offsets, int groups,
+                                     int weights, long long rows_total, int N, int K, int b_mn_major,
+                                     int block_n, int32_t* status, void* stream);
+
+/*
  * The up projection with its SwiGLU fused into the GEMM epilogue: one kernel writes
  *   h13   bf16 [rows_total, 2F] (pitch ldh): gate columns then up columns, the residual the
  *         backward pass reads, and

@@ -43,6 +43,10 @@ SIGNATURES = {
         I,
         [P, LL, P, LL, LL, P, P, P, LL, P, LL, P, I, I, LL, I, I, I, I, P, P],
     ),
+    "b200moe_grouped_gemm_fp8_scatter": (
+        I,
+        [P, LL, P, LL, LL, P, P, P, LL, P, P, LL, P, I, I, LL, I, I, I, I, P, P],
+    ),
     "b200moe_grouped_gemm_fp8_swiglu": (
         I,
         [P, LL, P, LL, LL, P, P, P, LL, P, LL, P, LL, LL, P, I, I, LL, I, I, F, I, P, P],

@@ -29,6 +29,7 @@
 #include "host_util.h"
 
 #include <atomic>
+#include <cstdlib>
 
 namespace b200 {
 
@@ -70,6 +71,7 @@ struct GemmFp8Params {
   long long ldo;
   const int* row_token;
   const float* row_weight;
+  const int* row_map;  // optional: output row r is stored at d[row_map[r]] (NULL: in place)
   int sched_slot;
   int* status;
 };
@@ -492,8 +494,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // contiguous bytes per instruction (whole 32-byte sectors).
       {
         uint8_t* stage = stage_base + (warp - 4) * kStageWarpBytes;
-        const int warp_row0 = c.grow - lane;  // global row of lane 0
         const int rows_here = c.rows_valid - q * 32;  // rows of this warp that belong to the group
+        // where this lane's row goes: in place, or wherever the caller's map sends it (rows
+        // that arrived as [source rank][expert] and were multiplied in expert order go back)
+        const int out_row = (p.row_map != nullptr && lane < rows_here) ? p.row_map[grow] : grow;
 #pragma unroll
         for (int cc = 0; cc < kChunks; ++cc) {
           if (p.addend != nullptr && lane < rows_here) {
@@ -565,9 +569,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int pass = 0; pass < 4; ++pass) {
             const int r = pass * 8 + (lane >> 2);
+            const int dst_row = __shfl_sync(0xffffffffu, out_row, r);
             if (r < rows_here && col + 8 <= p.N) {
               const uint4 v = *reinterpret_cast<const uint4*>(stage + r * kStageRowBytes + piece * 16);
-              *reinterpret_cast<uint4*>(p.d + (long long)(warp_row0 + r) * p.ldd + col) = v;
+              *reinterpret_cast<uint4*>(p.d + (long long)dst_row * p.ldd + col) = v;
             }
           }
         }
@@ -658,7 +663,14 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmF
   const long long m_tiles_bound = (p.rows_total + kBlockM - 1) / kBlockM + p.groups;
   const long long n_tiles = EPI == 1 ? p.N / 256 : (p.N + BLOCK_N - 1) / BLOCK_N;
   long long grid = m_tiles_bound * n_tiles;
-  const int sms = sm_count();
+  // Tiles are drawn dynamically, so this kernel always asks for every SM: CTAs that find their
+  // SM taken by a concurrent kernel start late and take fewer tiles.  (B200MOE_GEMM_HONOUR_LIMIT=1
+  // makes it respect b200moe_set_cta_limit like the statically scheduled kernels.)
+  static const bool honour = [] {
+    const char* v = getenv("B200MOE_GEMM_HONOUR_LIMIT");
+    return v != nullptr && v[0] == '1';
+  }();
+  const int sms = honour ? sm_count() : sm_count_device();
   if (grid > sms) grid = sms;
   if (grid < 1) grid = 1;
   static std::atomic<unsigned> next_slot{0};
@@ -677,9 +689,10 @@ using namespace b200;
 static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_scale, long long as_row_stride,
                                  long long as_kb_stride, const void* b, const float* b_scale, void* d,
                                  long long ldd, float* out_f32, long long ldo, const int32_t* row_token,
-                                 const float* row_weight, const void* addend, long long ldc,
-                                 const int32_t* offsets, int groups, int weights, long long rows_total, int N,
-                                 int K, int b_mn_major, int block_n, int32_t* status, void* stream) {
+                                 const float* row_weight, const int32_t* row_map, const void* addend,
+                                 long long ldc, const int32_t* offsets, int groups, int weights,
+                                 long long rows_total, int N, int K, int b_mn_major, int block_n,
+                                 int32_t* status, void* stream) {
   const bool fused = out_f32 != nullptr;
   if (!a || !a_scale || !b || !b_scale || !offsets || !status) return B200MOE_ERR_ARG;
   if (fused ? (!row_token || !row_weight || d != nullptr) : !d) return B200MOE_ERR_ARG;
@@ -730,6 +743,7 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
   p.ldo = ldo;
   p.row_token = row_token;
   p.row_weight = row_weight;
+  p.row_map = row_map;
   p.status = status;
   if (!b_mn_major) {
     // B is [groups, N, K], K contiguous; scales [groups, ceil(N/128), ceil(K/128)].
@@ -771,7 +785,22 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
                                         int32_t* status, void* stream) {
   if (!d) return B200MOE_ERR_ARG;
   return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, d, ldd, nullptr, 0,
-                               nullptr, nullptr, addend, ldc, offsets, groups, weights, rows_total, N, K,
+                               nullptr, nullptr, nullptr, addend, ldc, offsets, groups, weights, rows_total, N, K,
+                               b_mn_major, block_n, status, stream);
+}
+
+// The same product with its rows stored where `row_map` says: d[row_map[r], :] = product[r, :].
+// row_map must be a permutation of the rows that belong to a group (rows_total entries).
+extern "C" int b200moe_grouped_gemm_fp8_scatter(const void* a, long long lda, const float* a_scale,
+                                                long long as_row_stride, long long as_kb_stride, const void* b,
+                                                const float* b_scale, void* d, long long ldd,
+                                                const int32_t* row_map, const void* addend, long long ldc,
+                                                const int32_t* offsets, int groups, int weights,
+                                                long long rows_total, int N, int K, int b_mn_major, int block_n,
+                                                int32_t* status, void* stream) {
+  if (!d || !row_map) return B200MOE_ERR_ARG;
+  return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, d, ldd, nullptr, 0,
+                               nullptr, nullptr, row_map, addend, ldc, offsets, groups, weights, rows_total, N, K,
                                b_mn_major, block_n, status, stream);
 }
 
@@ -787,8 +816,8 @@ extern "C" int b200moe_grouped_gemm_fp8_combine(const void* a, long long lda, co
                                                 int b_mn_major, int32_t* status, void* stream) {
   if (!out_f32) return B200MOE_ERR_ARG;
   return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, nullptr, 0, out_f32, ldo,
-                               row_token, row_weight, addend, ldc, offsets, groups, weights, rows_total, N, K,
-                               b_mn_major, 256, status, stream);
+                               row_token, row_weight, nullptr, addend, ldc, offsets, groups, weights, rows_total,
+                               N, K, b_mn_major, 256, status, stream);
 }
 
 // Up projection with the SwiGLU epilogue fused: h13 (bf16, gate columns then up columns, the
@@ -859,6 +888,7 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.ldo = 0;
   p.row_token = nullptr;
   p.row_weight = nullptr;
+  p.row_map = nullptr;
   p.status = status;
   return launch_gemm<256, false, 1>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -182,10 +182,11 @@ def _scale_buffer(rows, blocks, device):
     return torch.empty((blocks, max(rows, 1)), dtype=torch.float32, device=device)[:, :rows].t()
 
 
-def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False):
+def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False, copy_out=None):
     """E4M3 rows and fp32 scales of bf16 `x [T, D]`; output row r reads input row
     `gather[r] // gather_div`. Returns (q [R, D] float8_e4m3fn, scales [R, blocks]); with
-    `with_copy` also the gathered bf16 rows themselves, written by the same pass."""
+    `with_copy` also the gathered bf16 rows themselves, written by the same pass (into
+    `copy_out [R, D]` when given)."""
     _need_cuda(x, gather)
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
         raise NativeError("x must be bf16 [rows, width] with unit inner stride")
@@ -194,14 +195,20 @@ def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False
     q = torch.empty((rows, width), dtype=FP8, device=x.device)
     blocks = (width + 127) // 128 if mode == "1x128" else 1
     scales = _scale_buffer(rows, blocks, x.device)
-    copy = torch.empty((rows, width), dtype=torch.bfloat16, device=x.device) if with_copy else None
+    copy = None
+    if copy_out is not None:
+        if copy_out.shape != (rows, width) or copy_out.dtype != torch.bfloat16 or copy_out.stride(1) != 1:
+            raise NativeError("copy_out must be bf16 [rows, width] with unit inner stride")
+        copy, with_copy = copy_out, True
+    elif with_copy:
+        copy = torch.empty((rows, width), dtype=torch.bfloat16, device=x.device)
     if rows == 0:
         return (q, scales, copy) if with_copy else (q, scales)
     check(
         lib.b200moe_quantize_rows(
             x.data_ptr(), x.stride(0), _ptr(gather), int(gather_div), rows, width, q.data_ptr(),
             q.stride(0), scales.data_ptr(), scales.stride(0), scales.stride(1),
-            0 if mode == "1x128" else 1, _ptr(copy), width, _stream(),
+            0 if mode == "1x128" else 1, _ptr(copy), width if copy is None else copy.stride(0), _stream(),
         ),
         "quantize_rows",
     )
@@ -298,11 +305,12 @@ def quantize_blocks(weight):
 
 # ------------------------------------------------------------------------------- GEMMs
 def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, block_n=256, out=None,
-                     addend=None):
+                     addend=None, row_map=None):
     """bf16 `[rows, N]` of the grouped block-FP8 product. `b_q` is `[G, N, K]`
     (`b_mn_major=False`) or `[G, K, N]` read along its rows (`b_mn_major=True`);
-    `a_scale` is `[rows, K/128]` (any strides) or `[rows]`/`[rows, 1]` for one scale per row."""
-    device = _need_cuda(a_q, a_scale, b_q, b_scale, offsets, addend)
+    `a_scale` is `[rows, K/128]` (any strides) or `[rows]`/`[rows, 1]` for one scale per row.
+    `row_map` (int32 `[rows]`, a permutation) stores product row r at `out[row_map[r]]`."""
+    device = _need_cuda(a_q, a_scale, b_q, b_scale, offsets, addend, row_map)
     rows, k = a_q.shape
     weights = b_q.shape[0]
     groups = offsets.numel() - 1  # a multiple of `weights`: group g multiplies weight g % weights
@@ -326,16 +334,30 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
     if rows == 0:
         return out
     with _Timed("fp8", 2.0 * rows * n * k):
-        check(
-            lib.b200moe_grouped_gemm_fp8(
-                a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
-                b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), _ptr(addend),
-                0 if addend is None else addend.stride(0), offsets.data_ptr(),
-                groups, weights, rows, n, k, 1 if b_mn_major else 0, int(block_n),
-                status_block(device).data_ptr(), _stream(),
-            ),
-            "grouped_gemm_fp8",
-        )
+        if row_map is None:
+            check(
+                lib.b200moe_grouped_gemm_fp8(
+                    a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
+                    b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), _ptr(addend),
+                    0 if addend is None else addend.stride(0), offsets.data_ptr(),
+                    groups, weights, rows, n, k, 1 if b_mn_major else 0, int(block_n),
+                    status_block(device).data_ptr(), _stream(),
+                ),
+                "grouped_gemm_fp8",
+            )
+        else:
+            if row_map.dtype != torch.int32 or row_map.numel() != rows or not row_map.is_contiguous():
+                raise NativeError("row_map must be a contiguous int32 vector with one entry per row")
+            check(
+                lib.b200moe_grouped_gemm_fp8_scatter(
+                    a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
+                    b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), out.stride(0), row_map.data_ptr(),
+                    _ptr(addend), 0 if addend is None else addend.stride(0), offsets.data_ptr(),
+                    groups, weights, rows, n, k, 1 if b_mn_major else 0, int(block_n),
+                    status_block(device).data_ptr(), _stream(),
+                ),
+                "grouped_gemm_fp8_scatter",
+            )
     _count()
     return out
 

@@ -295,3 +295,19 @@ def test_fused_combine_store_matches_gemm_then_combine(counts, n, k, top_k):
     assert (diff <= magnitude * 2.0 ** -7 + 1e-6).all(), diff.max().item()
     mx, mean = O.rel_errors(fused.cpu(), expected.double().cpu())
     assert mx <= MAX_REL and mean <= MEAN_REL
+
+
+@pytest.mark.parametrize("mn_major", [False, True])
+def test_scattered_store_places_rows_by_the_map(mn_major):
+    """`row_map`: product row r lands at out[row_map[r]], bit-identical to the plain store."""
+    ops = _ops()
+    counts = [70, 0, 131, 15, 260]
+    a_q, a_s, b_q, b_s, offs = _case(counts, 384, 256, seed=11, mn_major=mn_major)
+    dev = [t.to(DEV) for t in (a_q, a_s, b_q, b_s, offs)]
+    rows = sum(counts)
+    plain = ops.grouped_gemm_fp8(*dev, b_mn_major=mn_major)
+    row_map = torch.randperm(rows, generator=torch.Generator().manual_seed(5)).to(torch.int32).to(DEV)
+    out = torch.full((rows, 384), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.grouped_gemm_fp8(*dev, b_mn_major=mn_major, out=out, row_map=row_map)
+    ops.check_status(DEV)
+    assert torch.equal(out[row_map.long()], plain)

@@ -34,3 +34,29 @@ def test_lengths_must_cover_every_row():
     with pytest.raises(ValueError):
         layer._normalized_lengths((0, 8), 8)
     assert layer._normalized_lengths(None, 8) == (8,)
+
+
+@pytest.mark.parametrize("world,local,seed", [(2, 3, 0), (4, 2, 1), (8, 4, 2), (1, 5, 3)])
+def test_regroup_index_orders_received_rows_by_expert(world, local, seed):
+    """Rows received as [source rank][local expert] segments are renumbered by expert, the
+    sources in rank order inside an expert; the index is a permutation and empty segments are
+    fine."""
+    from mlops_b200.ep import regroup_index
+
+    g = torch.Generator().manual_seed(seed)
+    counts = torch.randint(0, 6, (world, local), generator=g)
+    counts[0, 0] = 0
+    offsets = torch.zeros(world * local + 1, dtype=torch.int32)
+    offsets[1:] = counts.reshape(-1).cumsum(0).to(torch.int32)
+    rows = int(counts.sum())
+    by_expert, source = regroup_index(offsets, world, local, rows)
+    # brute force: walk experts, then sources, and list the arrival positions
+    expected, expected_offsets = [], [0]
+    for e in range(local):
+        for s in range(world):
+            lo = int(offsets[s * local + e])
+            expected.extend(range(lo, lo + int(counts[s, e])))
+        expected_offsets.append(len(expected))
+    assert by_expert.tolist() == expected_offsets
+    assert source.tolist() == expected
+    assert sorted(source.tolist()) == list(range(rows))
