@@ -16,7 +16,7 @@ Workloads (shapes only; weights are random, data synthetic, seeded):
   c4p the same layer at profiling size (32 experts, T=4096: the same 1024 rows per expert,
       a few GB on the device) for ncu captures
   c5  Qwen3-30B-A3B-shaped with rank-16 LoRA on a frozen base and Zipf(1.2) expert popularity:
-      D=2048, 128 experts, F=768, softmax top-8, T=65536 (single GPU only)
+      D=2048, 128 experts, F=768, softmax top-8, T=65536 per GPU (expert-parallel at N > 1)
   c3  Mixtral-8x7B-shaped: D=4096, 8 experts, F=14336, softmax top-2, T=16384
   c1  the small CPU-runnable case: D=256, 8 experts, F=512, softmax top-2, T=512
 """
@@ -240,8 +240,6 @@ def gpu_arm(args, cfg):
 
     lora = None
     if cfg.get("lora_rank"):
-        if distributed:
-            raise SystemExit("the LoRA workload runs on one GPU (expert-parallel LoRA is not built)")
         from mlops_b200.lora import expert_lora
         from mlops_b200.weights import BlockFP8Weight
 
@@ -251,10 +249,12 @@ def gpu_arm(args, cfg):
         router[:, 0] = torch.log(popularity / popularity.sum())
         x[:, 0] = 1.0
         x_host[:, 0] = 1.0
-        factors = [(torch.randn(E, r, D, device=device, generator=gw) * 0.02).bfloat16(),
-                   (torch.randn(E, 2 * F, r, device=device, generator=gw) * 0.01).bfloat16(),
-                   (torch.randn(E, r, F, device=device, generator=gw) * 0.02).bfloat16(),
-                   (torch.randn(E, D, r, device=device, generator=gw) * 0.01).bfloat16()]
+        gf = torch.Generator(device=device).manual_seed(31 + rank)  # this rank's experts' factors
+        El = experts_local
+        factors = [(torch.randn(El, r, D, device=device, generator=gf) * 0.02).bfloat16(),
+                   (torch.randn(El, 2 * F, r, device=device, generator=gf) * 0.01).bfloat16(),
+                   (torch.randn(El, r, F, device=device, generator=gf) * 0.02).bfloat16(),
+                   (torch.randn(El, D, r, device=device, generator=gf) * 0.01).bfloat16()]
         for f in factors:
             f.requires_grad_(True)
         lora = dict(factors=factors, w13=BlockFP8Weight(*w13), w2=BlockFP8Weight(*w2))
@@ -271,7 +271,9 @@ def gpu_arm(args, cfg):
                                            routed_scaling=cfg["scaling"], expert_map="strided"),
             dist.group.WORLD, router_weight=router, router_bias=bias, w13=w13, w2=w2, shared=shared,
             device=device, chunks=int(os.environ["B200MOE_EP_CHUNKS"]) if "B200MOE_EP_CHUNKS" in os.environ else None,
-            comm_sms=int(os.environ.get("B200MOE_EP_LIMIT_SMS", "0")))
+            comm_sms=int(os.environ.get("B200MOE_EP_LIMIT_SMS", "0")),
+            lora=None if lora is None else dict(zip(("a13", "b13", "a2", "b2"), lora["factors"]), scale=1.0),
+            frozen_base=lora is not None)
 
     rows_received = []
 

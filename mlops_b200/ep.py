@@ -160,8 +160,10 @@ class ExpertParallelMoE:
     with local expert gradients and UN-reduced replicated gradients."""
 
     def __init__(self, config: ExpertParallelConfig, ep_group, *, router_weight, w13, w2, router_bias=None,
-                 shared=None, device=None, weight_grad_dtype=torch.bfloat16, chunks=None, comm_sms=0):
+                 shared=None, device=None, weight_grad_dtype=torch.bfloat16, chunks=None, comm_sms=0,
+                 lora=None, frozen_base=False):
         self.config = config
+        self.frozen_base = bool(frozen_base)  # `forward_backward` then skips the base weight gradients
         self.group = ep_group
         self.world = dist.get_world_size(ep_group)
         self.rank = dist.get_rank(ep_group)
@@ -186,6 +188,21 @@ class ExpertParallelMoE:
 
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
             ops.set_cta_limit(max(sms - self.comm_sms, 2) // 2 * 2)
+        # expert LoRA on this rank's shard: dict(a13 [E/G, r, D], b13 [E/G, 2F, r], a2 [E/G, r, F],
+        # b2 [E/G, D, r] bf16, scale).  The factors are kept as the rank kernels want them: rank
+        # padded to a multiple of 8, B factors rank-major.
+        self.lora = None
+        if lora is not None:
+            from .lora import _pad_rank
+
+            a13, rank = _pad_rank(lora["a13"].detach(), 1)
+            b13, _ = _pad_rank(lora["b13"].detach(), 2)
+            a2, _ = _pad_rank(lora["a2"].detach(), 1)
+            b2, _ = _pad_rank(lora["b2"].detach(), 2)
+            if a13.shape[0] != self.local_experts or rank > 64:
+                raise ValueError("LoRA factors must hold this rank's experts, with rank <= 64")
+            self.lora = dict(a13=a13, b13t=b13.transpose(1, 2).contiguous(), a2=a2,
+                             b2t=b2.transpose(1, 2).contiguous(), scale=float(lora["scale"]), rank=rank)
         self.keys = placement(config, self.world, self.device)
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.bytes_moved = 0
@@ -282,6 +299,11 @@ class ExpertParallelMoE:
             x_rows = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
             row_w = torch.empty(total, dtype=torch.float32, device=flat.device)
             h13 = torch.empty((total, 2 * cfg.intermediate), dtype=torch.bfloat16, device=flat.device)
+            lora = self.lora
+            t1 = t2 = None
+            if lora is not None:  # x A13^T and act A2^T of every row: the factor gradients need them
+                t1 = torch.empty((total, lora["a13"].shape[1]), dtype=torch.bfloat16, device=flat.device)
+                t2 = torch.empty_like(t1)
             regroup = [regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
                                      plans[c].recv_rows) for c in range(chunks)]
 
@@ -319,9 +341,21 @@ class ExpertParallelMoE:
                 # order by the down projection's store
                 x_q, x_s, _ = ops.quantize_rows(recv_x[rows], gather=source, copy_out=x_rows[rows])
                 row_w[rows] = recv_w[rows][source.long()]
-                ops.grouped_gemm_fp8(x_q, x_s, *self.w13, offsets, out=h13[rows])
-                a_q, a_s, _ = ops.swiglu_quantize(h13[rows], limit=cfg.swiglu_limit)
-                y = ops.grouped_gemm_fp8(a_q, a_s, *self.w2, offsets, row_map=source)
+                if lora is None:
+                    ops.grouped_gemm_fp8(x_q, x_s, *self.w13, offsets, out=h13[rows])
+                    a_q, a_s, _ = ops.swiglu_quantize(h13[rows], limit=cfg.swiglu_limit)
+                    y = ops.grouped_gemm_fp8(a_q, a_s, *self.w2, offsets, row_map=source)
+                else:
+                    # each LoRA term enters its base product as an addend before the one rounding
+                    # (the single-GPU form: mlops_b200/lora.py)
+                    t1[rows] = ops.lora_project(x_rows[rows], lora["a13"], offsets, rank_major=True)
+                    c1 = ops.lora_expand(t1[rows], lora["b13t"], offsets, wide_major=False, scale=lora["scale"])
+                    ops.grouped_gemm_fp8(x_q, x_s, *self.w13, offsets, out=h13[rows], addend=c1)
+                    a_q, a_s, act = ops.swiglu_quantize(h13[rows], limit=cfg.swiglu_limit, quantized=True,
+                                                        rounded=True)
+                    t2[rows] = ops.lora_project(act, lora["a2"], offsets, rank_major=True)
+                    c2 = ops.lora_expand(t2[rows], lora["b2t"], offsets, wide_major=False, scale=lora["scale"])
+                    y = ops.grouped_gemm_fp8(a_q, a_s, *self.w2, offsets, row_map=source, addend=c2)
                 self._mark("expert fwd")
                 y_back, work = exchange(y, plans[c], self.group, back=True, async_op=True)
                 self.bytes_moved += y.numel() * 2
@@ -343,12 +377,12 @@ class ExpertParallelMoE:
         self._mark("stats")
         saved = dict(flat=flat, logits=logits, weights=weights, ids=ids, parts=parts, plans=plans, starts=starts,
                      x_rows=x_rows, row_w=row_w, regroup=regroup, h13=h13, shared_h13=shared_h13, counts=counts,
-                     shape=x.shape)
+                     shape=x.shape, t1=t1, t2=t2)
         return output.reshape(x.shape), aux, counts, psum, saved
 
     # ---------------------------------------------------------------------- backward
     def backward(self, saved, grad_output, grad_aux=None, grad_probability_sum=None, *, need_router=True,
-                 need_experts=True):
+                 need_experts=True, need_lora=True):
         from . import layer, ops
 
         cfg = self.config
@@ -362,7 +396,13 @@ class ExpertParallelMoE:
             dy = grad_output.reshape_as(flat).contiguous()
             recv_dy = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
             regroup = saved["regroup"]
-            dy_rows = torch.empty((total, width), dtype=flat.dtype, device=flat.device) if need_experts else None
+            lora = self.lora  # its terms are part of the input gradient whether or not the factors train
+            factor_grads = lora is not None and need_lora
+            keep_rows = need_experts or lora is not None
+            dy_rows = torch.empty((total, width), dtype=flat.dtype, device=flat.device) if keep_rows else None
+            t2g = dt1 = None
+            if factor_grads:
+                t2g, dt1 = torch.empty_like(saved["t1"]), torch.empty_like(saved["t1"])
 
             def send(c):
                 part = parts[c]
@@ -384,7 +424,7 @@ class ExpertParallelMoE:
                     if tensor is not None:
                         tensor.record_stream(torch.cuda.current_stream())
             gh_b = act_scaled = None
-            if need_experts:
+            if keep_rows:
                 gh_b = torch.empty((total, 2 * cfg.intermediate), dtype=torch.bfloat16, device=flat.device)
                 act_scaled = torch.empty((total, cfg.intermediate), dtype=torch.bfloat16, device=flat.device)
             returns = []
@@ -397,17 +437,29 @@ class ExpertParallelMoE:
                 count = starts[c + 1] - starts[c]
                 identity = torch.arange(count, dtype=torch.int32, device=flat.device)
                 offsets, source = regroup[c]
-                if need_experts:
+                if keep_rows:
                     dy_q, dy_s, _ = ops.quantize_rows(recv_dy[rows], gather=source, copy_out=dy_rows[rows])
                 else:
                     dy_q, dy_s = ops.quantize_rows(recv_dy[rows], gather=source)
-                r = ops.grouped_gemm_fp8(dy_q, dy_s, *self.w2, offsets, b_mn_major=True)
+                r_add = dx_add = None
+                if lora is not None:
+                    dy_b2 = ops.lora_project(dy_rows[rows], lora["b2t"], offsets, rank_major=True)
+                    r_add = ops.lora_expand(dy_b2, lora["a2"], offsets, wide_major=False, scale=lora["scale"])
+                    if factor_grads:
+                        t2g[rows] = dy_b2
+                r = ops.grouped_gemm_fp8(dy_q, dy_s, *self.w2, offsets, b_mn_major=True, addend=r_add)
                 dscore, gh_q, gh_s, _, _ = ops.dswiglu_routed(
                     saved["h13"][rows], r, saved["row_w"][rows], identity, limit=cfg.swiglu_limit, quantized=True,
-                    rounded=need_experts, scaled_activation=need_experts,
+                    rounded=keep_rows, scaled_activation=keep_rows,
                     rounded_out=None if gh_b is None else gh_b[rows],
                     scaled_out=None if act_scaled is None else act_scaled[rows])
-                grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, *self.w13, offsets, b_mn_major=True, row_map=source)
+                if lora is not None:
+                    gh_b13 = ops.lora_project(gh_b[rows], lora["b13t"], offsets, rank_major=True)
+                    dx_add = ops.lora_expand(gh_b13, lora["a13"], offsets, wide_major=False, scale=lora["scale"])
+                    if factor_grads:
+                        dt1[rows] = gh_b13
+                grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, *self.w13, offsets, b_mn_major=True, row_map=source,
+                                                 addend=dx_add)
                 dscore_arrival = torch.empty_like(dscore)
                 dscore_arrival[source.long()] = dscore
                 dscore = dscore_arrival
@@ -417,10 +469,24 @@ class ExpertParallelMoE:
                 self.bytes_moved += grad_rows.numel() * 2
                 returns.append((grad_rows, dscore, back_rows, back_score, work_rows, work_score))
             grad_w13 = grad_w2 = None
+            lora_grads = {}
+            # every chunk is one segment of expert-ordered rows
+            all_offsets = torch.cat(
+                [regroup[c][0][: -1 if c + 1 < chunks else None] + starts[c] for c in range(chunks)])
+            if factor_grads:  # grouped weight gradients with one narrow side (lora.py, single GPU)
+                scale, rank = lora["scale"], lora["rank"]
+                narrow = lambda t, factor: (t.float() * factor).to(t.dtype)  # noqa: E731
+                experts_here, fdtype = self.local_experts, torch.bfloat16
+                lora_grads["grad_b2"] = ops.grouped_wgrad(
+                    dy_rows, narrow(saved["t2"], saved["row_w"][:, None] * scale), all_offsets, experts_here,
+                    fdtype)[:, :, :rank].contiguous()
+                lora_grads["grad_a2"] = ops.grouped_wgrad(narrow(t2g, scale), act_scaled, all_offsets,
+                                                          experts_here, fdtype)[:, :rank].contiguous()
+                lora_grads["grad_b13"] = ops.grouped_wgrad(gh_b, narrow(saved["t1"], scale), all_offsets,
+                                                           experts_here, fdtype)[:, :, :rank].contiguous()
+                lora_grads["grad_a13"] = ops.grouped_wgrad(narrow(dt1, scale), saved["x_rows"], all_offsets,
+                                                           experts_here, fdtype)[:, :rank].contiguous()
             if need_experts:  # local weight gradients over every chunk; overlaps the last return
-                # every chunk is one segment of expert-ordered rows
-                all_offsets = torch.cat(
-                    [regroup[c][0][: -1 if c + 1 < chunks else None] + starts[c] for c in range(chunks)])
                 grad_w2 = ops.grouped_wgrad(dy_rows, act_scaled, all_offsets, self.local_experts,
                                             self.weight_grad_dtype)
                 grad_w13 = ops.grouped_wgrad(gh_b, saved["x_rows"], all_offsets, self.local_experts,
@@ -447,11 +513,11 @@ class ExpertParallelMoE:
                 grad_x.add_(shared_grads[0])
         self._mark("router grads")
         return dict(grad_x=grad_x.reshape(saved["shape"]), grad_router=grad_router, grad_w13=grad_w13,
-                    grad_w2=grad_w2, grad_shared_w13=shared_grads[1], grad_shared_w2=shared_grads[2])
+                    grad_w2=grad_w2, grad_shared_w13=shared_grads[1], grad_shared_w2=shared_grads[2], **lora_grads)
 
     def forward_backward(self, x, residual, grad_output):
         output, aux, counts, _psum, saved = self.forward(x, residual)
-        grads = self.backward(saved, grad_output)
+        grads = self.backward(saved, grad_output, need_experts=not self.frozen_base)
         return output, grads["grad_x"], aux, counts
 
     def close(self):

@@ -25,3 +25,15 @@ def test_two_rank_layer_matches_single_gpu(expert_map, mode):
     done = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
     assert "ep worker ok" in done.stdout
+
+
+def test_two_rank_expert_lora_matches_single_gpu():
+    """Expert LoRA with a frozen base under expert parallelism against `expert_lora` on one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29614", str(ROOT / "tests" / "ep_lora_worker.py")]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+    assert "ep lora worker ok" in done.stdout
