@@ -22,8 +22,7 @@ namespace b200 {
 enum : int {
   ERR_NONE = 0,
   ERR_WAIT_TIMEOUT = 1,   // an mbarrier wait ran past its limit
-  ERR_BAD_OFFSETS = 2,    // group offsets not monotone / out of range
-  ERR_TOO_MANY_GROUPS = 3
+  ERR_BAD_OFFSETS = 2     // group offsets not monotone / out of range
 };
 
 __device__ __forceinline__ void report_error(int* status, int code, int where, int detail) {
@@ -36,16 +35,6 @@ __device__ __forceinline__ void report_error(int* status, int code, int where, i
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "elect.sync _|P, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
 }
 
 // ----------------------------------------------------------------------------
@@ -63,14 +52,6 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Arrival without release ordering.  The default (release) form makes the hardware wait for
-// the thread's outstanding global loads before the arrival becomes visible -- hundreds of
-// cycles when a prefetch is in flight.  Use it where what the waiter consumes is not ordinary
-// memory written by this thread: a TMEM buffer whose reads were already completed by
-// tcgen05.wait::ld and ordered by tcgen05.fence::before_thread_sync.
-__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
@@ -137,29 +118,6 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t cta) 
       ::"r"(smem_u32(bar)), "r"(cta)
       : "memory");
 }
-// The same with a cluster-scope release: for an arrival that publishes generic-proxy writes
-// of this thread to another CTA.  A cluster-scope release costs about a microsecond, so it is
-// kept off the per-K-block path.
-__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
-  asm volatile(
-      "{\n\t.reg .b32 remote;\n\t"
-      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}"
-      ::"r"(smem_u32(bar)), "r"(cta)
-      : "memory");
-}
-// try_wait that also acquires writes released by another CTA of the cluster.
-__device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 
 // Upper bound of any single wait, in SM clock cycles (about two seconds).
 #ifndef B200_WAIT_LIMIT_CYCLES
@@ -169,8 +127,7 @@ __device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity)
 // Bounded wait.  Returns false when the limit ran out or when another role of
 // this CTA already raised the abort flag; the caller must then unwind.  try_wait itself
 // suspends the thread for a hardware-defined time, so the abort flag and the clock are
-// looked at only every few rounds: a spinning role must not compete with the tensor cores
-// and the TMA unit for shared-memory bandwidth.
+// looked at only every few rounds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int where) {
   if (mbar_try(bar, parity)) return true;
@@ -220,21 +177,6 @@ __device__ __forceinline__ bool mbar_spin_warp(uint64_t* bar, uint32_t parity, v
   int ok = 1;
   if ((threadIdx.x & 31) == 0) ok = mbar_spin(bar, parity, abort_flag, status, where) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  int* status, int where) {
-  if (mbar_try_cluster(bar, parity)) return true;
-  const long long start = clock64();
-  while (true) {
-    if (mbar_try_cluster(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - start > B200_WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
-      report_error(status, ERR_WAIT_TIMEOUT, where, (int)parity);
-      return false;
-    }
-  }
 }
 
 // ----------------------------------------------------------------------------
@@ -336,15 +278,6 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, u
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // One arrival on the mbarrier at this offset in every CTA named by `cta_mask`, once all MMAs
 // issued so far have retired (a commit; it carries no load).
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
@@ -420,24 +353,6 @@ __device__ __forceinline__ float warp_sum(float v) {
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
-}
-// Packed fp32 pairs (Blackwell fma.rn.f32x2: two fused multiply-adds per instruction).
-__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
-  uint64_t v;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
-  return v;
-}
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-  return pack_u32x2(__float_as_uint(lo), __float_as_uint(hi));
-}
-// acc = a * b + acc, element-wise on two packed fp32 values
-__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint64_t a, uint64_t b) {
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
-}
-__device__ __forceinline__ uint32_t pack_bf16x2(uint64_t packed) {
-  uint32_t lo, hi;
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(packed));
-  return pack_bf16x2(__uint_as_float(lo), __uint_as_float(hi));
 }
 // RN-even conversion to E4M3 with saturation to +-448 (finite).
 __device__ __forceinline__ uint8_t to_e4m3(float v) {

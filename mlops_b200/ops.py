@@ -101,7 +101,7 @@ def check_status(device=None) -> None:
     code, where_block, where, detail = block.tolist()
     if code != 0:
         block.zero_()
-        names = {1: "bounded wait ran out", 2: "malformed offsets or ids", 3: "too many groups"}
+        names = {1: "bounded wait ran out", 2: "malformed offsets or ids"}
         raise NativeError(
             f"device status: {names.get(code, code)} (block {where_block}, where {where}, detail {detail})"
         )
