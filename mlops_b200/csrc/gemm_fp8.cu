@@ -110,12 +110,21 @@ __device__ __forceinline__ TileCoord locate_m_tile(int mt, const int* m_tile_sta
   return c;
 }
 
-template <int BLOCK_N, bool B_MN_MAJOR, int EPI>
+// SPLIT (256-wide tile, plain or combining store): each K block is issued as two N=128
+// halves into the two 128-column halves of its accumulator buffer, each with its own "full"
+// mbarrier and its own hardware barrier for the release.  A half is drained by the four
+// epilogue warps that own its columns, so the retire -> drain -> release -> reissue loop of
+// one half runs beside the multiplication of the other three halves in flight.
+template <int BLOCK_N, bool B_MN_MAJOR, int EPI, bool SPLIT = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const __grid_constant__ CUtensorMap tmap_b, const GemmFp8Params p) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
+  static_assert(!SPLIT || (BLOCK_N == 256 && EPI != 1), "the split issue is for the plain 256-wide tile");
+  constexpr int kHalves = SPLIT ? 2 : 1;  // separately released parts of an accumulator buffer
+  // hardware barrier of (buffer, half); its participants: the warps that drain it and its issuer
+  constexpr uint32_t kRelThreads = SPLIT ? (4 + 1) * 32 : kAccBarrierThreads;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -124,9 +133,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTileBytes);
   uint64_t* full = bars;                    // [kStages]
   uint64_t* empty = bars + kStages;         // [kStages]
-  uint64_t* tfull = bars + 2 * kStages;     // [2]
-  // (bars + 2*kStages + 2, +3 unused: an accumulator buffer is handed back to its issuer on a
-  // hardware barrier, id 1 + buffer, by the eight epilogue warps)
+  uint64_t* tfull = bars + 2 * kStages;     // [2 buffers][2 halves] (one per buffer unless SPLIT)
+  // (an accumulator buffer, or half, is handed back to its issuer on a hardware barrier,
+  // id 1 + buffer * halves + half, by the epilogue warps that drain it)
   uint64_t* drain = bars + 2 * kStages + 4;   // [2] one per issuer
   uint64_t* amax_bar = bars + 2 * kStages + 6;  // [4] row-quarter pairs of the fused SwiGLU epilogue
   uint64_t* sched_full = bars + 2 * kStages + 10;   // [4] ring of tile ids: slot published
@@ -152,8 +161,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(&tfull[0], 1);
-    mbar_init(&tfull[1], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&tfull[i], 1);
     mbar_init(&drain[0], 1);
     mbar_init(&drain[1], 1);
     for (int i = 0; i < 4; ++i) mbar_init(&amax_bar[i], 64);
@@ -298,7 +306,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------ UMMA issuers ------------------------------
     B200_REG_DEC();
     // The whole warp walks the loop (the hardware barrier counts warps); lane 0 issues.
-    constexpr uint32_t idesc = make_idesc(0, 0, 0, B_MN_MAJOR ? 1 : 0, kBlockM, BLOCK_N);
+    constexpr uint32_t idesc = make_idesc(0, 0, 0, B_MN_MAJOR ? 1 : 0, kBlockM, BLOCK_N / kHalves);
     const uint32_t mine = warp == 1 ? 0u : 1u;  // parity of the K blocks (and the buffer) of this warp
     uint32_t it = 0;  // K blocks since the kernel started: stage it % kStages, buffer it & 1
     bool ok = true;
@@ -325,21 +333,27 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // MN-major: 32 K-rows of 128 bytes further.
         constexpr uint64_t kStepA = (uint64_t)(32 >> 4);
         constexpr uint64_t kStepB = (uint64_t)(B_MN_MAJOR ? ((32 * 128) >> 4) : (32 >> 4));
-        const uint32_t d_tmem = tmem_base + mine * BLOCK_N;
-        const uint32_t empty_bar = smem_u32(&empty[s]), tfull_bar = smem_u32(&tfull[mine]);
-        if (it >= 2) {
-          // the buffer holds an earlier K block: its eight readers hand it back here.  An
-          // epilogue warp that unwinds arrives once more, so this cannot wait forever.
-          named_sync(kAccBarrier + mine, kAccBarrierThreads);
-        }
-        if (lane == 0) {
-          tc_fence_after_sync();
-          umma_f8(d_tmem, adesc, bdesc, idesc, 0u);
-          umma_f8(d_tmem, adesc + kStepA, bdesc + kStepB, idesc, 1u);
-          umma_f8(d_tmem, adesc + 2 * kStepA, bdesc + 2 * kStepB, idesc, 1u);
-          umma_f8(d_tmem, adesc + 3 * kStepA, bdesc + 3 * kStepB, idesc, 1u);
-          umma_commit_addr(empty_bar);
-          umma_commit_addr(tfull_bar);
+        const uint32_t empty_bar = smem_u32(&empty[s]);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) {
+          // 128 columns of B further: 128 K-major rows, or one MN-major panel -- 16 KB either way
+          const uint64_t bdesc_h = bdesc + (uint64_t)((h * 128 * kBlockK) >> 4);
+          const uint32_t d_tmem = tmem_base + mine * BLOCK_N + h * 128;
+          const uint32_t tfull_bar = smem_u32(&tfull[mine * kHalves + h]);
+          if (it >= 2) {
+            // this part of the buffer holds an earlier K block: its readers hand it back here.
+            // An epilogue warp that unwinds arrives once more, so this cannot wait forever.
+            named_sync(kAccBarrier + mine * kHalves + h, kRelThreads);
+          }
+          if (lane == 0) {
+            tc_fence_after_sync();
+            umma_f8(d_tmem, adesc, bdesc_h, idesc, 0u);
+            umma_f8(d_tmem, adesc + kStepA, bdesc_h + kStepB, idesc, 1u);
+            umma_f8(d_tmem, adesc + 2 * kStepA, bdesc_h + 2 * kStepB, idesc, 1u);
+            umma_f8(d_tmem, adesc + 3 * kStepA, bdesc_h + 3 * kStepB, idesc, 1u);
+            umma_commit_addr(tfull_bar);
+            if (h == kHalves - 1) umma_commit_addr(empty_bar);
+          }
         }
         // one lane reads the flag so that the warp leaves the loop together (a warp that split
         // here would come back to the hardware barrier with lanes missing)
@@ -438,7 +452,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int buf = ab & 1;
           const uint32_t aph = (ab >> 1) & 1;
           ++ab;
-          if (!mbar_spin_warp(&tfull[buf], aph, abort_flag, p.status, 4)) { ok = false; break; }
+          const int part = SPLIT ? buf * 2 + half : buf;  // what this warp waits for and hands back
+          if (!mbar_spin_warp(&tfull[part], aph, abort_flag, p.status, 4)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N +
                                  (EPI == 1 ? half * 64 : half * kCols);
@@ -453,7 +468,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           auto release = [&]() {
             tc_fence_before_sync();
             __syncwarp();
-            named_arrive(kAccBarrier + buf, kAccBarrierThreads);
+            named_arrive(kAccBarrier + part, kRelThreads);
           };
           uint32_t ra[32], rb[32];
           tmem_ld_32x32(taddr + tcol(0), ra);
@@ -624,8 +639,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     if (!ok) {
       // Unwinding: an issuer may be waiting on a hardware barrier for this warp.
-      named_arrive(kAccBarrier + 0, kAccBarrierThreads);
-      named_arrive(kAccBarrier + 1, kAccBarrierThreads);
+      named_arrive(kAccBarrier + (SPLIT ? half : 0), kRelThreads);
+      named_arrive(kAccBarrier + (SPLIT ? 2 + half : 1), kRelThreads);
     }
   }
 
@@ -652,11 +667,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <int BLOCK_N, bool B_MN, int EPI = 0>
+template <int BLOCK_N, bool B_MN, int EPI = 0, bool SPLIT = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp8Params& p,
                        cudaStream_t stream) {
   using Cfg = GemmCfg<BLOCK_N>;
-  auto kern = grouped_gemm_fp8_kernel<BLOCK_N, B_MN, EPI>;
+  auto kern = grouped_gemm_fp8_kernel<BLOCK_N, B_MN, EPI, SPLIT>;
   // Function attributes are per device; setting one is a cheap host-side call.
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
     return B200MOE_ERR_LAUNCH;
@@ -770,10 +785,21 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
     p.bs_k_stride = nblocks;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (fused) return b_mn_major ? launch_gemm<256, true, 2>(ta, tb, p, s) : launch_gemm<256, false, 2>(ta, tb, p, s);
+  // the 256-wide tile issues each K block in two halves (B200MOE_GEMM_SPLIT=0: in one piece)
+  static const bool split = [] {
+    const char* v = getenv("B200MOE_GEMM_SPLIT");
+    return v == nullptr || v[0] != '0';
+  }();
+  if (fused) {
+    if (split)
+      return b_mn_major ? launch_gemm<256, true, 2, true>(ta, tb, p, s) : launch_gemm<256, false, 2, true>(ta, tb, p, s);
+    return b_mn_major ? launch_gemm<256, true, 2>(ta, tb, p, s) : launch_gemm<256, false, 2>(ta, tb, p, s);
+  }
   if (block_n == 128) {
     return b_mn_major ? launch_gemm<128, true>(ta, tb, p, s) : launch_gemm<128, false>(ta, tb, p, s);
   }
+  if (split)
+    return b_mn_major ? launch_gemm<256, true, 0, true>(ta, tb, p, s) : launch_gemm<256, false, 0, true>(ta, tb, p, s);
   return b_mn_major ? launch_gemm<256, true>(ta, tb, p, s) : launch_gemm<256, false>(ta, tb, p, s);
 }
 
