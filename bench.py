@@ -266,10 +266,17 @@ def gpu_arm(args, cfg):
     if distributed:
         from mlops_b200 import ep as ep_module
 
+        # Group-limited routing with balanced load: experts in contiguous blocks, so a token's
+        # experts sit on few ranks and it is sent once per rank (de-duplicated dispatch).
+        # Skewed popularity (the LoRA workload): experts strided over the ranks, one row per
+        # assignment.
+        dedup = os.environ.get("B200MOE_EP_DEDUP", "1" if cfg["n_group"] > 1 else "0") == "1"
+        expert_map = os.environ.get("B200MOE_EP_MAP", "contiguous" if dedup else "strided")
+
         ep = ep_module.ExpertParallelMoE(
             ep_module.ExpertParallelConfig(hidden=D, experts=E, intermediate=F, top_k=K, routing_mode=cfg["mode"],
                                            n_group=cfg["n_group"], topk_group=cfg["topk_group"],
-                                           routed_scaling=cfg["scaling"], expert_map="strided"),
+                                           routed_scaling=cfg["scaling"], expert_map=expert_map, dedup=dedup),
             dist.group.WORLD, router_weight=router, router_bias=bias, w13=w13, w2=w2, shared=shared,
             device=device, chunks=int(os.environ["B200MOE_EP_CHUNKS"]) if "B200MOE_EP_CHUNKS" in os.environ else None,
             comm_sms=int(os.environ.get("B200MOE_EP_LIMIT_SMS", "0")),
@@ -412,7 +419,8 @@ def gpu_arm(args, cfg):
         "config": {"workload": cfg["name"], "tokens_per_gpu": T, "hidden": D, "experts": E, "intermediate": F,
                    "top_k": K, "routing": cfg["mode"],
                    "router_bias": "N(0, 0.001), balanced load" if bias is not None else None, "shared_expert": bool(cfg["shared"]),
-                   "expert_parallel": world, "expert_map": "strided" if distributed else "local",
+                   "expert_parallel": world, "expert_map": ep.config.expert_map if distributed else "local",
+                   "dedup_dispatch": bool(distributed and ep.config.dedup),
                    "rows_per_rank": per_rank_rows, "weights": "block-FP8 e4m3 128x128, random N(0,0.02)",
                    "activations": "e4m3 1x128 blocks", "weight_grads": "bf16 operands, fp32 sums, bf16 out",
                    "l2": "inputs exceed L2 (no flush needed)" if T * D * 2 > (126 << 20) else "inputs fit L2"},

@@ -41,6 +41,11 @@ class ExpertParallelConfig:
     routed_scaling: float = 1.0
     swiglu_limit: float | None = None
     expert_map: str = "contiguous"  # "contiguous": expert e on rank e // (E/G); "strided": rank e % G
+    # send a token once to every rank that holds any of its experts (with the list of those
+    # experts) instead of once per expert; the receiver replicates.  Pays off when the experts of
+    # a token cluster on few ranks: group-limited routing with a contiguous map (reference:
+    # expert_parallel/quack/runtime.py:106, "dedup")
+    dedup: bool = False
 
     def validate(self, world: int) -> None:
         if self.experts % world:
@@ -83,25 +88,88 @@ class ExchangePlan:
     segment_offsets: torch.Tensor  # int32 [G * E/G + 1]: received rows as [source][local expert]
     recv_rows: int
     send_rows: int
+    # de-duplicated dispatch: token copies instead of rows (None when not used)
+    send_copies: list[int] | None = None
+    recv_copies: list[int] | None = None
 
 
-def make_plans(send_counts: torch.Tensor, group) -> list[ExchangePlan]:
+def copy_mask(keys: torch.Tensor, world: int, local: int) -> torch.Tensor:
+    """`[tokens, world]` bool: the ranks that hold at least one of a token's experts
+    (`keys [tokens, K]` are placement keys, rank = key // local)."""
+    mask = torch.zeros((keys.shape[0], world), dtype=torch.bool, device=keys.device)
+    mask.scatter_(1, torch.div(keys.long(), local, rounding_mode="floor"), True)
+    return mask
+
+
+def build_copies(mask: torch.Tensor, keys: torch.Tensor, weights: torch.Tensor, local: int, copies: int):
+    """The sender's side of a de-duplicated dispatch. One copy per (rank, token) pair of `mask`,
+    ordered by rank, then token. Returns `(token [copies] int32, ids [copies, K] int32,
+    route_weight [copies, K] fp32)`: which token a copy is, and for each of the token's K
+    assignments the local expert on the copy's rank (-1: that assignment lives elsewhere) with its
+    route weight. No host synchronisation: `copies` comes from the plan."""
+    tokens, world = mask.shape
+    device = mask.device
+    flat = mask.t().reshape(-1)  # rank-major
+    slot = torch.where(flat, flat.long().cumsum(0) - 1, copies)  # unused pairs go to a dump slot
+    token_of = torch.empty(copies + 1, dtype=torch.int64, device=device)
+    rank_of = torch.empty(copies + 1, dtype=torch.int64, device=device)
+    token_of.scatter_(0, slot, torch.arange(tokens, device=device).repeat(world))
+    rank_of.scatter_(0, slot, torch.arange(world, device=device).repeat_interleave(tokens))
+    token_of, rank_of = token_of[:copies], rank_of[:copies]
+    key = keys.long()[token_of]  # [copies, K]
+    here = torch.div(key, local, rounding_mode="floor") == rank_of[:, None]
+    ids = torch.where(here, key - rank_of[:, None] * local, -1).to(torch.int32)
+    route_weight = torch.where(here, weights.float()[token_of], 0.0)
+    return token_of.to(torch.int32), ids.contiguous(), route_weight.contiguous()
+
+
+def expand_copies(ids: torch.Tensor, recv_copies, local: int, rows: int, sort=None):
+    """The receiver's side: `ids [copies, K]` (local expert or -1) of the copies received from
+    each rank (`recv_copies[s]` of them from rank s, in token order). Returns `(assignment
+    [rows] int32, segment_offsets int32 [world * local + 1])`: the received assignments as
+    `[source rank][local expert][token]` rows -- exactly the layout and order a row-per-assignment
+    dispatch delivers -- each named by `copy * K + slot`."""
+    if sort is None:
+        from . import ops
+
+        sort = ops.sort_assignments
+    world = len(recv_copies)
+    device = ids.device
+    source = torch.repeat_interleave(torch.arange(world, device=device),
+                                     torch.tensor(recv_copies, device=device), output_size=ids.shape[0])
+    # assignments that live on another rank sort behind every real (source, expert) group
+    key = torch.where(ids >= 0, source[:, None] * local + ids.long(), world * local).to(torch.int32)
+    order, offsets, _slots, _counts = sort(key.contiguous(), world * local + 1)
+    return order[:rows].contiguous(), offsets[: world * local + 1].contiguous()
+
+
+
+def make_plans(send_counts: torch.Tensor, group, copy_counts: torch.Tensor | None = None) -> list[ExchangePlan]:
     """`send_counts [C, E]`: rows per placement key of each of C token chunks held by this rank
-    (any integer dtype, on the group's device). One all-to-all of all the counts and one host
+    (any integer dtype, on the group's device); `copy_counts [C, G]` (optional): token copies per
+    destination rank for a de-duplicated dispatch. One all-to-all of all the counts and one host
     read of the split sizes give one plan per chunk."""
     world = dist.get_world_size(group)
     chunks, experts = send_counts.shape
     local = experts // world
     mine = send_counts.to(torch.int64).view(chunks, world, local).permute(1, 0, 2).contiguous()  # [G, C, El]
+    if copy_counts is not None:  # one more column per (rank, chunk)
+        mine = torch.cat([mine, copy_counts.to(torch.int64).t().reshape(world, chunks, 1)], dim=2).contiguous()
     theirs = torch.empty_like(mine)
     dist.all_to_all_single(theirs, mine, group=group)
-    sizes = torch.stack([mine.sum(2), theirs.sum(2)]).cpu()  # the one device-to-host copy: [2, G, C]
+    sizes = [mine[:, :, :local].sum(2), theirs[:, :, :local].sum(2)]
+    if copy_counts is not None:
+        sizes += [mine[:, :, local], theirs[:, :, local]]
+    sizes = torch.stack(sizes).cpu()  # the one device-to-host copy: [2 or 4, G, C]
     plans = []
     for c in range(chunks):
         send_splits, recv_splits = sizes[0, :, c].tolist(), sizes[1, :, c].tolist()
         offsets = torch.zeros(world * local + 1, dtype=torch.int32, device=send_counts.device)
-        offsets[1:] = theirs[:, c, :].reshape(-1).cumsum(0).to(torch.int32)
-        plans.append(ExchangePlan(send_splits, recv_splits, offsets, int(sum(recv_splits)), int(sum(send_splits))))
+        offsets[1:] = theirs[:, c, :local].reshape(-1).cumsum(0).to(torch.int32)
+        plan = ExchangePlan(send_splits, recv_splits, offsets, int(sum(recv_splits)), int(sum(send_splits)))
+        if copy_counts is not None:
+            plan.send_copies, plan.recv_copies = sizes[2, :, c].tolist(), sizes[3, :, c].tolist()
+        plans.append(plan)
     return plans
 
 
@@ -134,12 +202,16 @@ def make_plan(send_counts: torch.Tensor, group) -> ExchangePlan:
 
 
 def exchange(rows: torch.Tensor, plan: ExchangePlan, group, *, back: bool = False, async_op: bool = False,
-             out: torch.Tensor | None = None):
+             out: torch.Tensor | None = None, copies: bool = False):
     """Dispatch (`back=False`: send my sorted rows, receive the rows of my experts) or return
     (`back=True`: the inverse). Returns `(received, work)`; `work` is None unless `async_op`.
-    `out` (optional) receives the rows instead of a fresh tensor."""
-    send, recv = (plan.recv_splits, plan.send_splits) if back else (plan.send_splits, plan.recv_splits)
-    total = plan.send_rows if back else plan.recv_rows
+    `out` (optional) receives the rows instead of a fresh tensor. `copies`: the rows are the
+    token copies of a de-duplicated dispatch (forward direction only)."""
+    if copies:
+        send, recv, total = plan.send_copies, plan.recv_copies, int(sum(plan.recv_copies))
+    else:
+        send, recv = (plan.recv_splits, plan.send_splits) if back else (plan.send_splits, plan.recv_splits)
+        total = plan.send_rows if back else plan.recv_rows
     received = out if out is not None else torch.empty((total, *rows.shape[1:]), dtype=rows.dtype,
                                                        device=rows.device)
     payload, target = rows, received
@@ -233,7 +305,8 @@ class ExpertParallelMoE:
 
     def report(self):
         return dict(world=self.world, rank=self.rank, local_experts=self.local_experts,
-                    expert_map=self.config.expert_map, transport="nccl all_to_all_single, bf16 rows",
+                    expert_map=self.config.expert_map, dedup=self.config.dedup,
+                    transport="nccl all_to_all_single, bf16 rows",
                     chunks=self.chunks,
                     bytes_moved=self.bytes_moved)
 
@@ -280,21 +353,27 @@ class ExpertParallelMoE:
                 wanted = max(2, min(4, rows_per_expert // 2048))
             chunks = max(1, min(wanted, tokens))
             bounds = [tokens * c // chunks for c in range(chunks + 1)]
+            dedup = cfg.dedup and self.world > 1
             parts = []
             for c in range(chunks):
                 lo, hi = bounds[c], bounds[c + 1]
                 order, _offsets, slots, key_counts = ops.sort_assignments(keys[lo:hi], cfg.experts)
                 parts.append(dict(lo=lo, hi=hi, order=order, slots=slots, key_counts=key_counts))
+                if dedup:
+                    parts[-1]["mask"] = copy_mask(keys[lo:hi], self.world, self.local_experts)
             self._mark("route+sort")
-            plans = make_plans(torch.stack([part["key_counts"] for part in parts]), self.group)
+            plans = make_plans(torch.stack([part["key_counts"] for part in parts]), self.group,
+                               copy_counts=torch.stack([part["mask"].sum(0) for part in parts]) if dedup else None)
             self._mark("plan")
             total = sum(plan.recv_rows for plan in plans)
             self.last_recv_rows = total
             starts = [0]
             for plan in plans:
                 starts.append(starts[-1] + plan.recv_rows)
-            recv_x = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
-            recv_w = torch.empty(total, dtype=torch.float32, device=flat.device)
+            recv_x = recv_w = None
+            if not dedup:
+                recv_x = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
+                recv_w = torch.empty(total, dtype=torch.float32, device=flat.device)
             # what the backward pass reads, all in expert order (within a chunk)
             x_rows = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
             row_w = torch.empty(total, dtype=torch.float32, device=flat.device)
@@ -309,8 +388,22 @@ class ExpertParallelMoE:
 
             def send(c):
                 part = parts[c]
-                rows = ops.dispatch(flat[part["lo"]:part["hi"]], part["order"], cfg.top_k)
-                row_weights = weights[part["lo"]:part["hi"]].reshape(-1)[part["order"].long()].contiguous()
+                lo, hi = part["lo"], part["hi"]
+                if dedup:
+                    # one copy of a token per destination rank, and what to do with it there:
+                    # K (local expert or -1, route weight) pairs, the weights as raw bits
+                    token, copy_ids, copy_w = build_copies(part["mask"], keys[lo:hi], weights[lo:hi],
+                                                           self.local_experts, int(sum(plans[c].send_copies)))
+                    part["copy_token"] = token
+                    rows = ops.dispatch(flat[lo:hi], token, 1)
+                    meta = torch.cat([copy_ids, copy_w.view(torch.int32)], dim=1)
+                    got_rows, wx = exchange(rows, plans[c], self.group, async_op=True, copies=True)
+                    got_meta, ww = exchange(meta, plans[c], self.group, async_op=True, copies=True)
+                    part["recv_copies"], part["recv_meta"] = got_rows, got_meta
+                    self.bytes_moved += rows.numel() * 2
+                    return rows, meta, wx, ww
+                rows = ops.dispatch(flat[lo:hi], part["order"], cfg.top_k)
+                row_weights = weights[lo:hi].reshape(-1)[part["order"].long()].contiguous()
                 _, wx = exchange(rows, plans[c], self.group, async_op=True, out=recv_x[starts[c]:starts[c + 1]])
                 _, ww = exchange(row_weights, plans[c], self.group, async_op=True,
                                  out=recv_w[starts[c]:starts[c + 1]])
@@ -339,8 +432,21 @@ class ExpertParallelMoE:
                 offsets, source = regroup[c]
                 # expert order from here on: gathered by the quantiser, given back in arrival
                 # order by the down projection's store
-                x_q, x_s, _ = ops.quantize_rows(recv_x[rows], gather=source, copy_out=x_rows[rows])
-                row_w[rows] = recv_w[rows][source.long()]
+                if dedup:
+                    # the copies become this rank's assignments: [source][expert][token] rows as a
+                    # row-per-assignment dispatch delivers them, then expert order
+                    part = parts[c]
+                    meta = part.pop("recv_meta")
+                    assignment, _segments = expand_copies(meta[:, :cfg.top_k].contiguous(), plans[c].recv_copies,
+                                                          self.local_experts, plans[c].recv_rows)
+                    pick = assignment[source.long()].contiguous()  # expert-order row -> copy * K + slot
+                    part["pick"] = pick
+                    x_q, x_s, _ = ops.quantize_rows(part.pop("recv_copies"), gather=pick, gather_div=cfg.top_k,
+                                                    copy_out=x_rows[rows])
+                    row_w[rows] = meta[:, cfg.top_k:].contiguous().view(torch.float32).reshape(-1)[pick.long()]
+                else:
+                    x_q, x_s, _ = ops.quantize_rows(recv_x[rows], gather=source, copy_out=x_rows[rows])
+                    row_w[rows] = recv_w[rows][source.long()]
                 if lora is None:
                     ops.grouped_gemm_fp8(x_q, x_s, *self.w13, offsets, out=h13[rows])
                     a_q, a_s, _ = ops.swiglu_quantize(h13[rows], limit=cfg.swiglu_limit)
@@ -394,7 +500,8 @@ class ExpertParallelMoE:
             tokens, width = flat.shape
             total = starts[-1]
             dy = grad_output.reshape_as(flat).contiguous()
-            recv_dy = torch.empty((total, width), dtype=flat.dtype, device=flat.device)
+            dedup = "pick" in parts[0]
+            recv_dy = None if dedup else torch.empty((total, width), dtype=flat.dtype, device=flat.device)
             regroup = saved["regroup"]
             lora = self.lora  # its terms are part of the input gradient whether or not the factors train
             factor_grads = lora is not None and need_lora
@@ -406,8 +513,13 @@ class ExpertParallelMoE:
 
             def send(c):
                 part = parts[c]
-                rows = ops.dispatch(dy[part["lo"]:part["hi"]], part["order"], cfg.top_k)
-                _, work = exchange(rows, plans[c], self.group, async_op=True, out=recv_dy[starts[c]:starts[c + 1]])
+                if dedup:  # the same copies as in the forward pass
+                    rows = ops.dispatch(dy[part["lo"]:part["hi"]], part["copy_token"], 1)
+                    part["recv_dy_copies"], work = exchange(rows, plans[c], self.group, async_op=True, copies=True)
+                else:
+                    rows = ops.dispatch(dy[part["lo"]:part["hi"]], part["order"], cfg.top_k)
+                    _, work = exchange(rows, plans[c], self.group, async_op=True,
+                                       out=recv_dy[starts[c]:starts[c + 1]])
                 self.bytes_moved += rows.numel() * 2
                 return rows, work
 
@@ -437,10 +549,14 @@ class ExpertParallelMoE:
                 count = starts[c + 1] - starts[c]
                 identity = torch.arange(count, dtype=torch.int32, device=flat.device)
                 offsets, source = regroup[c]
-                if keep_rows:
-                    dy_q, dy_s, _ = ops.quantize_rows(recv_dy[rows], gather=source, copy_out=dy_rows[rows])
+                if dedup:
+                    arrived, gather, div = parts[c].pop("recv_dy_copies"), parts[c]["pick"], cfg.top_k
                 else:
-                    dy_q, dy_s = ops.quantize_rows(recv_dy[rows], gather=source)
+                    arrived, gather, div = recv_dy[rows], source, 1
+                if keep_rows:
+                    dy_q, dy_s, _ = ops.quantize_rows(arrived, gather=gather, gather_div=div, copy_out=dy_rows[rows])
+                else:
+                    dy_q, dy_s = ops.quantize_rows(arrived, gather=gather, gather_div=div)
                 r_add = dx_add = None
                 if lora is not None:
                     dy_b2 = ops.lora_project(dy_rows[rows], lora["b2t"], offsets, rank_major=True)

@@ -44,7 +44,8 @@ def main():
     config = ep.ExpertParallelConfig(hidden=width, experts=experts, intermediate=inner, top_k=top_k,
                                      routing_mode=mode, n_group=4 if shared_on else 1,
                                      topk_group=2 if shared_on else 1, routed_scaling=2.5 if shared_on else 1.0,
-                                     expert_map=expert_map)
+                                     expert_map=expert_map,
+                                     dedup=expert_map == "contiguous")  # one case each way
     local = experts // world
     mine = [e for e in range(experts) if int(ep.placement(config, world)[e]) // local == rank]
     mine.sort(key=lambda e: int(ep.placement(config, world)[e]))
