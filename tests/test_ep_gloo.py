@@ -87,6 +87,56 @@ def test_two_ranks_exchange_rows_by_expert_owner(expert_map):
     assert len(results[0]["splits"]) == 2
 
 
+def _dedup_case(rank, world):
+    """De-duplicated dispatch over real collectives: copies and their expert lists travel, the
+    receiver expands them, and what it ends up with equals what the row-per-assignment dispatch
+    of the same tokens delivers (rows and order)."""
+    from mlops_b200 import ep
+    from oracle import moe_oracle as O
+
+    config = ep.ExpertParallelConfig(hidden=128, experts=8, intermediate=128, top_k=3, dedup=True)
+    ep.handshake(config, dist.group.WORLD)
+    local = config.experts // world
+    g = torch.Generator().manual_seed(300 + rank)
+    tokens = 29 + 7 * rank
+    ids = torch.stack([torch.randperm(config.experts, generator=g)[:3] for _ in range(tokens)]).to(torch.int32)
+    weights = torch.rand(tokens, 3, generator=g)
+    x = torch.randn(tokens, 8, generator=g)
+    order, offsets, _slots = O.sort_assignments(ids, config.experts)
+    mask = ep.copy_mask(ids, world, local)
+    plan = ep.make_plans((offsets[1:] - offsets[:-1]).reshape(1, -1), dist.group.WORLD,
+                         copy_counts=mask.sum(0).reshape(1, -1))[0]
+    assert plan.send_copies == mask.sum(0).tolist()
+    # reference: one row per assignment
+    rows = x[order.long() // 3]
+    row_w = weights.reshape(-1)[order.long()]
+    expected_rows, _ = ep.exchange(rows, plan, dist.group.WORLD)
+    expected_w, _ = ep.exchange(row_w, plan, dist.group.WORLD)
+    # de-duplicated
+    token, copy_ids, copy_w = ep.build_copies(mask, ids, weights, local, sum(plan.send_copies))
+    got_rows, _ = ep.exchange(x[token.long()], plan, dist.group.WORLD, copies=True)
+    got_meta, _ = ep.exchange(torch.cat([copy_ids, copy_w.view(torch.int32)], dim=1), plan, dist.group.WORLD,
+                              copies=True)
+
+    def cpu_sort(keys, groups):
+        flat = keys.reshape(-1).long()
+        offs = torch.zeros(groups + 1, dtype=torch.int32)
+        offs[1:] = torch.bincount(flat, minlength=groups).cumsum(0).to(torch.int32)
+        return torch.sort(flat, stable=True).indices.to(torch.int32), offs, None, None
+
+    assignment, segments = ep.expand_copies(got_meta[:, :3].contiguous(), plan.recv_copies, local, plan.recv_rows,
+                                            sort=cpu_sort)
+    assert torch.equal(segments, plan.segment_offsets)
+    assert torch.equal(got_rows[assignment.long() // 3], expected_rows)
+    assert torch.equal(got_meta[:, 3:].contiguous().view(torch.float32).reshape(-1)[assignment.long()], expected_w)
+    return dict(copies=sum(plan.send_copies), rows=plan.send_rows)
+
+
+def test_two_ranks_deduplicated_dispatch_equals_row_per_assignment():
+    results = _run(_dedup_case)
+    assert all(r["copies"] < r["rows"] for r in results)  # fewer rows travel
+
+
 def _mismatch_case(rank, world):
     from mlops_b200 import ep
 
