@@ -377,7 +377,8 @@ def gpu_arm(args, cfg):
         torch.cuda.current_stream().wait_event(uploaded[slot])
         out, grad_x, aux, counts = step(*buffers[slot])
         consumed[slot].record(torch.cuda.current_stream())
-        summary = torch.stack([out.float().sum(), grad_x.float().sum(), aux.float(), counts.float().max()])
+        summary = torch.stack([out.sum(dtype=torch.float32), grad_x.sum(dtype=torch.float32), aux.float(),
+                               counts.float().max()])
         host_result.copy_(summary, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         state["i"] = i + 1
