@@ -132,9 +132,11 @@ def _dedup_case(rank, world):
     return dict(copies=sum(plan.send_copies), rows=plan.send_rows)
 
 
-def test_two_ranks_deduplicated_dispatch_equals_row_per_assignment():
-    results = _run(_dedup_case)
-    assert all(r["copies"] < r["rows"] for r in results)  # fewer rows travel
+@pytest.mark.parametrize("world", [2, 4])
+def test_deduplicated_dispatch_equals_row_per_assignment(world):
+    results = _run(_dedup_case, world=world)
+    assert all(r["copies"] <= r["rows"] for r in results)
+    assert sum(r["copies"] for r in results) < sum(r["rows"] for r in results)  # fewer rows travel
 
 
 def _mismatch_case(rank, world):
