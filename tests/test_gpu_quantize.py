@@ -55,6 +55,22 @@ def test_quantize_rows_bit_exact(rows, width, mode):
     assert torch.equal(q2.cpu().view(U8), q2_ref.view(U8)) and torch.equal(s2.cpu(), s2_ref)
 
 
+def test_quantize_rows_writes_the_gathered_rows_into_a_given_slice():
+    """`copy_out`: the quantiser also writes the bf16 rows it gathered, into a caller's slice
+    (a pitched view of a larger buffer), bit for bit; the E4M3 result does not change."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(90, 384, generator=g).bfloat16().to(DEV)
+    gather = torch.randint(0, 90 * 3, (200,), generator=g).to(torch.int32).to(DEV)
+    q_ref, s_ref = ops.quantize_rows(x, gather=gather, gather_div=3)
+    big = torch.full((260, 384), float("nan"), dtype=torch.bfloat16, device=DEV)
+    q, s, copy = ops.quantize_rows(x, gather=gather, gather_div=3, copy_out=big[30:230])
+    assert copy.data_ptr() == big[30:230].data_ptr()
+    assert torch.equal(big[30:230], x[torch.div(gather, 3, rounding_mode="floor").long()])
+    assert big[:30].isnan().all() and big[230:].isnan().all()
+    assert torch.equal(q.view(U8), q_ref.view(U8)) and torch.equal(s, s_ref)
+
+
 def test_quantize_rows_empty():
     ops = _ops()
     q, s = ops.quantize_rows(torch.zeros(0, 256, dtype=torch.bfloat16, device=DEV))
