@@ -47,6 +47,8 @@ extern "C" {
  * weights fp32 [tokens, top_k] and ids int32 [tokens, top_k], picks in descending
  * selection value, ties to the lowest expert id.  `bias` (fp32 [experts], may be NULL),
  * n_group, topk_group and routed_scaling are read in mode SIGMOID_NOAUX_TC only.
+ * NaN selection values rank above every number (the order of a stable descending sort), so
+ * ids are always K distinct experts in range; the NaN shows in the weights.
  * Limits: experts <= 1024, top_k <= 32, n_group <= 32 when group selection is active.
  * Reference: src/mlops/kernels/moe_router.py:235-344 (`route`).
  */
@@ -85,7 +87,9 @@ int b200moe_sort_assignments_static(const int32_t* ids, long long assignments, i
 
 /*
  * E4M3 quantisation of bf16 rows, optionally gathered: output row r reads input row
- * gather[r] / gather_div (gather may be NULL: row r).  q is [rows, width] bytes with
+ * gather[r] / gather_div (gather may be NULL: row r) of x [src_rows, width]; an index outside
+ * [0, src_rows) is reported in `status` (code 2) and row 0 is read instead.
+ * q is [rows, width] bytes with
  * byte pitch ldq; scale of (row r, block b) is written to
  * scales[r * scale_row_stride + b * scale_block_stride] (block b = columns 128b..128b+127;
  * mode B200MOE_SCALE_ROW writes only b = 0).  width % 8 == 0.  `copy` (optional, 1x128 mode)
@@ -94,10 +98,10 @@ int b200moe_sort_assignments_static(const int32_t* ids, long long assignments, i
  * Reference: src/mlops/kernels/quack_moe/quantize_rows.py:140-207 (`quantize_rows_fp8`,
  * per-row); the 1x128 mode applies the same equations per block.
  */
-int b200moe_quantize_rows(const void* x, long long ldx, const int32_t* gather, int gather_div,
-                          long long rows, int width, void* q, long long ldq, float* scales,
+int b200moe_quantize_rows(const void* x, long long ldx, long long src_rows, const int32_t* gather,
+                          int gather_div, long long rows, int width, void* q, long long ldq, float* scales,
                           long long scale_row_stride, long long scale_block_stride, int mode, void* copy,
-                          long long ldc, void* stream);
+                          long long ldc, int32_t* status, void* stream);
 
 /*
  * SwiGLU of h13 = [gate | up] (bf16 [rows, 2*width]) computed in fp32 and rounded once
@@ -113,18 +117,19 @@ int b200moe_swiglu_quantize(const void* h13, long long ldh, long long rows, int 
 
 /*
  * Routed SwiGLU backward.  r = dy_row @ W2 before the route weight (bf16 [rows, width]),
- * score(row) = route_weights[order[row]].  Outputs (each may be NULL):
+ * score(row) = route_weights[order[row]] (route_weights has n_weights entries; an order entry
+ * outside is reported in `status` and entry 0 is used).  Outputs (each may be NULL):
  *   dscore fp32 [rows] = <r, act>; grad_h13 = dSwiGLU(score * r) as E4M3 + 1x128 scales
  *   ([rows, 2*width], needs width % 128 == 0) and/or bf16; act_scaled = score * act (bf16).
  * Reference: src/mlops/kernels/quack_moe/swiglu_rows.py:292-316
  * (`routed_swiglu_rows_backward`).
  */
 int b200moe_dswiglu_routed(const void* h13, long long ldh, const void* r, long long ldr,
-                           const float* route_weights, const int32_t* order, long long rows, int width,
-                           float* dscore, void* grad_h13_q, long long ldq, float* grad_h13_scales,
-                           long long scale_row_stride, long long scale_block_stride,
+                           const float* route_weights, long long n_weights, const int32_t* order,
+                           long long rows, int width, float* dscore, void* grad_h13_q, long long ldq,
+                           float* grad_h13_scales, long long scale_row_stride, long long scale_block_stride,
                            void* grad_h13_bf16, long long ldg, void* act_scaled, long long lda,
-                           float limit, int limited, void* stream);
+                           float limit, int limited, int32_t* status, void* stream);
 
 /*
  * Weight quantisation: w [experts, out, in] (bf16, or fp32 when src_is_fp32) ->
@@ -153,6 +158,11 @@ int b200moe_quantize_blocks(const void* w, int src_is_fp32, int experts, int out
  * groups <= 1024.  `weights` is the number of weight matrices in b: group g multiplies
  * matrix g % weights (groups must be a multiple of it), so rows that arrive as
  * [source rank][local expert] segments need no regrouping; weights == groups is the plain case.
+ * Tile scheduling: launches on an ordinary stream draw their tiles from a device-side counter
+ * owned by that stream (up to 64 streams per device get one; launches on one stream never
+ * overlap, so a counter is never shared by two running kernels).  Launches into a stream under
+ * capture, into the per-thread default stream, or into a 65th stream assign tiles by CTA index
+ * instead: same results, no shared state, safe under any graph replay.
  * Reference: src/mlops/kernels/block_fp8.py:249-341 (`grouped_block_gemm`) and
  * src/mlops/kernels/quack_moe/block_fp8_gemm.py:1424-1484 (`block_fp8_gemm`,
  * `block_fp8_transposed_gemm`).
@@ -166,7 +176,8 @@ int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
 
 /*
  * b200moe_grouped_gemm_fp8 with a scattered store: d[row_map[r], 0:N] = product[r, 0:N]
- * (row_map: int32 [rows_total], a permutation of the rows that belong to a group).  The
+ * (row_map: int32 [rows_total], a permutation of the rows that belong to a group; an entry
+ * outside [0, rows_total) is reported in `status` and that row is not stored).  The
  * expert-parallel layer multiplies received rows in expert order and gives them back in the
  * [source rank][expert] order the return exchange wants, without a pass of its own.
  * No counterpart in the reference (its transport returns rows through MoonEP's own buffers,
@@ -204,7 +215,8 @@ int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, const float* a
  *   out_f32[row_token[r], 0:N] += row_weight[r] * bf16(product[r, 0:N])
  * (the product rounded to bf16 first, as the stored expert output would be).  out_f32
  * [tokens, N] (pitch ldo floats, a multiple of 4) must hold each token's starting value (zero);
- * row_token / row_weight give, per expert-order row, its token and route weight.  The other
+ * row_token / row_weight give, per expert-order row, its token and route weight (a token outside
+ * [0, tokens) is reported in `status` and its row is not added).  The other
  * arguments are those of b200moe_grouped_gemm_fp8 (tile width 256).  The K contributions of a
  * token arrive in no fixed order: results are not bitwise repeatable, which is why the
  * two-kernel form (b200moe_grouped_gemm_fp8 + b200moe_combine) is the default.
@@ -215,7 +227,7 @@ int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, const float* a
  */
 int b200moe_grouped_gemm_fp8_combine(const void* a, long long lda, const float* a_scale,
                                      long long as_row_stride, long long as_kb_stride, const void* b,
-                                     const float* b_scale, float* out_f32, long long ldo,
+                                     const float* b_scale, float* out_f32, long long ldo, long long tokens,
                                      const int32_t* row_token, const float* row_weight, const void* addend,
                                      long long ldc, const int32_t* offsets, int groups, int weights,
                                      long long rows_total, int N, int K, int b_mn_major, int32_t* status,
@@ -271,18 +283,21 @@ int b200moe_combine(const void* src, long long lds, long long src_rows, const in
                     long long tokens, int width, int top_k, void* stream);
 
 /*
- * dst[r] = src[gather[r] / gather_div], bf16 rows.
+ * dst[r] = src[gather[r] / gather_div], bf16 rows of src [src_rows, width].  An index outside
+ * [0, src_rows) is reported in `status` (code 2) and row 0 is copied instead.
  * Reference: src/mlops/kernels/moe_dispatch.py:122-124 (`dispatch`).
  */
-int b200moe_gather_rows(const void* src, long long lds, const int32_t* gather, int gather_div,
-                        long long rows, int width, void* dst, long long ldd, void* stream);
+int b200moe_gather_rows(const void* src, long long lds, long long src_rows, const int32_t* gather,
+                        int gather_div, long long rows, int width, void* dst, long long ldd,
+                        int32_t* status, void* stream);
 
 /*
  * out[i] = values[slots[i]] for i < n (fp32): a per-sorted-row scalar in assignment order.
+ * values has n_values entries; a slot outside is reported in `status` and entry 0 is read.
  * Reference: src/mlops/providers/moe_common.py:325-329 (route-weight gradient gather).
  */
-int b200moe_gather_scalar(const float* values, const int32_t* slots, long long n, float* out,
-                          void* stream);
+int b200moe_gather_scalar(const float* values, long long n_values, const int32_t* slots, long long n,
+                          float* out, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

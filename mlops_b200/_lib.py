@@ -32,11 +32,11 @@ SIGNATURES = {
     "b200moe_sort_assignments_workspace_bytes": (LL, [LL, I]),
     "b200moe_sort_assignments": (I, [P, LL, I, P, P, P, P, P, P, P]),
     "b200moe_sort_assignments_static": (I, [P, LL, I, P, P, P, P, P, P]),
-    "b200moe_quantize_rows": (I, [P, LL, P, I, LL, I, P, LL, P, LL, LL, I, P, LL, P]),
+    "b200moe_quantize_rows": (I, [P, LL, LL, P, I, LL, I, P, LL, P, LL, LL, I, P, LL, P, P]),
     "b200moe_swiglu_quantize": (I, [P, LL, LL, I, P, LL, P, LL, LL, P, LL, F, I, P]),
     "b200moe_dswiglu_routed": (
         I,
-        [P, LL, P, LL, P, P, LL, I, P, P, LL, P, LL, LL, P, LL, P, LL, F, I, P],
+        [P, LL, P, LL, P, LL, P, LL, I, P, P, LL, P, LL, LL, P, LL, P, LL, F, I, P, P],
     ),
     "b200moe_quantize_blocks": (I, [P, I, I, I, I, P, P, P]),
     "b200moe_grouped_gemm_fp8": (
@@ -53,7 +53,7 @@ SIGNATURES = {
     ),
     "b200moe_grouped_gemm_fp8_combine": (
         I,
-        [P, LL, P, LL, LL, P, P, P, LL, P, P, P, LL, P, I, I, LL, I, I, I, P, P],
+        [P, LL, P, LL, LL, P, P, P, LL, LL, P, P, P, LL, P, I, I, LL, I, I, I, P, P],
     ),
     "b200moe_finish_combine": (I, [P, LL, P, LL, P, LL, LL, I, P]),
     "b200moe_grouped_wgrad_bf16": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, P, P]),
@@ -61,8 +61,8 @@ SIGNATURES = {
     "b200moe_lora_project": (I, [P, LL, P, I, P, I, LL, I, I, P, LL, P]),
     "b200moe_lora_expand": (I, [P, LL, P, I, P, I, LL, I, I, F, P, LL, P]),
     "b200moe_combine": (I, [P, LL, LL, P, P, P, LL, P, LL, LL, I, I, P]),
-    "b200moe_gather_rows": (I, [P, LL, P, I, LL, I, P, LL, P]),
-    "b200moe_gather_scalar": (I, [P, P, LL, P, P]),
+    "b200moe_gather_rows": (I, [P, LL, LL, P, I, LL, I, P, LL, P, P]),
+    "b200moe_gather_scalar": (I, [P, LL, P, LL, P, P, P]),
 }
 
 

@@ -56,21 +56,33 @@ combine_kernel(const __nv_bfloat16* __restrict__ src, long long lds, long long s
 
 // dst[r] = src[gather[r] / gather_div] (bf16 rows), the expert-ordered copy of token rows.
 __global__ void __launch_bounds__(256)
-gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, const int* __restrict__ gather,
-                   int gather_div, long long rows, int D, __nv_bfloat16* __restrict__ dst, long long ldd) {
+gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, long long src_rows,
+                   const int* __restrict__ gather, int gather_div, long long rows, int D,
+                   __nv_bfloat16* __restrict__ dst, long long ldd, int* status) {
   const int lane = threadIdx.x & 31;
   const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= rows) return;
-  const long long s = gather[r] / gather_div;
+  long long s = gather[r] / gather_div;
+  if (s < 0 || s >= src_rows) {  // reported, and row 0 is copied instead of a read out of bounds
+    if (lane == 0) report_error(status, ERR_BAD_OFFSETS, 22, (int)r);
+    s = 0;
+  }
   for (int c = lane * 8; c < D; c += 256)
     *reinterpret_cast<uint4*>(dst + r * ldd + c) = *reinterpret_cast<const uint4*>(src + s * lds + c);
 }
 
 // out[t, k] = values[slots[t, k]]: a per-sorted-row scalar brought back to assignment order.
-__global__ void gather_scalar_kernel(const float* __restrict__ values, const int* __restrict__ slots,
-                                     long long n, float* __restrict__ out) {
+__global__ void gather_scalar_kernel(const float* __restrict__ values, long long n_values,
+                                     const int* __restrict__ slots, long long n, float* __restrict__ out,
+                                     int* status) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) out[i] = values[slots[i]];
+  if (i >= n) return;
+  long long s = slots[i];
+  if (s < 0 || s >= n_values) {
+    report_error(status, ERR_BAD_OFFSETS, 23, (int)i);
+    s = 0;
+  }
+  out[i] = values[s];
 }
 
 // out[t] = bf16(sums[t] + residual[t]): the rounding that ends a combine whose route-weighted
@@ -126,24 +138,26 @@ extern "C" int b200moe_combine(const void* src, long long lds, long long src_row
   return launch_status();
 }
 
-extern "C" int b200moe_gather_rows(const void* src, long long lds, const int32_t* gather, int gather_div,
-                                   long long rows, int width, void* dst, long long ldd, void* stream) {
-  if (!src || !gather || !dst || rows < 0 || width <= 0 || gather_div <= 0) return B200MOE_ERR_ARG;
+extern "C" int b200moe_gather_rows(const void* src, long long lds, long long src_rows, const int32_t* gather,
+                                   int gather_div, long long rows, int width, void* dst, long long ldd,
+                                   int32_t* status, void* stream) {
+  if (!src || !gather || !dst || !status || rows < 0 || width <= 0 || gather_div <= 0) return B200MOE_ERR_ARG;
+  if (rows > 0 && src_rows <= 0) return B200MOE_ERR_ARG;
   if ((width % 8) || (lds % 8) || (ldd % 8) || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15))
     return B200MOE_ERR_ALIGN;
   if (rows == 0) return B200MOE_OK;
   gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(src), lds, gather, gather_div, rows, width,
-      reinterpret_cast<__nv_bfloat16*>(dst), ldd);
+      reinterpret_cast<const __nv_bfloat16*>(src), lds, src_rows, gather, gather_div, rows, width,
+      reinterpret_cast<__nv_bfloat16*>(dst), ldd, status);
   return launch_status();
 }
 
-extern "C" int b200moe_gather_scalar(const float* values, const int32_t* slots, long long n, float* out,
-                                     void* stream) {
-  if (!values || !slots || !out || n < 0) return B200MOE_ERR_ARG;
+extern "C" int b200moe_gather_scalar(const float* values, long long n_values, const int32_t* slots, long long n,
+                                     float* out, int32_t* status, void* stream) {
+  if (!values || !slots || !out || !status || n < 0 || (n > 0 && n_values <= 0)) return B200MOE_ERR_ARG;
   if (n == 0) return B200MOE_OK;
   gather_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      values, slots, n, out);
+      values, n_values, slots, n, out, status);
   return launch_status();
 }
 

@@ -119,6 +119,18 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t cta) 
       : "memory");
 }
 
+// The same arrival with release semantics at cluster scope: the waiter in the other CTA may
+// consume what this thread (and, through the fence before it, its warp) wrote to shared memory
+// with ordinary stores.  Costs about a microsecond; used only where such stores happened.
+__device__ __forceinline__ void mbar_arrive_remote_release(uint64_t* bar, uint32_t cta) {
+  asm volatile(
+      "{\n\t.reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(cta)
+      : "memory");
+}
+
 // Upper bound of any single wait, in SM clock cycles (about two seconds).
 #ifndef B200_WAIT_LIMIT_CYCLES
 #define B200_WAIT_LIMIT_CYCLES (4000000000LL)

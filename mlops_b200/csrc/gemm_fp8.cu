@@ -28,8 +28,8 @@
 #include "common.cuh"
 #include "host_util.h"
 
-#include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 namespace b200 {
 
@@ -42,8 +42,13 @@ constexpr uint32_t kAccBarrier = 1;  // hardware barriers 1, 2: accumulator buff
 constexpr uint32_t kAccBarrierThreads = (8 + 1) * 32;  // eight epilogue warps and the buffer's issuer
 
 // Tile counters of the dynamic scheduler: [slot][0] next tile, [slot][1] CTAs that have finished.
-// A launch takes the next slot (host side, round robin); the last CTA to finish zeroes its slot,
-// so a slot is ready again long before 64 further launches have gone by.
+// A slot belongs to ONE stream of one device (host-side table below): launches on a stream run
+// one after the other, so no two launches that overlap on the GPU ever share a counter, and the
+// last CTA of a launch leaves its slot zeroed for the next launch on that stream.  A launch that
+// cannot be given a slot of its own (more than kSchedSlots streams seen on the device, a stream
+// under capture -- a graph replay runs on whatever stream it is launched into --, or the
+// per-thread default stream, one handle for many streams) gets sched_slot = -1 and strides over
+// the tiles by CTA index instead.
 constexpr int kSchedSlots = 64;
 __device__ int g_tile_counter[kSchedSlots][2];
 
@@ -72,7 +77,8 @@ struct GemmFp8Params {
   const int* row_token;
   const float* row_weight;
   const int* row_map;  // optional: output row r is stored at d[row_map[r]] (NULL: in place)
-  int sched_slot;
+  long long out_rows;  // rows of d (row_map) or of out_f32 (row_token): targets outside are skipped
+  int sched_slot;      // slot of g_tile_counter, or -1: tiles by CTA index
   int* status;
 };
 
@@ -248,8 +254,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       uint32_t it = 0, published = 0;
       bool ok = true;
+      uint32_t drawn = 0;
       auto draw = [&]() {
-        const int t = atomicAdd(&g_tile_counter[p.sched_slot][0], 1);
+        const int t = p.sched_slot >= 0 ? atomicAdd(&g_tile_counter[p.sched_slot][0], 1)
+                                        : (int)(blockIdx.x + (drawn++) * gridDim.x);
         return t < total_tiles ? t : -1;
       };
       auto publish = [&](int t) {
@@ -512,7 +520,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int rows_here = c.rows_valid - q * 32;  // rows of this warp that belong to the group
         // where this lane's row goes: in place, or wherever the caller's map sends it (rows
         // that arrived as [source rank][expert] and were multiplied in expert order go back)
-        const int out_row = (p.row_map != nullptr && lane < rows_here) ? p.row_map[grow] : grow;
+        int out_row = (p.row_map != nullptr && lane < rows_here) ? p.row_map[grow] : grow;
+        if (p.row_map != nullptr && lane < rows_here && (out_row < 0 || out_row >= p.out_rows)) {
+          report_error(p.status, ERR_BAD_OFFSETS, 11, grow);  // a map entry outside d: row not stored
+          out_row = -1;
+        }
 #pragma unroll
         for (int cc = 0; cc < kChunks; ++cc) {
           if (p.addend != nullptr && lane < rows_here) {
@@ -538,8 +550,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // same shared-memory transpose as the plain store).  The K experts of a token
             // arrive in no fixed order, so the sum is not bitwise repeatable: the plain
             // store plus `combine_kernel` is.
-            const int tok = lane < rows_here ? p.row_token[grow] : 0;
+            int tok = lane < rows_here ? p.row_token[grow] : 0;
             const float wgt = lane < rows_here ? p.row_weight[grow] : 0.f;
+            if (tok < 0 || tok >= p.out_rows) {
+              report_error(p.status, ERR_BAD_OFFSETS, 12, grow);  // no such token: row not added
+              tok = -1;
+            }
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
               __syncwarp();
@@ -559,7 +575,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (int pass = 0; pass < 4; ++pass) {
                 const int r = pass * 8 + (lane >> 2);
                 const int tok_r = __shfl_sync(0xffffffffu, tok, r);
-                if (r < rows_here && col + 4 <= p.N) {
+                if (r < rows_here && tok_r >= 0 && col + 4 <= p.N) {
                   const float4 v = *reinterpret_cast<const float4*>(stage + r * kStageRowBytes + piece * 16);
                   atomicAdd(reinterpret_cast<float4*>(p.out_f32 + (long long)tok_r * p.ldo + col), v);
                 }
@@ -585,7 +601,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int pass = 0; pass < 4; ++pass) {
             const int r = pass * 8 + (lane >> 2);
             const int dst_row = __shfl_sync(0xffffffffu, out_row, r);
-            if (r < rows_here && col + 8 <= p.N) {
+            if (r < rows_here && dst_row >= 0 && col + 8 <= p.N) {
               const uint4 v = *reinterpret_cast<const uint4*>(stage + r * kStageRowBytes + piece * 16);
               *reinterpret_cast<uint4*>(p.d + (long long)dst_row * p.ldd + col) = v;
             }
@@ -658,13 +674,37 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   // The thread that drew this CTA's tiles reports the CTA finished; the last one in the grid
   // leaves the slot zeroed for a later launch.
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && p.sched_slot >= 0) {
     const int finished = atomicAdd(&g_tile_counter[p.sched_slot][1], 1);
     if (finished == (int)gridDim.x - 1) {
       g_tile_counter[p.sched_slot][0] = 0;
       g_tile_counter[p.sched_slot][1] = 0;
     }
   }
+}
+
+// The scheduler slot of (current device, stream), or -1 when the launch must not draw its
+// tiles from a shared counter (see g_tile_counter).
+static int sched_slot_of(cudaStream_t stream) {
+  if (stream == cudaStreamPerThread) return -1;
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  static std::mutex lock;
+  static cudaStream_t table[64][kSchedSlots];
+  static int used[64];
+  std::lock_guard<std::mutex> guard(lock);
+  // the legacy default stream has two spellings; both are slot 0's key
+  const cudaStream_t key = (stream == nullptr) ? cudaStreamLegacy : stream;
+  for (int i = 0; i < used[dev]; ++i)
+    if (table[dev][i] == key) return i;
+  if (used[dev] == kSchedSlots) return -1;
+  table[dev][used[dev]] = key;
+  return used[dev]++;
 }
 
 template <int BLOCK_N, bool B_MN, int EPI = 0, bool SPLIT = false>
@@ -688,9 +728,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmF
   const int sms = honour ? sm_count() : sm_count_device();
   if (grid > sms) grid = sms;
   if (grid < 1) grid = 1;
-  static std::atomic<unsigned> next_slot{0};
   GemmFp8Params q = p;
-  q.sched_slot = (int)(next_slot.fetch_add(1) % (unsigned)kSchedSlots);
+  q.sched_slot = sched_slot_of(stream);
   kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, q);
   return launch_status();
 }
@@ -703,14 +742,15 @@ using namespace b200;
 // (out_f32 != NULL).
 static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_scale, long long as_row_stride,
                                  long long as_kb_stride, const void* b, const float* b_scale, void* d,
-                                 long long ldd, float* out_f32, long long ldo, const int32_t* row_token,
+                                 long long ldd, float* out_f32, long long ldo, long long tokens,
+                                 const int32_t* row_token,
                                  const float* row_weight, const int32_t* row_map, const void* addend,
                                  long long ldc, const int32_t* offsets, int groups, int weights,
                                  long long rows_total, int N, int K, int b_mn_major, int block_n,
                                  int32_t* status, void* stream) {
   const bool fused = out_f32 != nullptr;
   if (!a || !a_scale || !b || !b_scale || !offsets || !status) return B200MOE_ERR_ARG;
-  if (fused ? (!row_token || !row_weight || d != nullptr) : !d) return B200MOE_ERR_ARG;
+  if (fused ? (!row_token || !row_weight || d != nullptr || tokens <= 0) : !d) return B200MOE_ERR_ARG;
   if (fused && (block_n != 256 || (ldo % 4) || ((uintptr_t)out_f32 & 15) || (N % 4))) return B200MOE_ERR_ALIGN;
   if (groups <= 0 || N <= 0 || K <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
   if (weights <= 0 || groups % weights != 0) return B200MOE_ERR_ARG;
@@ -759,6 +799,7 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
   p.row_token = row_token;
   p.row_weight = row_weight;
   p.row_map = row_map;
+  p.out_rows = fused ? tokens : rows_total;
   p.status = status;
   if (!b_mn_major) {
     // B is [groups, N, K], K contiguous; scales [groups, ceil(N/128), ceil(K/128)].
@@ -810,7 +851,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const floa
                                         long long rows_total, int N, int K, int b_mn_major, int block_n,
                                         int32_t* status, void* stream) {
   if (!d) return B200MOE_ERR_ARG;
-  return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, d, ldd, nullptr, 0,
+  return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, d, ldd, nullptr, 0, 0,
                                nullptr, nullptr, nullptr, addend, ldc, offsets, groups, weights, rows_total, N, K,
                                b_mn_major, block_n, status, stream);
 }
@@ -825,24 +866,25 @@ extern "C" int b200moe_grouped_gemm_fp8_scatter(const void* a, long long lda, co
                                                 long long rows_total, int N, int K, int b_mn_major, int block_n,
                                                 int32_t* status, void* stream) {
   if (!d || !row_map) return B200MOE_ERR_ARG;
-  return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, d, ldd, nullptr, 0,
+  return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, d, ldd, nullptr, 0, 0,
                                nullptr, nullptr, row_map, addend, ldc, offsets, groups, weights, rows_total, N, K,
                                b_mn_major, block_n, status, stream);
 }
 
 // The down projection with the un-permute / combine fused into its store:
 //   out_f32[row_token[r], :] += row_weight[r] * bf16(sum_k ... [r, :])   (16-byte fp32 atomics)
-// out_f32 must hold the starting value of every token row (zero, or the residual).
+// out_f32 [tokens, N] must hold the starting value of every token row (zero, or the residual).
 extern "C" int b200moe_grouped_gemm_fp8_combine(const void* a, long long lda, const float* a_scale,
                                                 long long as_row_stride, long long as_kb_stride, const void* b,
                                                 const float* b_scale, float* out_f32, long long ldo,
-                                                const int32_t* row_token, const float* row_weight,
+                                                long long tokens, const int32_t* row_token,
+                                                const float* row_weight,
                                                 const void* addend, long long ldc, const int32_t* offsets,
                                                 int groups, int weights, long long rows_total, int N, int K,
                                                 int b_mn_major, int32_t* status, void* stream) {
   if (!out_f32) return B200MOE_ERR_ARG;
   return grouped_gemm_fp8_impl(a, lda, a_scale, as_row_stride, as_kb_stride, b, b_scale, nullptr, 0, out_f32, ldo,
-                               row_token, row_weight, nullptr, addend, ldc, offsets, groups, weights, rows_total,
+                               tokens, row_token, row_weight, nullptr, addend, ldc, offsets, groups, weights, rows_total,
                                N, K, b_mn_major, 256, status, stream);
 }
 
@@ -915,6 +957,7 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.row_token = nullptr;
   p.row_weight = nullptr;
   p.row_map = nullptr;
+  p.out_rows = rows_total;
   p.status = status;
   return launch_gemm<256, false, 1>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }

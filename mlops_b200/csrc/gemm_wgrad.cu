@@ -5,8 +5,8 @@
 // Both operands are token-major matrices, so the contraction (token) axis is the slow
 // axis of both: the tiles are loaded by TMA as K-rows of 128 bytes and handed to
 // tcgen05.mma as MN-major operands.  The K extent of a group is arbitrary; the rows of
-// the last K block that lie past the group's end are zeroed in the A tile before the
-// MMAs are issued, so the neighbouring group's rows contribute nothing.  Sums are fp32
+// the last K block that lie past the group's end are zeroed in both operand tiles before the
+// MMAs are issued, so the neighbouring group's rows contribute nothing (not even a NaN).  Sums are fp32
 // for the whole K loop (one TMEM accumulator per tile, two buffers so the epilogue of a
 // tile overlaps the MMAs of the next) and are written at the requested dtype; a group
 // without rows gets exact zeros (reference: src/mlops/kernels/moe_grouped_gemm.py:120-174,
@@ -202,10 +202,14 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
           if (!mbar_wait_warp(&full[s], ph, abort_flag, p.status, 22)) { ok = false; break; }
           const int valid = hi - lo - kb * kWgBlockK;
           if (valid < kWgBlockK) {
-            // rows [valid, 64) of both A panels: 128 bytes each, 16 bytes per lane-step
+            // rows [valid, 64) of every panel of BOTH operands: 128 bytes each, 16 bytes per
+            // lane-step.  (Zeroing one operand would leave 0 x Inf = NaN when the next group's
+            // rows hold an Inf or a NaN: groups must stay isolated.)
             const int nbytes = (kWgBlockK - valid) * 128;
-            for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl) {
-              uint8_t* base = sA + s * kWgABytes + pnl * kWgPanelBytes + valid * 128;
+            for (int pnl = 0; pnl < kWgBlockM / 64 + kWgBlockN / 64; ++pnl) {
+              uint8_t* base = (pnl < kWgBlockM / 64 ? sA + s * kWgABytes + pnl * kWgPanelBytes
+                                                    : sB + s * kWgBBytes + (pnl - kWgBlockM / 64) * kWgPanelBytes) +
+                              valid * 128;
               for (int o = lane * 16; o < nbytes; o += 32 * 16)
                 *reinterpret_cast<uint4*>(base + o) = make_uint4(0, 0, 0, 0);
             }
@@ -460,18 +464,24 @@ grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __gr
           if (!mbar_wait_warp(&landed[s], ph, abort_flag, p.status, 32)) { ok = false; break; }
           const int valid = hi - lo - kb * kWgBlockK;
           if (valid < kWgBlockK) {
+            // both operands (see the single-CTA kernel): this CTA's two G and two X panels
             const int nbytes = (kWgBlockK - valid) * 128;
-            for (int pnl = 0; pnl < 2; ++pnl) {
-              uint8_t* base = sA + s * kPairABytes + pnl * kWgPanelBytes + valid * 128;
+            for (int pnl = 0; pnl < 4; ++pnl) {
+              uint8_t* base = (pnl < 2 ? sA + s * kPairABytes + pnl * kWgPanelBytes
+                                       : sB + s * kPairBBytes + (pnl - 2) * kWgPanelBytes) + valid * 128;
               for (int o = lane * 16; o < nbytes; o += 32 * 16)
                 *reinterpret_cast<uint4*>(base + o) = make_uint4(0, 0, 0, 0);
             }
             fence_proxy_async_smem();
           }
           __syncwarp();
-          // The zeroed rows were made visible to the async proxy by the fence above; the
-          // arrival itself needs no cluster-scope release (which costs about a microsecond).
-          if (lane == 0) mbar_arrive_remote(&ready[s], 0);
+          // A stage that was only written by TMA needs no release from this thread.  One whose
+          // tail rows this warp zeroed is published with a cluster-scope release, so the leader's
+          // MMA issue is ordered after those stores (one K block per group and segment).
+          if (lane == 0) {
+            if (valid < kWgBlockK) mbar_arrive_remote_release(&ready[s], 0);
+            else mbar_arrive_remote(&ready[s], 0);
+          }
         }
       }
     }

@@ -46,14 +46,18 @@ __device__ __forceinline__ uint4 pack8_bf16(const float (&v)[8]) {
 
 // mode 0: one scale per 128-column block.  mode 1: one scale per row (two passes).
 __global__ void __launch_bounds__(kRowWarps * 32)
-quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ gather,
-                     int gather_div, long long rows, int D, uint8_t* __restrict__ q, long long ldq,
-                     float* __restrict__ scales, long long s_row, long long s_kb, int mode,
-                     __nv_bfloat16* __restrict__ copy, long long ldc) {
+quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, long long src_rows,
+                     const int* __restrict__ gather, int gather_div, long long rows, int D,
+                     uint8_t* __restrict__ q, long long ldq, float* __restrict__ scales, long long s_row,
+                     long long s_kb, int mode, __nv_bfloat16* __restrict__ copy, long long ldc, int* status) {
   const int lane = threadIdx.x & 31;
   const long long r = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (r >= rows) return;
-  const long long src = gather != nullptr ? (long long)(gather[r] / gather_div) : r;
+  long long src = gather != nullptr ? (long long)(gather[r] / gather_div) : r;
+  if (src < 0 || src >= src_rows) {  // a bad index is reported and reads row 0, never out of bounds
+    if (lane == 0) report_error(status, ERR_BAD_OFFSETS, 20, (int)r);
+    src = 0;
+  }
   const __nv_bfloat16* xr = x + src * ldx;
   uint8_t* qr = q + r * ldq;
   if (mode == 0) {
@@ -156,16 +160,21 @@ swiglu_quant_kernel(const __nv_bfloat16* __restrict__ h13, long long ldh, long l
 __global__ void __launch_bounds__(kRowWarps * 32)
 dswiglu_routed_kernel(const __nv_bfloat16* __restrict__ h13, long long ldh,
                       const __nv_bfloat16* __restrict__ rmat, long long ldr,
-                      const float* __restrict__ route_weights, const int* __restrict__ order,
-                      long long rows, int F, float* __restrict__ dscore,
+                      const float* __restrict__ route_weights, long long n_weights,
+                      const int* __restrict__ order, long long rows, int F, float* __restrict__ dscore,
                       uint8_t* __restrict__ gh_q, long long ldq, float* __restrict__ gh_scales,
                       long long s_row, long long s_kb, __nv_bfloat16* __restrict__ gh_bf16,
                       long long ldg, __nv_bfloat16* __restrict__ act_scaled, long long lda, float limit,
-                      int limited) {
+                      int limited, int* status) {
   const int lane = threadIdx.x & 31;
   const long long r = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (r >= rows) return;
-  const float score = route_weights[order[r]];
+  long long which = order[r];
+  if (which < 0 || which >= n_weights) {
+    if (lane == 0) report_error(status, ERR_BAD_OFFSETS, 21, (int)r);
+    which = 0;
+  }
+  const float score = route_weights[which];
   const __nv_bfloat16* hr = h13 + r * ldh;
   const __nv_bfloat16* rr = rmat + r * ldr;
   float dot = 0.f;
@@ -281,20 +290,21 @@ using namespace b200;
 
 static inline unsigned row_grid(long long rows) { return (unsigned)((rows + kRowWarps - 1) / kRowWarps); }
 
-extern "C" int b200moe_quantize_rows(const void* x, long long ldx, const int32_t* gather, int gather_div,
-                                     long long rows, int width, void* q, long long ldq, float* scales,
-                                     long long scale_row_stride, long long scale_block_stride, int mode,
-                                     void* copy, long long ldc, void* stream) {
-  if (!x || !q || !scales || rows < 0 || width <= 0 || (mode != 0 && mode != 1)) return B200MOE_ERR_ARG;
+extern "C" int b200moe_quantize_rows(const void* x, long long ldx, long long src_rows, const int32_t* gather,
+                                     int gather_div, long long rows, int width, void* q, long long ldq,
+                                     float* scales, long long scale_row_stride, long long scale_block_stride,
+                                     int mode, void* copy, long long ldc, int32_t* status, void* stream) {
+  if (!x || !q || !scales || !status || rows < 0 || width <= 0 || (mode != 0 && mode != 1)) return B200MOE_ERR_ARG;
+  if (rows > 0 && (src_rows <= 0 || (gather == nullptr && src_rows < rows))) return B200MOE_ERR_ARG;
   if (copy != nullptr && (mode != 0 || (ldc % 8) || ((uintptr_t)copy & 15))) return B200MOE_ERR_ARG;
   if (gather != nullptr && gather_div <= 0) return B200MOE_ERR_ARG;
   if ((width % 8) || (ldx % 8) || (ldq % 8) || ((uintptr_t)x & 15) || ((uintptr_t)q & 7))
     return B200MOE_ERR_ALIGN;
   if (rows == 0) return B200MOE_OK;
   quantize_rows_kernel<<<row_grid(rows), kRowWarps * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), ldx, gather, gather_div > 0 ? gather_div : 1, rows, width,
-      reinterpret_cast<uint8_t*>(q), ldq, scales, scale_row_stride, scale_block_stride, mode,
-      reinterpret_cast<__nv_bfloat16*>(copy), ldc);
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, src_rows, gather, gather_div > 0 ? gather_div : 1, rows,
+      width, reinterpret_cast<uint8_t*>(q), ldq, scales, scale_row_stride, scale_block_stride, mode,
+      reinterpret_cast<__nv_bfloat16*>(copy), ldc, status);
   return launch_status();
 }
 
@@ -316,13 +326,14 @@ extern "C" int b200moe_swiglu_quantize(const void* h13, long long ldh, long long
 }
 
 extern "C" int b200moe_dswiglu_routed(const void* h13, long long ldh, const void* r, long long ldr,
-                                      const float* route_weights, const int32_t* order, long long rows,
-                                      int width, float* dscore, void* grad_h13_q, long long ldq,
+                                      const float* route_weights, long long n_weights, const int32_t* order,
+                                      long long rows, int width, float* dscore, void* grad_h13_q, long long ldq,
                                       float* grad_h13_scales, long long scale_row_stride,
                                       long long scale_block_stride, void* grad_h13_bf16, long long ldg,
                                       void* act_scaled, long long lda, float limit, int limited,
-                                      void* stream) {
-  if (!h13 || !r || !route_weights || !order || rows < 0 || width <= 0) return B200MOE_ERR_ARG;
+                                      int32_t* status, void* stream) {
+  if (!h13 || !r || !route_weights || !order || !status || rows < 0 || width <= 0) return B200MOE_ERR_ARG;
+  if (rows > 0 && n_weights <= 0) return B200MOE_ERR_ARG;
   if (grad_h13_q && !grad_h13_scales) return B200MOE_ERR_ARG;
   if ((width % 8) || (ldh % 8) || (ldr % 8) || (ldq % 8) || (ldg % 8) || (lda % 8)) return B200MOE_ERR_ALIGN;
   if (((uintptr_t)h13 & 15) || ((uintptr_t)r & 15) || ((uintptr_t)grad_h13_q & 7) ||
@@ -331,9 +342,9 @@ extern "C" int b200moe_dswiglu_routed(const void* h13, long long ldh, const void
   if (rows == 0) return B200MOE_OK;
   dswiglu_routed_kernel<<<row_grid(rows), kRowWarps * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(h13), ldh, reinterpret_cast<const __nv_bfloat16*>(r), ldr,
-      route_weights, order, rows, width, dscore, reinterpret_cast<uint8_t*>(grad_h13_q), ldq, grad_h13_scales,
-      scale_row_stride, scale_block_stride, reinterpret_cast<__nv_bfloat16*>(grad_h13_bf16), ldg,
-      reinterpret_cast<__nv_bfloat16*>(act_scaled), lda, limit, limited);
+      route_weights, n_weights, order, rows, width, dscore, reinterpret_cast<uint8_t*>(grad_h13_q), ldq,
+      grad_h13_scales, scale_row_stride, scale_block_stride, reinterpret_cast<__nv_bfloat16*>(grad_h13_bf16), ldg,
+      reinterpret_cast<__nv_bfloat16*>(act_scaled), lda, limit, limited, status);
   return launch_status();
 }
 

@@ -33,9 +33,21 @@ struct Cand {
   float s;   // payload: the value the route weight is computed from
 };
 
+// The order of a stable descending torch.sort: NaN ranks above every number (and NaNs
+// among themselves by index), equal values go to the lower expert id.  A row of NaN logits
+// therefore still yields K distinct in-range ids, as the reference's sort does; the NaN
+// shows up in the route weights and the output, never in an index.
+__device__ __forceinline__ bool value_above(float v, float v2) {
+  const bool n1 = v != v, n2 = v2 != v2;
+  return (n1 || n2) ? (n1 && !n2) : (v > v2);
+}
 __device__ __forceinline__ bool better(float v, int e, float v2, int e2) {
+  const bool n1 = v != v, n2 = v2 != v2;
+  if (n1 || n2) return n1 && (!n2 || e < e2);
   return (v > v2) || (v == v2 && e < e2);
 }
+__device__ __forceinline__ float max_nan_high(float a, float b) { return value_above(b, a) ? b : a; }
+__device__ __forceinline__ float min_nan_high(float a, float b) { return value_above(b, a) ? a : b; }
 
 __device__ __forceinline__ Cand warp_argmax(Cand c) {
 #pragma unroll
@@ -89,15 +101,15 @@ route_topk_kernel(const float* __restrict__ logits, long long ld, int T, int E, 
           const int e = j * 32 + lane;
           if (e >= lo && e < hi) {
             const float v = sel[j];
-            if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
+            if (value_above(v, m1)) { m2 = m1; m1 = v; } else if (value_above(v, m2)) { m2 = v; }
           }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
           const float b1 = __shfl_xor_sync(0xffffffffu, m1, o);
           const float b2 = __shfl_xor_sync(0xffffffffu, m2, o);
-          const float n1 = fmaxf(m1, b1);
-          const float n2 = fmaxf(fminf(m1, b1), fmaxf(m2, b2));
+          const float n1 = max_nan_high(m1, b1);
+          const float n2 = max_nan_high(min_nan_high(m1, b1), max_nan_high(m2, b2));
           m1 = n1;
           m2 = n2;
         }
@@ -129,6 +141,25 @@ route_topk_kernel(const float* __restrict__ logits, long long ld, int T, int E, 
     for (int j = 0; j < EPL; ++j) {
       sel[j] = x[j];
       pay[j] = x[j];
+    }
+    if (mode == 1) {
+      // softmax_then_topk sorts probabilities.  A NaN, a +inf, or nothing but -inf in the row
+      // makes every probability NaN, and a stable sort of equal keys keeps index order.
+      float mx = NEG_INF;
+      bool odd = false;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        if (j * 32 + lane < E) {
+          odd = odd || (x[j] != x[j]);
+          mx = fmaxf(mx, x[j]);
+        }
+      }
+      mx = warp_max(mx);
+      odd = __any_sync(0xffffffffu, odd) || mx == -NEG_INF || mx == NEG_INF;
+      if (odd) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) sel[j] = __int_as_float(0x7fc00000);
+      }
     }
   }
 
@@ -190,6 +221,11 @@ route_topk_kernel(const float* __restrict__ logits, long long ld, int T, int E, 
 // ---------------------------------------------------------------------------
 // sort_assignments
 // ---------------------------------------------------------------------------
+// An id outside [0, E) is reported in the status block and sorted as the nearest valid
+// expert, so `order` and `slots` are always complete permutations: the kernels that index
+// with them never see an unwritten entry.
+__device__ __forceinline__ int clamp_id(int e, int E) { return e < 0 ? 0 : (e >= E ? E - 1 : e); }
+
 __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(const int* __restrict__ ids, int R, int E, int* __restrict__ chunk_hist, int* status) {
   extern __shared__ int hist[];
@@ -199,9 +235,12 @@ sort_hist_kernel(const int* __restrict__ ids, int R, int E, int* __restrict__ ch
   for (int i = threadIdx.x; i < kSortChunk; i += kSortThreads) {
     const int idx = base + i;
     if (idx < R) {
-      const int e = ids[idx];
-      if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
-      else report_error(status, ERR_BAD_OFFSETS, 10, idx);
+      int e = ids[idx];
+      if (e < 0 || e >= E) {
+        report_error(status, ERR_BAD_OFFSETS, 10, idx);
+        e = clamp_id(e, E);
+      }
+      atomicAdd(&hist[e], 1);
     }
   }
   __syncthreads();
@@ -263,8 +302,7 @@ sort_scatter_kernel(const int* __restrict__ ids, int R, int E, const int* __rest
   for (int i = lane; i < kPerWarp; i += 32) {
     const int idx = wbase + i;
     if (idx < R) {
-      const int e = ids[idx];
-      if (e >= 0 && e < E) atomicAdd(&mine[e], 1);
+      atomicAdd(&mine[clamp_id(ids[idx], E)], 1);
     }
   }
   __syncthreads();
@@ -280,10 +318,7 @@ sort_scatter_kernel(const int* __restrict__ ids, int R, int E, const int* __rest
   for (int i = lane; i < kPerWarp; i += 32) {
     const int idx = wbase + i;
     int e = -1;
-    if (idx < R) {
-      e = ids[idx];
-      if (e < 0 || e >= E) e = -1;
-    }
+    if (idx < R) e = clamp_id(ids[idx], E);
     const uint32_t peers = __match_any_sync(0xffffffffu, e);
     const int rank = __popc(peers & ((1u << lane) - 1u));
     int pos = 0;

@@ -195,6 +195,10 @@ def forward_routed(
             route_weights = route_weights.float().contiguous()
             route_ids = route_ids.to(torch.int32).contiguous()
         order, offsets, slots, counts = ops.sort_assignments(route_ids, experts)
+        if route is not None:
+            # the sort reported ids outside [0, experts) and placed them on the nearest expert;
+            # the residual handed to the statistics and to the backward pass says the same
+            route_ids = route_ids.clamp(0, experts - 1)
         x_q, x_s = ops.quantize_rows(h2_flat, gather=order, gather_div=int(top_k))
         if fuse_swiglu and w2_data.shape[2] % 128 == 0:
             h13, a_q, a_s = ops.grouped_gemm_fp8_swiglu(x_q, x_s, w13_data, w13_scale, offsets, limit=swiglu_limit)

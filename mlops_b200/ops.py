@@ -10,6 +10,8 @@ Names follow the reference's raw kernel functions (`route`, `sort_assignments`,
 
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from ._lib import NativeError, check, lib
@@ -48,6 +50,25 @@ class _Timed:
             self.stop.record()
             GEMM_TIMINGS.append((self.start, self.stop, self.kind, self.flops))
         return False
+
+
+def _on_tensor_device(fn):
+    """Runs `fn` with the device of its first CUDA tensor argument current, so the kernels are
+    launched on that device and on ITS current stream whatever device the caller had selected
+    (a model moved with `.to("cuda:1")` while cuda:0 is current). The library launches on the
+    current device; the wrappers therefore never rely on the caller having set it."""
+
+    @functools.wraps(fn)
+    def guarded(*args, **kwargs):
+        for value in (*args, *kwargs.values()):
+            if isinstance(value, torch.Tensor) and value.is_cuda:
+                if value.device.index == torch.cuda.current_device():
+                    break
+                with torch.cuda.device(value.device):
+                    return fn(*args, **kwargs)
+        return fn(*args, **kwargs)
+
+    return guarded
 
 
 def set_cta_limit(ctas: int) -> None:
@@ -108,6 +129,7 @@ def check_status(device=None) -> None:
 
 
 # ----------------------------------------------------------------------------- routing
+@_on_tensor_device
 def route_topk(logits, top_k, mode, *, bias=None, n_group=1, topk_group=1, routed_scaling=1.0):
     """(weights fp32 [T,K], ids int32 [T,K]) of fp32 logits [T,E]."""
     _need_cuda(logits, bias)
@@ -130,6 +152,7 @@ def route_topk(logits, top_k, mode, *, bias=None, n_group=1, topk_group=1, route
     return weights, ids
 
 
+@_on_tensor_device
 def sort_assignments(route_ids, experts):
     """(order int32 [R], offsets int32 [E+1], slots int32 [T,K], counts int64 [E])."""
     _need_cuda(route_ids)
@@ -155,6 +178,7 @@ def sort_assignments(route_ids, experts):
     return order, offsets, slots.view(route_ids.shape), counts
 
 
+@_on_tensor_device
 def sort_assignments_static(route_ids, experts, order, offsets, slots, counts):
     """`sort_assignments` into caller-provided outputs, using the library's built-in scratch
     instead of a workspace: for callers that cannot allocate (all device memory owned by their
@@ -182,6 +206,7 @@ def _scale_buffer(rows, blocks, device):
     return torch.empty((blocks, max(rows, 1)), dtype=torch.float32, device=device)[:, :rows].t()
 
 
+@_on_tensor_device
 def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False, copy_out=None):
     """E4M3 rows and fp32 scales of bf16 `x [T, D]`; output row r reads input row
     `gather[r] // gather_div`. Returns (q [R, D] float8_e4m3fn, scales [R, blocks]); with
@@ -206,9 +231,10 @@ def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False
         return (q, scales, copy) if with_copy else (q, scales)
     check(
         lib.b200moe_quantize_rows(
-            x.data_ptr(), x.stride(0), _ptr(gather), int(gather_div), rows, width, q.data_ptr(),
+            x.data_ptr(), x.stride(0), x.shape[0], _ptr(gather), int(gather_div), rows, width, q.data_ptr(),
             q.stride(0), scales.data_ptr(), scales.stride(0), scales.stride(1),
-            0 if mode == "1x128" else 1, _ptr(copy), width if copy is None else copy.stride(0), _stream(),
+            0 if mode == "1x128" else 1, _ptr(copy), width if copy is None else copy.stride(0),
+            status_block(x.device).data_ptr(), _stream(),
         ),
         "quantize_rows",
     )
@@ -216,6 +242,7 @@ def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False
     return (q, scales, copy) if with_copy else (q, scales)
 
 
+@_on_tensor_device
 def swiglu_quantize(h13, *, limit=None, quantized=True, rounded=False):
     """SwiGLU of h13 = [gate | up]. Returns (act_q, scales, act_bf16); entries not asked
     for are None."""
@@ -244,6 +271,7 @@ def swiglu_quantize(h13, *, limit=None, quantized=True, rounded=False):
     return act_q, scales, act
 
 
+@_on_tensor_device
 def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, rounded=False,
                    scaled_activation=False, rounded_out=None, scaled_out=None):
     """One pass over h13 and r: returns (dscore [rows] fp32, grad_h13_q, grad_h13_scales,
@@ -267,10 +295,11 @@ def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, 
     check(
         lib.b200moe_dswiglu_routed(
             h13.data_ptr(), h13.stride(0), r.data_ptr(), r.stride(0), weights_flat.data_ptr(),
-            order.data_ptr(), rows, width, dscore.data_ptr(), _ptr(gq), two_f, _ptr(gs),
+            weights_flat.numel(), order.data_ptr(), rows, width, dscore.data_ptr(), _ptr(gq), two_f, _ptr(gs),
             0 if gs is None else gs.stride(0), 0 if gs is None else gs.stride(1), _ptr(gb),
-            two_f if gb is None else gb.stride(0), _ptr(a_s), width if a_s is None else a_s.stride(0), 0.0 if limit is None else float(limit), 0 if limit is None else 1,
-            _stream(),
+            two_f if gb is None else gb.stride(0), _ptr(a_s), width if a_s is None else a_s.stride(0),
+            0.0 if limit is None else float(limit), 0 if limit is None else 1,
+            status_block(device).data_ptr(), _stream(),
         ),
         "dswiglu_routed",
     )
@@ -278,6 +307,7 @@ def dswiglu_routed(h13, r, route_weights, order, *, limit=None, quantized=True, 
     return dscore, gq, gs, gb, a_s
 
 
+@_on_tensor_device
 def quantize_blocks(weight):
     """(data E4M3 [E,out,in], scale fp32 [E, ceil(out/128), ceil(in/128)]) of a bf16 or
     fp32 weight."""
@@ -304,6 +334,7 @@ def quantize_blocks(weight):
 
 
 # ------------------------------------------------------------------------------- GEMMs
+@_on_tensor_device
 def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, block_n=256, out=None,
                      addend=None, row_map=None):
     """bf16 `[rows, N]` of the grouped block-FP8 product. `b_q` is `[G, N, K]`
@@ -362,6 +393,7 @@ def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False, b
     return out
 
 
+@_on_tensor_device
 def grouped_gemm_fp8_combine(a_q, a_scale, b_q, b_scale, offsets, order, route_weights, tokens, *,
                              residual=None, addend=None):
     """Down projection with the combine fused into its store: returns bf16 `[tokens, N]` =
@@ -394,7 +426,7 @@ def grouped_gemm_fp8_combine(a_q, a_scale, b_q, b_scale, offsets, order, route_w
             check(
                 lib.b200moe_grouped_gemm_fp8_combine(
                     a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0), as_kb,
-                    b_q.data_ptr(), b_scale.data_ptr(), sums.data_ptr(), sums.stride(0),
+                    b_q.data_ptr(), b_scale.data_ptr(), sums.data_ptr(), sums.stride(0), tokens,
                     row_token.data_ptr(), row_weight.data_ptr(), _ptr(addend),
                     0 if addend is None else addend.stride(0), offsets.data_ptr(), groups, weights, rows, n, k,
                     0, status_block(device).data_ptr(), _stream(),
@@ -414,6 +446,7 @@ def grouped_gemm_fp8_combine(a_q, a_scale, b_q, b_scale, offsets, order, route_w
     return out
 
 
+@_on_tensor_device
 def grouped_gemm_fp8_swiglu(a_q, a_scale, w13_q, w13_scale, offsets, *, limit=None, out=None):
     """Up projection with the SwiGLU epilogue fused. Returns `(h13 bf16 [rows, 2F], act_q E4M3
     [rows, F], act_scale [rows, F/128])`: the same three tensors as `grouped_gemm_fp8` followed
@@ -448,6 +481,7 @@ def grouped_gemm_fp8_swiglu(a_q, a_scale, w13_q, w13_scale, offsets, *, limit=No
     return h13, act_q, scales
 
 
+@_on_tensor_device
 def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
     """`[G, M, N]` with `out[e] = g[rows_e].T @ x[rows_e]` (bf16 operands, fp32 sums).
     `offsets` has `segments * groups + 1` entries; expert e sums over the ranges
@@ -474,6 +508,7 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
     return out
 
 
+@_on_tensor_device
 def lora_project(x, factor, offsets, *, rank_major):
     """`t [rows, r] = x[row] . factor[expert(row)]`; factor `[E, r, K]` (`rank_major`) or `[E, K, r]`."""
     device = _need_cuda(x, factor, offsets)
@@ -494,6 +529,7 @@ def lora_project(x, factor, offsets, *, rank_major):
     return out
 
 
+@_on_tensor_device
 def lora_expand(t, factor, offsets, *, wide_major, scale=1.0):
     """`c [rows, N] = scale * t[row] . factor[expert(row)]`; factor `[E, N, r]` (`wide_major`) or
     `[E, r, N]`."""
@@ -516,6 +552,7 @@ def lora_expand(t, factor, offsets, *, wide_major, scale=1.0):
 
 
 # ---------------------------------------------------------------------- permutation I/O
+@_on_tensor_device
 def combine(source, slots, weights, residual):
     """`residual + sum_k weights[:, k] * source[slots[:, k]]` as bf16 `[T, D]`."""
     device = _need_cuda(source, slots, weights, residual)
@@ -541,6 +578,7 @@ def dispatch_backward(source, slots):
     return combine(source, slots, None, None)
 
 
+@_on_tensor_device
 def dispatch(x, order, top_k):
     """bf16 rows of `x` in expert order: row j is `x[order[j] // top_k]`."""
     device = _need_cuda(x, order)
@@ -550,8 +588,8 @@ def dispatch(x, order, top_k):
         return out
     check(
         lib.b200moe_gather_rows(
-            x.data_ptr(), x.stride(0), order.data_ptr(), int(top_k), rows, x.shape[1],
-            out.data_ptr(), out.stride(0), _stream(),
+            x.data_ptr(), x.stride(0), x.shape[0], order.data_ptr(), int(top_k), rows, x.shape[1],
+            out.data_ptr(), out.stride(0), status_block(device).data_ptr(), _stream(),
         ),
         "dispatch",
     )
@@ -559,13 +597,15 @@ def dispatch(x, order, top_k):
     return out
 
 
+@_on_tensor_device
 def gather_scalar(values, slots):
     """`values[slots]` (fp32), shaped like `slots`."""
     _need_cuda(values, slots)
     out = torch.empty(slots.shape, dtype=torch.float32, device=values.device)
     check(
         lib.b200moe_gather_scalar(
-            values.data_ptr(), slots.data_ptr(), slots.numel(), out.data_ptr(), _stream()
+            values.data_ptr(), values.numel(), slots.data_ptr(), slots.numel(), out.data_ptr(),
+            status_block(values.device).data_ptr(), _stream()
         ),
         "gather_scalar",
     )

@@ -183,3 +183,69 @@ def test_fused_combine_layer_matches_within_one_rounding():
     assert mx <= 2.0 ** -6 and mean <= 1e-4, (mx, mean)
     for a, b in zip(plain[1:], fused[1:]):
         assert torch.equal(a, b)
+
+
+def test_nan_tokens_and_bad_route_ids_give_nan_or_a_status_never_a_fault():
+    """A diverged token (NaN activations, hence NaN logits) must come out as NaN rows, and
+    caller-supplied ids outside the expert range must be reported in the status block; neither
+    may index outside a buffer (every gather index is bounded on the device)."""
+    layer, ops = _layer()
+    from mlops_b200._lib import NativeError
+
+    c1 = inputs.config1()
+    w13 = tuple(t.to(DEV) for t in O.quantize_blocks(c1["w13"]))
+    w2 = tuple(t.to(DEV) for t in O.quantize_blocks(c1["w2"]))
+    x, router, dy = c1["x"].clone(), c1["router"].to(DEV), c1["dy"].to(DEV)
+    x[7] = float("nan")
+    x[100, 3] = float("inf")
+    x = x.to(DEV)
+    res = layer.forward_routed(x, torch.zeros_like(x), router, w13, w2, top_k=2, routing_mode="softmax_then_topk")
+    ids = res[6]
+    assert bool(((ids >= 0) & (ids < 8)).all())
+    grads = layer.backward_routed(dy, None, None, x, router, w13, w2, *res[4:], top_k=2,
+                                  routing_mode="softmax_then_topk")
+    torch.cuda.synchronize()
+    ops.check_status(DEV)  # NaN data is not an error: it propagates
+    out = res[0]
+    assert bool(torch.isnan(out[7]).all())
+    clean = torch.ones(x.shape[0], dtype=torch.bool)
+    clean[[7, 100]] = False
+    assert bool(torch.isfinite(out.cpu()[clean]).all())
+    assert bool(torch.isfinite(grads[0].cpu()[clean]).all())
+
+    # ids outside [0, E) handed in by the caller
+    x = c1["x"].to(DEV)
+    bad_ids = torch.randint(0, 8, (x.shape[0], 2), generator=torch.Generator().manual_seed(2)).to(torch.int32)
+    bad_ids[5, 0] = 99
+    bad_ids[6, 1] = -4
+    weights = torch.full((x.shape[0], 2), 0.5)
+    res = layer.forward_routed(x, torch.zeros_like(x), router, w13, w2, top_k=2, routing_mode="softmax_then_topk",
+                               route=(weights.to(DEV), bad_ids.to(DEV)))
+    layer.backward_routed(dy, None, None, x, router, w13, w2, *res[4:], top_k=2, routing_mode="softmax_then_topk")
+    torch.cuda.synchronize()
+    with pytest.raises(NativeError):
+        ops.check_status(DEV)
+    assert bool(torch.isfinite(res[0]).all())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_layer_on_a_device_that_is_not_current():
+    """Tensors on cuda:1 while cuda:0 is the current device (a model moved with `.to`): the
+    wrappers launch on the tensors' device and stream, and results equal those on cuda:0."""
+    layer, ops = _layer()
+    c1 = inputs.config1()
+    outs = []
+    for name in ("cuda:0", "cuda:1"):
+        torch.cuda.set_device(0)
+        w13 = tuple(t.to(name) for t in O.quantize_blocks(c1["w13"]))
+        w2 = tuple(t.to(name) for t in O.quantize_blocks(c1["w2"]))
+        x, router, dy = c1["x"].to(name), c1["router"].to(name), c1["dy"].to(name)
+        res = layer.forward_routed(x, torch.zeros_like(x), router, w13, w2, top_k=2,
+                                   routing_mode="softmax_then_topk")
+        grads = layer.backward_routed(dy, None, None, x, router, w13, w2, *res[4:], top_k=2,
+                                      routing_mode="softmax_then_topk")
+        torch.cuda.synchronize(name)
+        ops.check_status(name)
+        outs.append((res[0].cpu(), grads[0].cpu(), grads[3].cpu()))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)

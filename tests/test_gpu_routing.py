@@ -99,12 +99,48 @@ def test_sort_edge_cases():
     ops.check_status(DEV)
 
 
-def test_out_of_range_expert_id_is_reported_not_written():
+def test_out_of_range_expert_id_is_reported_and_sorted_as_the_nearest_expert():
+    """A bad id must not leave holes in `order` / `slots` (later kernels index with them): it is
+    reported in the status block and sorted as the nearest valid expert."""
     ops = _ops()
     from mlops_b200._lib import NativeError
 
-    ids = torch.tensor([[0, 9]], dtype=torch.int32, device=DEV)  # 9 >= experts
-    ops.sort_assignments(ids, 8)
+    ids = torch.tensor([[0, 9], [-3, 2]], dtype=torch.int32, device=DEV)  # 9 >= experts, -3 < 0
+    order, offsets, slots, counts = ops.sort_assignments(ids, 8)
     with pytest.raises(NativeError):
         ops.check_status(DEV)
     ops.check_status(DEV)  # the block was cleared
+    clamped = ids.cpu().clamp(0, 7)
+    o_ref, f_ref, s_ref = O.sort_assignments(clamped, 8)
+    assert torch.equal(order.cpu(), o_ref) and torch.equal(offsets.cpu(), f_ref) and torch.equal(slots.cpu(), s_ref)
+    assert int(counts.sum()) == 4
+
+
+@pytest.mark.parametrize("mode", ["softmax_then_topk", "topk_then_softmax", "sigmoid_noaux_tc"])
+def test_nan_and_infinite_logits_still_give_valid_ids(mode):
+    """The reference selects with stable descending sorts, where NaN ranks first: ids stay K
+    distinct experts in range and the NaN surfaces in the weights, never in an index."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(17)
+    experts, top_k = 64, 6
+    logits = torch.randn(40, experts, generator=g)
+    logits[0] = float("nan")                     # a diverged token: every logit NaN
+    logits[1, 5] = float("nan")                  # one NaN
+    logits[2, :60] = float("nan")                # fewer than K numbers left
+    logits[3, 7] = float("inf")
+    logits[4] = float("-inf")
+    logits[5, 9] = float("-inf")
+    kwargs = dict(bias=torch.randn(experts, generator=g) * 0.1, n_group=8, topk_group=4, routed_scaling=2.5) \
+        if mode == "sigmoid_noaux_tc" else {}
+    w_ref, ids_ref = O.route(logits, top_k, mode, **kwargs)
+    dev_kwargs = dict(kwargs)
+    if "bias" in dev_kwargs:
+        dev_kwargs["bias"] = dev_kwargs["bias"].to(DEV)
+    w, ids = ops.route_topk(logits.to(DEV), top_k, mode, **dev_kwargs)
+    ids_c = ids.cpu()
+    assert bool(((ids_c >= 0) & (ids_c < experts)).all())
+    assert all(len(set(row.tolist())) == top_k for row in ids_c)
+    assert torch.equal(ids_c, ids_ref), (ids_c[:6], ids_ref[:6])
+    finite = torch.isfinite(w_ref).all(-1)
+    torch.testing.assert_close(w.cpu()[finite], w_ref[finite], rtol=2e-6, atol=1e-7)
+    assert torch.equal(torch.isnan(w.cpu()), torch.isnan(w_ref))
