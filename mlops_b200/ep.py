@@ -642,3 +642,98 @@ class ExpertParallelMoE:
 
             ops.set_cta_limit(0)
         self.side_stream = None
+
+
+def parity_check(group, device, *, routing_mode="softmax_then_topk", n_group=1, topk_group=1,
+                 routed_scaling=1.0, shared=False, tokens=384, width=512, inner=256, experts_per_rank=4,
+                 seed=5) -> dict:
+    """The expert-parallel layer against the single-GPU layer on the gathered weights, on a
+    small case with this group's world size: every rank builds the same global experts, keeps
+    its shard, runs `ExpertParallelMoE` on its own tokens and `layer.forward_routed /
+    backward_routed` on the full weights, and compares. The outputs must be bit-equal (the
+    expert math is row-wise identical whichever rank runs it) and the gradients agree to
+    rounding; expert weight gradients are compared with the all-reduced single-GPU ones (every
+    rank's tokens contribute to an expert). Raises AssertionError on a mismatch; returns the
+    measured figures. This is the expectation the reference's multi-rank tests form
+    (`tests/expert_parallel/gpu/reference_quack.py:14-69`: run the oracle on global weights,
+    all-reduce the expected expert gradients, slice the own shard)."""
+    from . import layer, ops
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    experts = experts_per_rank * world
+    if n_group > 1:  # group-limited routing: one group per rank, half of the groups eligible
+        n_group, topk_group = world, max(1, world // 2)
+        top_k = min(4, experts_per_rank * topk_group)
+    else:
+        n_group = topk_group = 1
+        top_k = min(4, experts)
+    g = torch.Generator().manual_seed(seed)  # global parameters: identical on every rank
+    router = (torch.randn(experts, width, generator=g) * 0.05).to(device)
+    bias = (torch.randn(experts, generator=g) * 0.1).to(device) if routing_mode == "sigmoid_noaux_tc" else None
+    w13 = ops.quantize_blocks((torch.randn(experts, 2 * inner, width, generator=g) * 0.05).bfloat16().to(device))
+    w2 = ops.quantize_blocks((torch.randn(experts, width, inner, generator=g) * 0.05).bfloat16().to(device))
+    shared_w = None
+    if shared:
+        shared_w = ((torch.randn(2 * inner, width, generator=g) * 0.05).bfloat16().to(device),
+                    (torch.randn(width, inner, generator=g) * 0.05).bfloat16().to(device))
+    gl = torch.Generator().manual_seed(100 + rank)  # this rank's tokens
+    x = torch.randn(tokens, width, generator=gl).bfloat16().to(device)
+    residual = torch.randn(tokens, width, generator=gl).bfloat16().to(device)
+    dy = torch.randn(tokens, width, generator=gl).bfloat16().to(device)
+    dedup = n_group > 1
+    config = ExpertParallelConfig(hidden=width, experts=experts, intermediate=inner, top_k=top_k,
+                                  routing_mode=routing_mode, n_group=n_group, topk_group=topk_group,
+                                  routed_scaling=routed_scaling, expert_map="contiguous" if dedup else "strided",
+                                  dedup=dedup)
+    keys = placement(config, world)
+    mine = sorted((e for e in range(experts) if int(keys[e]) // experts_per_rank == rank), key=lambda e: int(keys[e]))
+    pick = torch.tensor(mine, device=device)
+    module = ExpertParallelMoE(config, group, router_weight=router, router_bias=bias,
+                               w13=(w13[0][pick].contiguous(), w13[1][pick].contiguous()),
+                               w2=(w2[0][pick].contiguous(), w2[1][pick].contiguous()), shared=shared_w,
+                               device=device, weight_grad_dtype=torch.float32, chunks=2)
+    output, aux, counts, _psum, saved = module.forward(x, residual)
+    grads = module.backward(saved, dy)
+    torch.cuda.synchronize(device)
+    ops.check_status(device)
+
+    base, shared_h13 = residual, None
+    if shared:
+        y_shared, shared_h13 = layer.shared_expert_forward(x, *shared_w)
+        base = residual + y_shared
+    kwargs = dict(top_k=top_k, routing_mode=routing_mode, router_bias=bias, n_group=n_group,
+                  topk_group=topk_group, routed_scaling=routed_scaling)
+    ref = layer.forward_routed(x, base, router, w13, w2, **kwargs)
+    ref_grads = layer.backward_routed(dy, None, None, x, router, w13, w2, *ref[4:], top_k=top_k,
+                                      routing_mode=routing_mode, weight_grad_dtype=torch.float32)
+    expected_x = ref_grads[0]
+    if shared:
+        expected_x = expected_x + layer.shared_expert_backward(dy, x, *shared_w, shared_h13)[0]
+
+    def max_rel(actual, expected):
+        a, e = actual.double(), expected.double()
+        rms = e.pow(2).mean().sqrt().clamp_min(1e-30)
+        return ((a - e).abs() / torch.maximum(e.abs(), rms)).max().item()
+
+    result = {"world": world, "experts": experts, "top_k": top_k, "tokens_per_rank": tokens,
+              "routing": routing_mode, "dedup_dispatch": dedup,
+              "counts_equal": bool(torch.equal(counts, ref[2])),
+              "output_bit_equal": bool(torch.equal(output, ref[0])),
+              "grad_x_max_rel": max_rel(grads["grad_x"], expected_x),
+              "grad_router_max_rel": max_rel(grads["grad_router"], ref_grads[2])}
+    for name, full in (("grad_w13", ref_grads[3]), ("grad_w2", ref_grads[4])):
+        total = full.clone()
+        dist.all_reduce(total, group=group)
+        result[name + "_max_rel"] = max_rel(grads[name], total[pick])
+    flags = torch.tensor([float(result["counts_equal"] and result["output_bit_equal"]),
+                          -result["grad_x_max_rel"], -result["grad_router_max_rel"],
+                          -result["grad_w13_max_rel"], -result["grad_w2_max_rel"]], device=device)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=group)  # the worst rank decides
+    worst = flags.tolist()
+    result.update(output_bit_equal=bool(worst[0] == 1.0) and result["output_bit_equal"],
+                  grad_x_max_rel=-worst[1], grad_router_max_rel=-worst[2], grad_w13_max_rel=-worst[3],
+                  grad_w2_max_rel=-worst[4])
+    module.close()
+    assert worst[0] == 1.0, f"expert-parallel output differs from the single-GPU layer: {result}"
+    assert -worst[1] <= 2e-2 and -worst[2] <= 1e-3 and -worst[3] <= 1e-3 and -worst[4] <= 1e-3, result
+    return result

@@ -11,14 +11,20 @@ products are the E4M3 tcgen05 GEMMs; each LoRA term is formed by the rank-r kern
 gradient; the factors' gradients are grouped weight gradients with one narrow side on the
 tcgen05 weight-gradient kernel. The reference validates `implementation=` against a literal
 tuple, so this function is reached by importing it, not through that argument.
+
+Like the plain layer, the computation is a functional custom-operator pair
+(`b200moe::moe_lora_fwd` / `b200moe::moe_lora_bwd`) with fake implementations and autograd
+registered on the forward operator, so it can be traced and counted like the reference's
+operators (`docs/PROVIDERS.md:86-112`).
 """
 
 from __future__ import annotations
 
 import torch
+from torch.utils.flop_counter import register_flop_formula
 
-from . import layer, ops
-from .weights import components
+from . import layer, ops, provider
+from .weights import holds_blocks
 
 
 def _pad_rank(factor, axis):
@@ -35,106 +41,229 @@ def _pad_rank(factor, axis):
     return out, rank
 
 
-class _ExpertLoRA(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, router_bias, options):
-        w13, w2 = components(gate_up), components(down)
-        experts = w13[0].shape[0]
-        top_k, scale, limit = options["top_k"], options["scale"], options["swiglu_limit"]
+def _kernel_factors(a13, b13, a2, b2):
+    """The factors as the rank-r kernels read them: ranks padded, the B factors rank-major
+    (`[E, r, wide]`) so every kernel stages its factor with 16-byte loads (a few MB per call)."""
+    a13p, rank = _pad_rank(a13.detach(), 1)
+    b13p, _ = _pad_rank(b13.detach(), 2)
+    a2p, _ = _pad_rank(a2.detach(), 1)
+    b2p, _ = _pad_rank(b2.detach(), 2)
+    return a13p, b13p.transpose(1, 2).contiguous(), a2p, b2p.transpose(1, 2).contiguous(), rank
+
+
+_THIRTEEN = tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                  torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                  torch.Tensor]
+_NINE = tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+              torch.Tensor, torch.Tensor, torch.Tensor]
+
+
+@torch.library.custom_op("b200moe::moe_lora_fwd", mutates_args=())
+def moe_lora_fwd(hidden: torch.Tensor, residual: torch.Tensor, router_weight: torch.Tensor, gate_up: torch.Tensor,
+                 down: torch.Tensor, a13: torch.Tensor, b13: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor,
+                 router_bias: torch.Tensor, top_k: int, routing_mode: str, scale: float, n_group: int,
+                 topk_group: int, routed_scaling: float, lengths: list[int], swiglu_limit: float | None,
+                 weight_components: list[torch.Tensor]) -> _THIRTEEN:
+    """`(output, aux, counts, probability_sum, logits, route_weights, route_ids, order, offsets,
+    slots, h13, t1, t2)`: the plain layer's results and residuals plus the two rank-r
+    intermediates `t1 = x A13^T`, `t2 = act A2^T` the factor gradients need."""
+    w13, w2 = provider._with_scales(gate_up, down, weight_components)
+    experts = gate_up.shape[0]
+    with torch.no_grad(), torch.cuda.device(hidden.device):
         flat = hidden.reshape(-1, hidden.shape[-1]).contiguous()
         residual_flat = residual.reshape_as(flat).contiguous()
-        a13p, rank = _pad_rank(a13.detach(), 1)
-        b13p, _ = _pad_rank(b13.detach(), 2)
-        a2p, _ = _pad_rank(a2.detach(), 1)
-        b2p, _ = _pad_rank(b2.detach(), 2)
-        # the B factors are also kept rank-major ([E, r, wide]): every rank-r kernel then stages
-        # its factor with 16-byte loads (a few MB, transposed once per call)
-        b13t = b13p.transpose(1, 2).contiguous()
-        b2t = b2p.transpose(1, 2).contiguous()
+        a13p, b13t, a2p, b2t, _rank = _kernel_factors(a13, b13, a2, b2)
         logits = layer.router_logits(flat, router_weight)
         weights, ids = ops.route_topk(
-            logits, top_k, options["routing_mode"], bias=router_bias, n_group=options["n_group"],
-            topk_group=options["topk_group"], routed_scaling=options["routed_scaling"],
-        )
+            logits, top_k, routing_mode, bias=None if router_bias.numel() == 0 else router_bias, n_group=n_group,
+            topk_group=topk_group, routed_scaling=routed_scaling)
         order, offsets, slots, counts = ops.sort_assignments(ids, experts)
         x_rows = ops.dispatch(flat, order, top_k)
         x_q, x_s = ops.quantize_rows(x_rows)
         t1 = ops.lora_project(x_rows, a13p, offsets, rank_major=True)
         c1 = ops.lora_expand(t1, b13t, offsets, wide_major=False, scale=scale)
         h13 = ops.grouped_gemm_fp8(x_q, x_s, *w13, offsets, addend=c1)
-        a_q, a_s, act = ops.swiglu_quantize(h13, limit=limit, quantized=True, rounded=True)
+        a_q, a_s, act = ops.swiglu_quantize(h13, limit=swiglu_limit, quantized=True, rounded=True)
         t2 = ops.lora_project(act, a2p, offsets, rank_major=True)
         c2 = ops.lora_expand(t2, b2t, offsets, wide_major=False, scale=scale)
         y = ops.grouped_gemm_fp8(a_q, a_s, *w2, offsets, addend=c2)
         output = ops.combine(y, slots, weights, residual_flat).reshape(hidden.shape)
         aux, counts, probability_sum = layer.routing_statistics(
-            logits, ids, counts, routing_mode=options["routing_mode"], lengths=options["lengths"], experts=experts)
-        ctx.save_for_backward(flat, router_weight, *w13, *w2, a13p, b13t, a2p, b2t, logits, weights, ids, order,
-                              offsets, slots, h13, t1, t2)
-        ctx.options, ctx.rank, ctx.shape = options, rank, hidden.shape
-        ctx.logical = (gate_up.dtype, down.dtype)
-        ctx.mark_non_differentiable(counts)
-        return output, aux, counts, probability_sum
+            logits, ids, counts, routing_mode=routing_mode, lengths=tuple(lengths), experts=experts)
+    return output, aux, counts, probability_sum, logits, weights, ids, order, offsets, slots, h13, t1, t2
 
-    @staticmethod
-    def backward(ctx, grad_output, grad_aux, _grad_counts, grad_probability_sum):
-        (flat, router_weight, w13_d, w13_s, w2_d, w2_s, a13, b13, a2, b2, logits, weights, ids, order, offsets,
-         slots, h13, t1, t2) = ctx.saved_tensors
-        options, rank = ctx.options, ctx.rank
-        need = ctx.needs_input_grad
-        top_k, scale, limit = options["top_k"], options["scale"], options["swiglu_limit"]
-        experts = w13_d.shape[0]
-        if grad_output is None:
-            grad_output = torch.zeros(ctx.shape, dtype=flat.dtype, device=flat.device)
+
+@moe_lora_fwd.register_fake
+def _moe_lora_fwd_fake(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, router_bias, top_k,
+                       routing_mode, scale, n_group, topk_group, routed_scaling, lengths, swiglu_limit,
+                       weight_components):
+    rows = hidden.numel() // hidden.shape[-1]
+    experts, assignments = router_weight.shape[0], rows * int(top_k)
+    padded = -(-a13.shape[1] // 8) * 8
+    new = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=hidden.device)  # noqa: E731
+    return (
+        torch.empty_like(hidden, memory_format=torch.contiguous_format),
+        new((), torch.float32), new((experts,), torch.int64), new((experts,), torch.float32),
+        new((rows, experts), torch.float32), new((rows, int(top_k)), torch.float32),
+        new((rows, int(top_k)), torch.int32), new((assignments,), torch.int32),
+        new((experts + 1,), torch.int32), new((rows, int(top_k)), torch.int32),
+        new((assignments, gate_up.shape[1]), hidden.dtype), new((assignments, padded), hidden.dtype),
+        new((assignments, padded), hidden.dtype),
+    )
+
+
+@torch.library.custom_op("b200moe::moe_lora_bwd", mutates_args=())
+def moe_lora_bwd(grad_output: torch.Tensor, grad_aux: torch.Tensor, grad_probability_sum: torch.Tensor,
+                 hidden: torch.Tensor, router_weight: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
+                 a13: torch.Tensor, b13: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor, logits: torch.Tensor,
+                 route_weights: torch.Tensor, route_ids: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor,
+                 slots: torch.Tensor, h13: torch.Tensor, t1: torch.Tensor, t2: torch.Tensor, top_k: int,
+                 routing_mode: str, scale: float, lengths: list[int], weight_grad_dtype: torch.dtype | None,
+                 swiglu_limit: float | None, need_router: bool, need_w13: bool, need_w2: bool,
+                 need_factors: bool, weight_components: list[torch.Tensor]) -> _NINE:
+    """`(grad_hidden, grad_residual, grad_router, grad_w13, grad_w2, grad_a13, grad_b13, grad_a2,
+    grad_b2)`; gradients whose flag is false are empty placeholders and are not computed (a
+    frozen base launches no base-weight gradient: `tests/test_sonicmoe_lora.py:209-233`)."""
+    (w13_d, w13_s), (w2_d, w2_s) = provider._with_scales(gate_up, down, weight_components)
+    experts = w13_d.shape[0]
+    wdtype = torch.bfloat16 if weight_grad_dtype is None else weight_grad_dtype
+    weights, ids = route_weights, route_ids
+    with torch.no_grad(), torch.cuda.device(hidden.device):
+        flat = hidden.reshape(-1, hidden.shape[-1]).contiguous()
         dy = grad_output.reshape_as(flat).contiguous()
+        a13p, b13t, a2p, b2t, rank = _kernel_factors(a13, b13, a2, b2)
         counts = (offsets[1:] - offsets[:-1]).long()
-        need_factors = any(need[5:9])
+        empty = lambda dtype: torch.empty(0, dtype=dtype, device=flat.device)  # noqa: E731
 
         dy_rows = ops.dispatch(dy, order, top_k)
         dy_q, dy_s = ops.quantize_rows(dy_rows)
-        t2g = ops.lora_project(dy_rows, b2, offsets, rank_major=True)           # dy B2      [R, r]
-        r_add = ops.lora_expand(t2g, a2, offsets, wide_major=False, scale=scale)  # s dy B2 A2 [R, F]
+        t2g = ops.lora_project(dy_rows, b2t, offsets, rank_major=True)              # dy B2      [R, r]
+        r_add = ops.lora_expand(t2g, a2p, offsets, wide_major=False, scale=scale)   # s dy B2 A2 [R, F]
         r = ops.grouped_gemm_fp8(dy_q, dy_s, w2_d, w2_s, offsets, b_mn_major=True, addend=r_add)
         dscore, gh_q, gh_s, gh_b, act_scaled = ops.dswiglu_routed(
-            h13, r, weights, order, limit=limit, quantized=True, rounded=True, scaled_activation=True)
+            h13, r, weights, order, limit=swiglu_limit, quantized=True, rounded=True, scaled_activation=True)
         grad_route_weights = ops.gather_scalar(dscore, slots)
 
         x_rows = ops.dispatch(flat, order, top_k)
-        dt1 = ops.lora_project(gh_b, b13, offsets, rank_major=True)             # gh B13     [R, r]
-        grad_a13 = grad_b13 = grad_a2 = grad_b2 = None
+        dt1 = ops.lora_project(gh_b, b13t, offsets, rank_major=True)                # gh B13     [R, r]
+        fdtype = a13.dtype
+        grad_a13 = grad_b13 = grad_a2 = grad_b2 = empty(fdtype)
         if need_factors:
             row_weight = weights.reshape(-1)[order.long()].float()[:, None]
-            fdtype = a13.dtype
             grad_b2 = ops.grouped_wgrad(dy_rows, (t2.float() * (row_weight * scale)).to(t2.dtype), offsets,
-                                        experts, fdtype)[:, :, :rank]
+                                        experts, fdtype)[:, :, :rank].contiguous()
             grad_a2 = ops.grouped_wgrad((t2g.float() * scale).to(t2g.dtype), act_scaled, offsets, experts,
-                                        fdtype)[:, :rank]
+                                        fdtype)[:, :rank].contiguous()
             grad_b13 = ops.grouped_wgrad(gh_b, (t1.float() * scale).to(t1.dtype), offsets, experts,
-                                         fdtype)[:, :, :rank]
+                                         fdtype)[:, :, :rank].contiguous()
             grad_a13 = ops.grouped_wgrad((dt1.float() * scale).to(dt1.dtype), x_rows, offsets, experts,
-                                         fdtype)[:, :rank]
-        dx_add = ops.lora_expand(dt1, a13, offsets, wide_major=False, scale=scale)
+                                         fdtype)[:, :rank].contiguous()
+        dx_add = ops.lora_expand(dt1, a13p, offsets, wide_major=False, scale=scale)
         grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, w13_d, w13_s, offsets, b_mn_major=True, addend=dx_add)
         grad_h2 = ops.dispatch_backward(grad_rows, slots)
 
-        grad_w13 = grad_w2 = None
-        if need[3]:  # a trainable base gets its gradient as in the plain layer
-            grad_w13 = ops.grouped_wgrad(gh_b, x_rows, offsets, experts, ctx.logical[0])
-        if need[4]:
-            grad_w2 = ops.grouped_wgrad(dy_rows, act_scaled, offsets, experts, ctx.logical[1])
+        # a trainable base gets its gradient as in the plain layer
+        grad_w13 = ops.grouped_wgrad(gh_b, x_rows, offsets, experts, wdtype) if need_w13 else empty(wdtype)
+        grad_w2 = ops.grouped_wgrad(dy_rows, act_scaled, offsets, experts, wdtype) if need_w2 else empty(wdtype)
 
         grad_logits = layer.routing_gradient(
             grad_aux, grad_probability_sum, grad_route_weights, weights, ids, logits, counts,
-            routing_mode=options["routing_mode"], lengths=options["lengths"])
-        grad_router = None
-        if need[2]:
-            grad_router = layer._router_weight_gradient(grad_logits, flat, router_weight.dtype)
+            routing_mode=routing_mode, lengths=tuple(lengths))
+        rdtype = router_weight.dtype if weight_grad_dtype is None else weight_grad_dtype
+        grad_router = (layer._router_weight_gradient(grad_logits, flat, rdtype) if need_router
+                       else empty(router_weight.dtype))
         grad_h2.addmm_(grad_logits.to(flat.dtype), getattr(router_weight, "_data", router_weight).to(flat.dtype))
-        contig = lambda t: None if t is None else t.contiguous()  # noqa: E731
-        return (grad_h2.reshape(ctx.shape) if need[0] else None, grad_output.clone() if need[1] else None,
-                grad_router, grad_w13, grad_w2, contig(grad_a13) if need[5] else None,
-                contig(grad_b13) if need[6] else None, contig(grad_a2) if need[7] else None,
-                contig(grad_b2) if need[8] else None, None, None)
+    return (grad_h2.reshape(hidden.shape), grad_output.clone(), grad_router, grad_w13, grad_w2, grad_a13, grad_b13,
+            grad_a2, grad_b2)
+
+
+@moe_lora_bwd.register_fake
+def _moe_lora_bwd_fake(grad_output, grad_aux, grad_probability_sum, hidden, router_weight, gate_up, down, a13, b13,
+                       a2, b2, logits, route_weights, route_ids, order, offsets, slots, h13, t1, t2, top_k,
+                       routing_mode, scale, lengths, weight_grad_dtype, swiglu_limit, need_router, need_w13,
+                       need_w2, need_factors, weight_components):
+    wdtype = torch.bfloat16 if weight_grad_dtype is None else weight_grad_dtype
+    rdtype = router_weight.dtype if weight_grad_dtype is None else weight_grad_dtype
+    new = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=hidden.device)  # noqa: E731
+    factor = lambda f: new(tuple(f.shape), f.dtype) if need_factors else new((0,), f.dtype)  # noqa: E731
+    return (
+        torch.empty_like(hidden, memory_format=torch.contiguous_format),
+        torch.empty_like(grad_output, memory_format=torch.contiguous_format),
+        new(tuple(router_weight.shape), rdtype) if need_router else new((0,), router_weight.dtype),
+        new(tuple(gate_up.shape), wdtype) if need_w13 else new((0,), wdtype),
+        new(tuple(down.shape), wdtype) if need_w2 else new((0,), wdtype),
+        factor(a13), factor(b13), factor(a2), factor(b2),
+    )
+
+
+def _lora_flops(hidden, router_weight, gate_up, down, a13, top_k, forward, frozen_base):
+    base = provider._logical_flops(hidden, router_weight, gate_up, down, top_k, forward)
+    rows = (hidden.numel() // hidden.shape[-1]) * int(top_k)
+    width, packed, inner, rank = hidden.shape[-1], gate_up.shape[1], down.shape[2], a13.shape[1]
+    branch = 2 * rows * rank * (width + packed + inner + width)  # project + expand, both projections
+    if forward:
+        return base + branch
+    if frozen_base:  # no base weight gradient: the input-gradient half of the backward products
+        base -= 2 * rows * width * packed + 2 * rows * inner * width
+    return base + 2 * branch
+
+
+@register_flop_formula(torch.ops.b200moe.moe_lora_fwd, get_raw=True)
+def _moe_lora_fwd_flops(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, router_bias, top_k,
+                        *_rest, out_val=None, **_kwargs):
+    return _lora_flops(hidden, router_weight, gate_up, down, a13, top_k, True, False)
+
+
+@register_flop_formula(torch.ops.b200moe.moe_lora_bwd, get_raw=True)
+def _moe_lora_bwd_flops(grad_output, grad_aux, grad_probability_sum, hidden, router_weight, gate_up, down, a13,
+                        b13, a2, b2, logits, route_weights, route_ids, order, offsets, slots, h13, t1, t2, top_k,
+                        routing_mode, scale, lengths, weight_grad_dtype, swiglu_limit, need_router, need_w13,
+                        need_w2, *_rest, out_val=None, **_kwargs):
+    return _lora_flops(hidden, router_weight, gate_up, down, a13, top_k, False, not (need_w13 or need_w2))
+
+
+def _setup_context(ctx, inputs, output):
+    (hidden, _residual, router_weight, gate_up, down, a13, b13, a2, b2, _bias, top_k, routing_mode, scale,
+     _n_group, _topk_group, _scaling, lengths, swiglu_limit, weight_components) = inputs
+    (_out, _aux, counts, _psum, logits, weights, ids, order, offsets, slots, h13, t1, t2) = output
+    ctx.save_for_backward(hidden, router_weight, gate_up, down, a13, b13, a2, b2, logits, weights, ids, order,
+                          offsets, slots, h13, t1, t2, *weight_components)
+    ctx.top_k, ctx.routing_mode, ctx.scale = int(top_k), routing_mode, float(scale)
+    ctx.lengths, ctx.swiglu_limit, ctx.components = list(lengths), swiglu_limit, len(weight_components)
+    ctx.weight_grad_dtype = provider._context_weight_gradient_dtype()
+    ctx.logical = gate_up.dtype if gate_up.dtype != torch.float8_e4m3fn else torch.bfloat16
+    ctx.mark_non_differentiable(counts, logits, weights, ids, order, offsets, slots, h13, t1, t2)
+
+
+def _autograd_backward(ctx, grad_output, grad_aux, _g_counts, grad_probability_sum, *_metadata_grads):
+    saved = ctx.saved_tensors
+    tensors, components = saved[:17], list(saved[17:])
+    hidden, router_weight = tensors[0], tensors[1]
+    if grad_output is None:
+        grad_output = torch.zeros_like(hidden)
+    if grad_aux is None:
+        grad_aux = torch.zeros((), dtype=torch.float32, device=hidden.device)
+    if grad_probability_sum is None:
+        grad_probability_sum = torch.zeros(router_weight.shape[0], dtype=torch.float32, device=hidden.device)
+    need = ctx.needs_input_grad
+    wdtype = ctx.weight_grad_dtype
+    if wdtype is None and ctx.logical != torch.bfloat16:
+        wdtype = ctx.logical
+    grads = moe_lora_bwd(
+        grad_output, grad_aux, grad_probability_sum, *tensors, ctx.top_k, ctx.routing_mode, ctx.scale, ctx.lengths,
+        wdtype, ctx.swiglu_limit, bool(need[2]), bool(need[3]), bool(need[4]), bool(any(need[5:9])), components)
+    grad_router = grads[2]
+    if ctx.weight_grad_dtype is None and need[2] and grad_router.dtype != router_weight.dtype:
+        grad_router = grad_router.to(router_weight.dtype)
+    picked = [grads[0], grads[1], grad_router, *grads[3:]]
+    return (*[g if n else None for g, n in zip(picked, need[:9])], *([None] * 9), [None] * ctx.components)
+
+
+moe_lora_fwd.register_autograd(_autograd_backward, setup_context=_setup_context)
+provider._CONTAINER_OPERATORS.extend([moe_lora_fwd, moe_lora_bwd])
+for _cls in list(provider._DISPATCH_REGISTERED):  # containers registered before this module loaded
+    moe_lora_fwd.register_torch_dispatch(_cls, provider._unwrap_containers)
+    moe_lora_bwd.register_torch_dispatch(_cls, provider._unwrap_containers)
 
 
 def expert_lora(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, *, top_k, routing_mode, scale,
@@ -146,6 +275,8 @@ def expert_lora(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2
         raise ValueError(f"mlops_b200.expert_lora serves implementation 'b200' (or 'auto'), not {implementation!r}")
     if compute_precision not in (None, "fp8_block"):
         raise ValueError("mlops_b200.expert_lora computes the base in block FP8 only")
+    if not (holds_blocks(gate_up) and holds_blocks(down)):
+        raise ValueError("gate_up and down must be block-FP8 containers (E4M3, 128x128 block scales)")
     if swiglu_limit is not None:
         swiglu_limit = float(swiglu_limit)
         if not swiglu_limit > 0:
@@ -159,11 +290,13 @@ def expert_lora(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2
             raise ValueError(f"{name} must be bf16 with shape {expected[name]}")
     if rank > 64:
         raise ValueError("ranks up to 64 are supported")
+    for weight in (gate_up, down):
+        if type(weight) not in provider._DISPATCH_REGISTERED:
+            provider.register_container(type(weight))
     rows = hidden.numel() // hidden.shape[-1]
-    options = dict(
-        top_k=int(top_k), routing_mode=str(routing_mode), scale=float(scale), n_group=int(n_group),
-        topk_group=int(topk_group), routed_scaling=float(routed_scaling), swiglu_limit=swiglu_limit,
-        lengths=(rows,) if lengths is None else tuple(int(v) for v in lengths),
-    )
-    bias = None if router_bias is None or router_bias.numel() == 0 else router_bias
-    return _ExpertLoRA.apply(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, bias, options)
+    normalized = [rows] if lengths is None else [int(v) for v in lengths]
+    bias = router_bias if router_bias is not None else torch.empty(0, dtype=torch.float32, device=hidden.device)
+    outputs = moe_lora_fwd(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, bias, int(top_k),
+                           str(routing_mode), float(scale), int(n_group), int(topk_group), float(routed_scaling),
+                           normalized, swiglu_limit, [])
+    return outputs[:4]

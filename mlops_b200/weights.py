@@ -1,11 +1,15 @@
-"""A block-FP8 expert-weight container for hosts that do not have the reference installed.
+"""Block-FP8 expert weights as this library sees them.
 
-`BlockFP8Weight` here has the reference container's shape (`src/mlops/block_fp8.py:49-154`
-of als244/mlops): `_data` E4M3 `[E, out, in]`, `_scale` fp32 `[E, ceil(out/128),
-ceil(in/128)]`, a logical dtype that is the dtype of the gradients it receives, rows in
-`nn.Linear` order. The provider accepts either class (anything that carries `_data` and
-`_scale`). Quantisation runs on this library's CUDA kernel; publication from a master weight
-(`container.copy_(master)`) re-quantises as at construction.
+The expert GEMMs read two plain tensors per weight: E4M3 bytes `[E, out, in]` and one fp32
+scale per 128x128 block, `[E, ceil(out/128), ceil(in/128)]` -- the storage of the
+reference's `mlops.block_fp8.BlockFP8Weight` (als244/mlops `src/mlops/block_fp8.py:49-68`).
+Any object that carries them as `_data` and `_scale` is accepted (`split`, `holds_blocks`),
+so the reference's own container goes straight through.
+
+For callers that do not have the reference installed, `BlockFP8Weight` below is a tensor
+subclass with the same two attributes: it looks like a `[E, out, in]` tensor of the dtype its
+gradient should have (so an optimizer or autograd can treat it as a parameter), is built by
+this library's CUDA quantiser, and re-quantises when a master weight is copied into it.
 """
 
 from __future__ import annotations
@@ -16,95 +20,136 @@ from torch.utils._python_dispatch import return_and_correct_aliasing
 from . import ops
 
 FP8 = torch.float8_e4m3fn
+BLOCK = 128
 
 
-def components(weight):
-    """`(data, scale)` of a block-FP8 container (this class or the reference's)."""
-    data = getattr(weight, "_data", None)
-    scale = getattr(weight, "_scale", None)
-    if data is None or scale is None:
-        raise TypeError("expected a BlockFP8Weight container (E4M3 data with 128x128 block scales)")
-    return data, scale
+def _scale_shape(shape):
+    experts, out, inner = shape
+    return (experts, (out + BLOCK - 1) // BLOCK, (inner + BLOCK - 1) // BLOCK)
 
 
-def is_block_fp8(weight) -> bool:
-    data = getattr(weight, "_data", None)
-    scale = getattr(weight, "_scale", None)
-    return (
-        isinstance(data, torch.Tensor) and isinstance(scale, torch.Tensor) and data.dtype == FP8
-        and data.dim() == 3 and scale.dtype == torch.float32
-        and tuple(scale.shape) == (data.shape[0], -(-data.shape[1] // 128), -(-data.shape[2] // 128))
-    )
+def holds_blocks(weight) -> bool:
+    """Whether `weight` carries E4M3 data with matching 128x128 block scales."""
+    data, scale = getattr(weight, "_data", None), getattr(weight, "_scale", None)
+    if not (isinstance(data, torch.Tensor) and isinstance(scale, torch.Tensor)):
+        return False
+    return (data.dtype == FP8 and data.dim() == 3 and scale.dtype == torch.float32
+            and tuple(scale.shape) == _scale_shape(data.shape))
 
 
-class _Quantize(torch.autograd.Function):
+def split(weight):
+    """`(data, scale)` of a block-FP8 container; TypeError for anything else."""
+    if not holds_blocks(weight):
+        raise TypeError("expected block-FP8 expert weights: E4M3 `_data` [E, out, in] with fp32 `_scale` "
+                        "per 128x128 block")
+    return weight._data, weight._scale
+
+
+
+
+class _StraightThrough(torch.autograd.Function):
+    """quantize(): the container's gradient is handed to the master weight unchanged."""
+
     @staticmethod
-    def forward(ctx, weight, dtype):
-        data, scale = ops.quantize_blocks(weight.detach())
-        return BlockFP8Weight(data, scale, dtype=weight.dtype if dtype is None else dtype)
+    def forward(ctx, master, logical):
+        data, scale = ops.quantize_blocks(master.detach())
+        return BlockFP8Weight(data, scale, dtype=logical or master.dtype)
 
     @staticmethod
     def backward(ctx, grad):
-        return grad, None  # straight through: the container's gradient is the weight's
+        return grad, None
+
+
+def _like(func, args, kwargs):
+    # factory ops autograd and optimizers call on a parameter: answer with an ordinary tensor
+    # of the logical dtype, shaped like the data
+    source = args[0]
+    kwargs = dict(kwargs)
+    kwargs.setdefault("dtype", source.dtype)
+    return func(source._data, *args[1:], **kwargs)
+
+
+def _detach(func, args, kwargs):
+    source = args[0]
+    alias = BlockFP8Weight(source._data.detach(), source._scale.detach(), dtype=source.dtype)
+    return return_and_correct_aliasing(func, args, kwargs, alias)  # detach is a view: keep it one
+
+
+def _clone(func, args, kwargs):
+    source = args[0]
+    return BlockFP8Weight(source._data.clone(), source._scale.clone(), dtype=source.dtype)
+
+
+def _copy(func, args, kwargs):
+    target, source = args[0], args[1]
+    if not isinstance(target, BlockFP8Weight):  # container -> ordinary tensor: its values
+        return target.copy_(source.dequantize(dtype=target.dtype))
+    if isinstance(source, BlockFP8Weight):
+        data, scale = source._data, source._scale
+    else:  # publication of a master weight: quantise it as at construction
+        data, scale = ops.quantize_blocks(source.to(target.device))
+    target._data.copy_(data)
+    target._scale.copy_(scale)
+    return target
+
+
+_ATEN = torch.ops.aten
+_HANDLERS = {
+    _ATEN.detach.default: _detach,
+    _ATEN.clone.default: _clone,
+    _ATEN.copy_.default: _copy,
+    _ATEN.empty_like.default: _like,
+    _ATEN.zeros_like.default: _like,
+    _ATEN.ones_like.default: _like,
+    _ATEN.new_empty_strided.default: _like,
+}
 
 
 class BlockFP8Weight(torch.Tensor):
+    """`[E, out, in]` expert weights stored as E4M3 with 128x128 block scales."""
+
     @staticmethod
     def __new__(cls, data, scale, *, dtype=torch.bfloat16):
-        if data.dim() != 3 or data.dtype != FP8:
-            raise ValueError("Expected E4M3 data [experts, out, in]")
-        experts, out, inner = data.shape
-        expected = (experts, -(-out // 128), -(-inner // 128))
-        if tuple(scale.shape) != expected or scale.dtype != torch.float32:
-            raise ValueError(f"Expected FP32 block scales {expected}")
-        value = torch.Tensor._make_wrapper_subclass(cls, tuple(data.shape), device=data.device, dtype=dtype)
-        value._data, value._scale = data, scale
-        return value
-
-    def __repr__(self):
-        return f"BlockFP8Weight(shape={tuple(self.shape)}, logical_dtype={self.dtype}, device={self.device})"
+        if not (isinstance(data, torch.Tensor) and data.dtype == FP8 and data.dim() == 3):
+            raise ValueError("data: E4M3 tensor [experts, out, in] wanted")
+        if scale.dtype != torch.float32 or tuple(scale.shape) != _scale_shape(data.shape):
+            raise ValueError(f"scale: fp32 tensor {_scale_shape(data.shape)} wanted for data {tuple(data.shape)}")
+        self = torch.Tensor._make_wrapper_subclass(cls, data.shape, dtype=dtype, device=data.device)
+        self._data = data
+        self._scale = scale
+        return self
 
     @classmethod
-    def quantize(cls, weight, *, dtype=None):
-        """A container of `weight [E, out, in]` (bf16 or fp32, on a CUDA device)."""
-        if weight.dim() != 3:
-            raise ValueError("Expected an [experts, out, in] weight")
-        return _Quantize.apply(weight, dtype)
+    def quantize(cls, master, *, dtype=None):
+        """Container of the CUDA tensor `master [E, out, in]` (bf16 or fp32). Differentiable:
+        the gradient of the container is the gradient of `master`."""
+        if master.dim() != 3:
+            raise ValueError("master weight: [experts, out, in] wanted")
+        return _StraightThrough.apply(master, dtype)
 
     def components(self):
         return self._data, self._scale
 
     def dequantize(self, *, dtype=None):
-        scale = self._scale.repeat_interleave(128, 1).repeat_interleave(128, 2)
-        scale = scale[:, : self.shape[1], : self.shape[2]]
-        return (self._data.float() * scale).to(self.dtype if dtype is None else dtype)
+        _e, out, inner = self.shape
+        per_element = self._scale.repeat_interleave(BLOCK, 1).repeat_interleave(BLOCK, 2)[:, :out, :inner]
+        return (self._data.float() * per_element).to(dtype or self.dtype)
 
+    def __repr__(self):
+        return f"{type(self).__name__}({tuple(self.shape)}, grads in {self.dtype}, on {self.device})"
+
+    # ---- what torch.compile / AOTAutograd need to take the container apart and rebuild it
     def __tensor_flatten__(self):
-        return ["_data", "_scale"], (self.dtype,)
+        return ["_data", "_scale"], self.dtype
 
     @staticmethod
-    def __tensor_unflatten__(inner, metadata, outer_size, outer_stride):
-        return BlockFP8Weight(inner["_data"], inner["_scale"], dtype=metadata[0])
+    def __tensor_unflatten__(inner, logical, outer_size, outer_stride):
+        return BlockFP8Weight(inner["_data"], inner["_scale"], dtype=logical)
 
     @classmethod
     def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
-        kwargs = kwargs or {}
-        aten, first = torch.ops.aten, args[0]
-        if func is aten.detach.default:
-            out = cls(first._data.detach(), first._scale.detach(), dtype=first.dtype)
-            return return_and_correct_aliasing(func, args, kwargs, out)
-        if func is aten.clone.default:
-            return cls(first._data.clone(), first._scale.clone(), dtype=first.dtype)
-        if func is aten.copy_.default:
-            destination, source = args[:2]
-            if isinstance(destination, cls):
-                data, scale = source.components() if isinstance(source, cls) else ops.quantize_blocks(source)
-                destination._data.copy_(data)
-                destination._scale.copy_(scale)
-                return destination
-            return destination.copy_(source.dequantize(dtype=destination.dtype))
-        if func in (aten.empty_like.default, aten.zeros_like.default, aten.ones_like.default):
-            return func(first._data, **dict(kwargs, dtype=kwargs.get("dtype", first.dtype)))
-        if func is aten.new_empty_strided.default:
-            return func(first._data, *args[1:], **dict(kwargs, dtype=kwargs.get("dtype", first.dtype)))
-        raise NotImplementedError(f"{func}: use the container's components or dequantize()")
+        handler = _HANDLERS.get(func)
+        if handler is None:
+            raise NotImplementedError(
+                f"{func} on a BlockFP8Weight: take `.components()` or `.dequantize()` first")
+        return handler(func, args, kwargs or {})

@@ -390,3 +390,83 @@ def backward_lora_block_fp8(grad_output, fwd, w13_q, w13_s, w2_q, w2_s, a13, b13
     grad_a13 = grouped_wgrad((dt1.float() * scale).to(bf), fwd["x_rows"], offsets, experts)
     return dict(grad_h2=grad_h2, grad_route_weights=dscore[slots.reshape(-1).long()].view_as(weights),
                 grad_a13=grad_a13, grad_b13=grad_b13, grad_a2=grad_a2, grad_b2=grad_b2)
+
+
+# ------------------------------------------- the whole layer, one expert at a time
+def layer_expert_major(h2, residual, grad_output, logits, w13_q, w13_s, w2_q, w2_s, *, top_k, routing_mode,
+                       router_bias=None, n_group=1, topk_group=1, routed_scaling=1.0, swiglu_limit=None,
+                       h13_for_backward=None, r_for_backward=None, keep_weight_grads=(),
+                       gemm_dtype=torch.float32):
+    """`forward_block_fp8` followed by `backward_block_fp8`, reorganised so that each expert's
+    two weights are dequantised ONCE and used for its four products (forward up / down, the two
+    input gradients) and its two weight gradients. Same equations, same rounding points; it
+    exists so that layers with hundreds of large experts (256 x [4096, 7168]) can be checked in
+    seconds and in bounded memory. Weight gradients are kept only for the experts listed in
+    `keep_weight_grads` (dicts expert -> fp32 tensor); `h13_for_backward`, when given, is the
+    saved pre-activation the backward half differentiates at (the device's own, so both sides
+    take the derivative at the same point), and `r_for_backward` the device's `dy W2` rows: with
+    both, every product of the backward half has bit-identical operands on the two sides (a
+    one-ulp bf16 difference in `r` otherwise moves single weight-gradient elements by more than
+    the rounding of the product itself). `r` is still computed here and returned."""
+    experts = w13_q.shape[0]
+    weights, ids = route(logits, top_k, routing_mode, bias=router_bias, n_group=n_group,
+                         topk_group=topk_group, routed_scaling=routed_scaling)
+    order, offsets, slots = sort_assignments(ids, experts)
+    token_of_row = torch.div(order.long(), int(top_k), rounding_mode="floor")
+    rows = order.numel()
+    inner = w2_q.shape[2]
+    x_q, x_s = quantize_rows(h2, gather=token_of_row)
+    dy_q, dy_s = quantize_rows(grad_output, gather=token_of_row)
+    x_f, dy_f = dequantize_rows(x_q, x_s, gemm_dtype), dequantize_rows(dy_q, dy_s, gemm_dtype)
+    score = weights.reshape(-1)[order.long()].float()
+    h13 = torch.zeros((rows, 2 * inner), dtype=torch.bfloat16)
+    y = torch.zeros((rows, h2.shape[1]), dtype=torch.bfloat16)
+    r = torch.zeros((rows, inner), dtype=torch.bfloat16)
+    grad_rows = torch.zeros((rows, h2.shape[1]), dtype=torch.bfloat16)
+    dscore = torch.zeros(rows, dtype=torch.float32)
+    grad_w13, grad_w2 = {}, {}
+    offs = offsets.tolist()
+    for e in range(experts):
+        lo, hi = offs[e], offs[e + 1]
+        if hi == lo:
+            if e in keep_weight_grads:
+                grad_w13[e] = torch.zeros(tuple(w13_q.shape[1:]), dtype=torch.float32)
+                grad_w2[e] = torch.zeros(tuple(w2_q.shape[1:]), dtype=torch.float32)
+            continue
+        w13 = dequantize_blocks(w13_q[e:e + 1], w13_s[e:e + 1], gemm_dtype)[0]
+        w2 = dequantize_blocks(w2_q[e:e + 1], w2_s[e:e + 1], gemm_dtype)[0]
+        h13[lo:hi] = (x_f[lo:hi] @ w13.t()).to(torch.bfloat16)
+        a_q, a_s = quantize_rows(swiglu(h13[lo:hi], swiglu_limit))
+        y[lo:hi] = (dequantize_rows(a_q, a_s, gemm_dtype) @ w2.t()).to(torch.bfloat16)
+        r[lo:hi] = (dy_f[lo:hi] @ w2).to(torch.bfloat16)
+        saved = h13[lo:hi] if h13_for_backward is None else h13_for_backward[lo:hi]
+        r_used = r[lo:hi] if r_for_backward is None else r_for_backward[lo:hi]
+        ds, grad_h13, act_scaled = dswiglu_routed(saved, r_used, score[lo:hi], swiglu_limit)
+        dscore[lo:hi] = ds
+        gh_q, gh_s = quantize_rows(grad_h13)
+        grad_rows[lo:hi] = (dequantize_rows(gh_q, gh_s, gemm_dtype) @ w13).to(torch.bfloat16)
+        if e in keep_weight_grads:
+            tokens_e = token_of_row[lo:hi]
+            dy_rows = grad_output[tokens_e].to(torch.bfloat16).to(gemm_dtype)
+            x_rows = h2[tokens_e].to(torch.bfloat16).to(gemm_dtype)
+            grad_w2[e] = (dy_rows.t() @ act_scaled.to(torch.bfloat16).to(gemm_dtype)).float()
+            grad_w13[e] = (grad_h13.to(torch.bfloat16).to(gemm_dtype).t() @ x_rows).float()
+    output = combine(y, slots, weights, residual)
+    grad_h2 = combine(grad_rows, slots, None, None)
+    grad_route_weights = dscore[slots.reshape(-1).long()].view_as(weights)
+    return dict(weights=weights, ids=ids, order=order, offsets=offsets, slots=slots, h13=h13, y=y,
+                output=output, r=r, grad_rows=grad_rows, grad_h2=grad_h2,
+                grad_route_weights=grad_route_weights, grad_w13=grad_w13, grad_w2=grad_w2)
+
+
+def plain_max_rel(actual, expected, floor=1e-2):
+    """The plain maximum relative error `|a - e| / |e|` over the elements whose magnitude is at
+    least `floor` x rms(e) (elements nearer zero have no meaningful relative error), with the
+    share of elements that takes part. Reported beside `rel_errors`, whose denominator is
+    floored at the tensor's RMS."""
+    a, e = actual.double(), expected.double()
+    rms = e.pow(2).mean().sqrt().clamp_min(1e-30)
+    mask = e.abs() >= floor * rms
+    if not bool(mask.any()):
+        return 0.0, 0.0
+    return ((a - e).abs()[mask] / e.abs()[mask]).max().item(), mask.double().mean().item()

@@ -11,6 +11,7 @@ from the seeded factories in `inputs.py`, and the fixture records their checksum
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -157,4 +158,6 @@ def main(reference_src: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src")
+    if len(sys.argv) < 2 and "MLOPS_REFERENCE_SRC" not in os.environ:
+        raise SystemExit("usage: make_golden.py /path/to/reference/src  (or set MLOPS_REFERENCE_SRC)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["MLOPS_REFERENCE_SRC"])

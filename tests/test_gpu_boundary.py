@@ -1,0 +1,221 @@
+"""The drop-in boundary on a B200.
+
+(1) The opaque-operator contract the reference sets for a provider (`docs/PROVIDERS.md:86-112`,
+checked by its `tests/test_custom_op_contracts.py:830-850`): `torch.library.opcheck` on the
+`b200moe::` operators (schema, autograd registration, fake tensors, AOT dispatch with dynamic
+shapes), functional schemas, FLOP formulas seen by `FlopCounterMode`.
+(2) The reference itself calling this library: `mlops.moe(...)` with the reference's own
+`BlockFP8Weight` containers on CUDA resolves to `b200.moe` (its `capture_dispatch()` says
+so) and the results agree with the CPU oracle and with the reference's native-PyTorch
+provider run on the CPU. The reference comes from `oracle/_ref` (see `oracle/build_ref.py`);
+where it is absent these cases are skipped, the others still run."""
+
+import pytest
+import torch
+
+import inputs
+from oracle import moe_oracle as O
+from oracle.build_ref import reference
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _plain_args(requires_grad=True):
+    from mlops_b200 import ops
+
+    c1 = inputs.config1()
+    x = c1["x"][:128].to(DEV).requires_grad_(requires_grad)
+    router = c1["router"].to(DEV).requires_grad_(requires_grad)
+    w13_q, w13_s = ops.quantize_blocks(c1["w13"].to(DEV))
+    w2_q, w2_s = ops.quantize_blocks(c1["w2"].to(DEV))
+    bias = torch.empty(0, device=DEV)
+    return (x, torch.zeros_like(x), router, w13_q, w2_q, bias, 2, "softmax_then_topk", 1, 1, 1.0, [128],
+            "float32", None, None, [w13_s, w2_s])
+
+
+def test_opcheck_of_the_routed_operator_pair():
+    from mlops_b200 import provider
+
+    # SchemaCheckMode's mutation check does arithmetic on every input, which E4M3 tensors have
+    # no kernels for (the reference drops `test_schema` for its FP8 cases for the same reason)
+    utilities = ("test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic")
+    results = torch.library.opcheck(provider.moe_fwd, _plain_args(), test_utils=utilities)
+    assert set(results.values()) == {"SUCCESS"}, results
+
+    args = _plain_args(requires_grad=False)
+    with torch.no_grad():
+        out = provider.moe_fwd(*args)
+    x, _res, router, w13_q, w2_q = args[:5]
+    dy = torch.randn_like(x)
+    bwd_args = (dy, torch.zeros((), device=DEV), torch.zeros(8, device=DEV), x, router, w13_q, w2_q, *out[4:], 2,
+                "softmax_then_topk", [128], None, None, True, True, False, args[-1])
+    results = torch.library.opcheck(provider.moe_bwd, bwd_args, test_utils=("test_faketensor",))
+    assert set(results.values()) == {"SUCCESS"}, results
+    grads = provider.moe_bwd(*bwd_args)
+    assert grads[4].numel() == 0 and grads[3].shape == w13_q.shape and grads[3].dtype == torch.bfloat16
+
+
+def test_opcheck_of_the_swiglu_operator():
+    from mlops_b200 import provider
+
+    h13 = torch.randn(96, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    for limit in (None, 0.75):
+        results = torch.library.opcheck(
+            provider.swiglu, (h13, limit),
+            test_utils=("test_schema", "test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic"))
+        assert set(results.values()) == {"SUCCESS"}, results
+
+
+def test_opcheck_of_the_lora_operator():
+    from mlops_b200 import lora
+
+    args = list(_plain_args())
+    x, residual, router, w13_q, w2_q, bias = args[:6]
+    g = torch.Generator().manual_seed(9)
+    factors = [(torch.randn(8, 12, 256, generator=g) * 0.02), (torch.randn(8, 1024, 12, generator=g) * 0.01),
+               (torch.randn(8, 12, 512, generator=g) * 0.02), (torch.randn(8, 256, 12, generator=g) * 0.01)]
+    factors = [f.bfloat16().to(DEV).requires_grad_(True) for f in factors]
+    op_args = (x, residual, router, w13_q, w2_q, *factors, bias, 2, "softmax_then_topk", 1.0, 1, 1, 1.0, [128],
+               None, args[-1])
+    results = torch.library.opcheck(
+        lora.moe_lora_fwd, op_args,
+        test_utils=("test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic"))
+    assert set(results.values()) == {"SUCCESS"}, results
+
+
+def test_operator_schemas_are_functional_and_outside_the_reference_namespace():
+    from mlops_b200 import lora, provider  # noqa: F401
+
+    for name in ("moe_fwd", "moe_bwd", "moe_lora_fwd", "moe_lora_bwd", "swiglu", "swiglu_bwd"):
+        schema = getattr(torch.ops.b200moe, name).default._schema
+        assert all(argument.alias_info is None for argument in schema.arguments)
+        assert all(result.alias_info is None for result in schema.returns)
+        assert "!" not in str(schema)
+
+
+def test_flop_counter_sees_18_d_f_per_routed_row():
+    from torch.utils.flop_counter import FlopCounterMode
+
+    from mlops_b200 import provider
+    from mlops_b200.weights import BlockFP8Weight
+
+    c1 = inputs.config1()
+    x = c1["x"].to(DEV).requires_grad_(True)
+    router = c1["router"].to(DEV).requires_grad_(True)
+    w13 = BlockFP8Weight.quantize(c1["w13"].to(DEV)).requires_grad_(True)
+    w2 = BlockFP8Weight.quantize(c1["w2"].to(DEV)).requires_grad_(True)
+    with FlopCounterMode(display=False) as counter:
+        out, *_ = provider.apply(x, torch.zeros_like(x), router, w13, w2, top_k=2, routing_mode="softmax_then_topk")
+        out.backward(c1["dy"].to(DEV))
+    rows, width, inner, experts = 512 * 2, 256, 512, 8
+    projections = 18 * width * inner * rows
+    total = counter.get_total_flops()
+    # projections + router GEMMs (2*T*D*E forward, twice that backward) + elementwise passes
+    assert projections < total < projections * 1.05 + 6 * 512 * width * experts, (total, projections)
+
+
+# ----------------------------------------------------------------- the reference as caller
+def _reference_or_skip():
+    mlops = reference()
+    if mlops is None:
+        pytest.skip("the reference package is not at oracle/_ref (run oracle/build_ref.py)")
+    return mlops
+
+
+def test_reference_dispatch_resolves_to_this_provider_on_cuda():
+    mlops = _reference_or_skip()
+    from mlops.block_fp8 import BlockFP8Weight as ReferenceWeight
+    from mlops.dispatch import capture_dispatch, explain_implementation, use_implementation
+
+    from mlops_b200 import ops, provider
+
+    provider.register()
+    c1 = inputs.config1()
+    x = c1["x"].to(DEV).requires_grad_(True)
+    router = c1["router"].to(DEV).requires_grad_(True)
+    # containers of the reference's own class, quantised by its CPU path and moved over
+    w13c = ReferenceWeight.quantize(c1["w13"])
+    w2c = ReferenceWeight.quantize(c1["w2"])
+    w13 = ReferenceWeight(w13c._data.to(DEV), w13c._scale.to(DEV), dtype=w13c.dtype).requires_grad_(True)
+    w2 = ReferenceWeight(w2c._data.to(DEV), w2c._scale.to(DEV), dtype=w2c.dtype).requires_grad_(True)
+    residual = torch.zeros_like(x)
+    kwargs = dict(top_k=2, routing_mode="softmax_then_topk")
+    explanation = explain_implementation("moe", x, residual, router, w13, w2, **kwargs)
+    assert explanation.candidates["b200.moe"].supported, explanation.candidates["b200.moe"].reason
+    with capture_dispatch() as trace:
+        out, aux, counts, psum = mlops.moe(x, residual, router, w13, w2, **kwargs)
+    assert trace["moe"] == {"b200.moe": 1}, trace
+    dy = c1["dy"].to(DEV)
+    grads = torch.autograd.grad(out, [x, router, w13, w2], dy)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    assert counts.dtype == torch.int64 and int(counts.sum()) == 1024
+    assert all(type(g) is torch.Tensor for g in grads) and grads[2].dtype == torch.bfloat16
+
+    # against the CPU oracle on identical block-FP8 operands
+    w13_q, w13_s = O.quantize_blocks(c1["w13"])
+    w2_q, w2_s = O.quantize_blocks(c1["w2"])
+    logits = O.router_logits(c1["x"], c1["router"])
+    fwd = O.forward_block_fp8(c1["x"], torch.zeros_like(c1["x"]), logits, w13_q, w13_s, w2_q, w2_s, top_k=2,
+                              routing_mode="softmax_then_topk")
+    assert torch.equal(counts.cpu(), torch.bincount(fwd["ids"].reshape(-1).long(), minlength=8))
+    mx, mean = O.rel_errors(out.float().cpu(), fwd["output"].float())
+    assert mx <= 2e-2 and mean <= 2e-3, (mx, mean)
+
+    # against the reference's own native-PyTorch provider on the CPU (bf16 on dequantised
+    # weights), at the reference's FP8-vs-bf16 bounds (tests/test_sonicmoe_block_fp8.py:350)
+    xc = c1["x"].clone().requires_grad_(True)
+    rc = c1["router"].clone().requires_grad_(True)
+    w13c.requires_grad_(True)
+    w2c.requires_grad_(True)
+    with use_implementation("moe", "native_torch.moe"):
+        ref_out, ref_aux, ref_counts, ref_psum = mlops.moe(xc, torch.zeros_like(xc), rc, w13c, w2c,
+                                                           compute_precision="bf16", **kwargs)
+    ref_grads = torch.autograd.grad(ref_out, [xc, rc, w13c, w2c], c1["dy"])
+
+    def frob(a, e):
+        return ((a.double().cpu() - e.double()).norm() / e.double().norm()).item()
+
+    assert torch.equal(counts.cpu(), ref_counts)
+    assert frob(out, ref_out) <= 4.5e-2  # measured 4.4e-2: E4M3 activation noise at this width
+    assert frob(grads[0], ref_grads[0]) < 8e-2 and frob(grads[1], ref_grads[1]) < 8e-2
+    assert frob(grads[2], ref_grads[2]) < 6e-2 and frob(grads[3], ref_grads[3]) < 6e-2
+    torch.testing.assert_close(aux.cpu(), ref_aux, rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(psum.cpu(), ref_psum, rtol=1e-3, atol=1e-3)
+
+
+def test_reference_contexts_reach_the_operator():
+    mlops = _reference_or_skip()
+    from mlops.block_fp8 import BlockFP8Weight as ReferenceWeight
+    from mlops.dispatch.context import weight_gradients_at
+    from mlops.kernels.moe_router import route_weight_precision
+
+    from mlops_b200 import provider
+
+    provider.register()
+    c1 = inputs.config1()
+    x = c1["x"].to(DEV)
+    router = c1["router"].to(DEV).requires_grad_(True)
+    w13c, w2c = ReferenceWeight.quantize(c1["w13"]), ReferenceWeight.quantize(c1["w2"])
+    w13 = ReferenceWeight(w13c._data.to(DEV), w13c._scale.to(DEV), dtype=w13c.dtype).requires_grad_(True)
+    w2 = ReferenceWeight(w2c._data.to(DEV), w2c._scale.to(DEV), dtype=w2c.dtype).requires_grad_(True)
+    kwargs = dict(top_k=2, routing_mode="softmax_then_topk")
+    dy = c1["dy"].to(DEV)
+    out, *_ = mlops.moe(x, torch.zeros_like(x), router, w13, w2, **kwargs)
+    plain = torch.autograd.grad(out, [router, w13], dy)
+    # the contexts are read at apply time and travel as operator arguments; autograd hands a
+    # parameter its gradient at the parameter's dtype, so a bf16-logical container still sees bf16
+    with weight_gradients_at(torch.float32), route_weight_precision("input"):
+        out32, *_ = mlops.moe(x, torch.zeros_like(x), router, w13, w2, **kwargs)
+        same = torch.autograd.grad(out32, [router, w13], dy)
+    assert torch.equal(out, out32)
+    assert same[1].dtype == torch.bfloat16 and torch.equal(same[1], plain[1])
+    torch.testing.assert_close(same[0], plain[0], rtol=1e-2, atol=1e-3)
+    # a container whose logical dtype is fp32 receives the fp32 sums themselves
+    w13_wide = ReferenceWeight(w13c._data.to(DEV), w13c._scale.to(DEV), dtype=torch.float32).requires_grad_(True)
+    out_wide, *_ = mlops.moe(x, torch.zeros_like(x), router, w13_wide, w2, **kwargs)
+    wide = torch.autograd.grad(out_wide, [router, w13_wide], dy)
+    assert torch.equal(out, out_wide)
+    assert wide[1].dtype == torch.float32 and wide[0].dtype == router.dtype
+    assert torch.equal(wide[1].bfloat16(), plain[1])  # the same fp32 sums, rounded later

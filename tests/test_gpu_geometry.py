@@ -1,0 +1,223 @@
+"""Whole-layer parity (forward and every gradient) at the real geometries of the large
+workloads, with the token count reduced until the CPU oracle finishes in well under a minute:
+
+* DeepSeek-V3-shaped: 256 experts, sigmoid scores with a selection bias ~ N(0, 0.1), 8 groups /
+  top-4 groups / top-8 experts, routed scaling 2.5, D = 7168, F = 2048, one shared expert;
+* Mixtral-8x7B-shaped: 8 experts, softmax top-2, D = 4096, F = 14336;
+* Qwen3-30B-A3B-shaped: 128 experts, softmax top-8, D = 2048, F = 768, rank-16 LoRA on a frozen
+  base, expert popularity skewed Zipf(1.2) through the logits.
+
+The kernels see these K / N / group counts in `test_gpu_gemm.py`; here the orchestration does
+(routing with groups, 256-way sort, empty and one-row experts, 56 K blocks per product).
+Expectation: `oracle.moe_oracle.layer_expert_major` (bit-equal to the oracle's forward/backward
+pair, checked on the CPU in `test_oracle_golden.py`). Bounds: integers exact; floating point
+max <= 2e-2 and mean <= 2e-3 in the oracle's metric, and the plain max relative error over the
+elements above 1e-2 x rms is printed beside it (an element a hundred times smaller than its
+tensor's rms has no meaningful relative error; for elements of at least rms size the plain
+relative error is asserted at the same 2e-2)."""
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+MAX_REL, MEAN_REL = 2e-2, 2e-3
+
+report: dict[str, tuple] = {}
+
+
+def _check(actual, expected, what):
+    a, e = actual.float().cpu(), expected.float()
+    mx, mean = O.rel_errors(a, e)
+    plain, share = O.plain_max_rel(a, e)
+    report[what] = (mx, mean, plain, share)
+    typical, _ = O.plain_max_rel(a, e, floor=1.0)
+    print(f"{what}: max {mx:.2e} mean {mean:.2e} | plain |a-e|/|e|: {plain:.2e} over the {share:.1%} of elements "
+          f">= 1e-2 x rms, {typical:.2e} over those >= rms")
+    assert mx <= MAX_REL and mean <= MEAN_REL, (what, mx, mean)
+    assert typical <= MAX_REL, (what, typical)  # elements of typical size or larger: plain relative error
+
+
+def _experts_on_device(experts, inner, width, seed):
+    """Random N(0, 0.02) experts quantised by the library's kernel (bit-exact against the
+    reference's quantiser, see test_gpu_quantize.py) a few experts at a time."""
+    from mlops_b200 import ops
+
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    w13_q = torch.empty((experts, 2 * inner, width), dtype=torch.float8_e4m3fn, device=DEV)
+    w13_s = torch.empty((experts, 2 * inner // 128, width // 128), dtype=torch.float32, device=DEV)
+    w2_q = torch.empty((experts, width, inner), dtype=torch.float8_e4m3fn, device=DEV)
+    w2_s = torch.empty((experts, width // 128, inner // 128), dtype=torch.float32, device=DEV)
+    step = max(1, (1 << 27) // (2 * inner * width))
+    for lo in range(0, experts, step):
+        hi = min(lo + step, experts)
+        w13_q[lo:hi], w13_s[lo:hi] = ops.quantize_blocks(
+            (torch.randn(hi - lo, 2 * inner, width, device=DEV, generator=g) * 0.02).bfloat16())
+        w2_q[lo:hi], w2_s[lo:hi] = ops.quantize_blocks(
+            (torch.randn(hi - lo, width, inner, device=DEV, generator=g) * 0.02).bfloat16())
+    return (w13_q, w13_s), (w2_q, w2_s)
+
+
+def _routed_case(tokens, width, experts, inner, top_k, mode, *, bias=None, n_group=1, topk_group=1, scaling=1.0,
+                 router_std=0.02, seed=0, kept=8):
+    from mlops_b200 import layer, ops
+
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(tokens, width, generator=g).bfloat16()
+    residual = torch.randn(tokens, width, generator=g).bfloat16()
+    dy = torch.randn(tokens, width, generator=g).bfloat16()
+    router = torch.randn(experts, width, generator=g) * router_std
+    w13, w2 = _experts_on_device(experts, inner, width, seed + 1)
+    dev = lambda t: None if t is None else t.to(DEV)  # noqa: E731
+    result = layer.forward_routed(dev(x), dev(residual), dev(router), w13, w2, top_k=top_k, routing_mode=mode,
+                                  router_bias=dev(bias), n_group=n_group, topk_group=topk_group,
+                                  routed_scaling=scaling)
+    output, aux, counts, psum, logits, route_weights, route_ids, order, offsets, slots, h13 = result
+    grads = layer.backward_routed(dev(dy), None, None, dev(x), dev(router), w13, w2, logits, route_weights,
+                                  route_ids, order, offsets, slots, h13, top_k=top_k, routing_mode=mode,
+                                  weight_grad_dtype=torch.float32)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    grad_h2, grad_residual, grad_router, grad_w13, grad_w2 = grads
+    # the backward pass's first product once more (same kernels, same inputs: bit-identical to
+    # what backward_routed formed), so the oracle can differentiate from the very same `r`
+    dy_q, dy_s = ops.quantize_rows(dev(dy), gather=order, gather_div=top_k)
+    r_dev = ops.grouped_gemm_fp8(dy_q, dy_s, *w2, offsets, b_mn_major=True)
+
+    counts_c = counts.cpu()
+    busiest = torch.argsort(counts_c, descending=True)
+    empty = (counts_c == 0).nonzero().flatten().tolist()
+    keep = sorted(set(busiest[:kept // 2].tolist() + busiest[-(kept // 2):].tolist() + empty[:2]))
+    cpu = lambda pair: tuple(t.cpu() for t in pair)  # noqa: E731
+    ref = O.layer_expert_major(
+        x, residual, dy, logits.cpu(), *cpu(w13), *cpu(w2), top_k=top_k, routing_mode=mode, router_bias=bias,
+        n_group=n_group, topk_group=topk_group, routed_scaling=scaling, h13_for_backward=h13.cpu(),
+        r_for_backward=r_dev.cpu(), keep_weight_grads=keep)
+    assert torch.equal(route_ids.cpu(), ref["ids"])
+    assert torch.equal(order.cpu(), ref["order"]) and torch.equal(offsets.cpu(), ref["offsets"])
+    assert torch.equal(slots.cpu(), ref["slots"])
+    assert torch.equal(counts_c, torch.bincount(ref["ids"].reshape(-1).long(), minlength=experts))
+    torch.testing.assert_close(route_weights.cpu(), ref["weights"], rtol=2e-6, atol=1e-7)
+    torch.testing.assert_close(logits.cpu(), O.router_logits(x, router), rtol=1e-4, atol=1e-4)
+    name = f"E{experts}-D{width}-F{inner}"
+    _check(h13, ref["h13"], f"{name} h13")
+    _check(output, ref["output"], f"{name} output")
+    _check(r_dev, ref["r"], f"{name} dy.W2")
+    aux_ref, _, psum_ref = O.routing_statistics(logits.cpu(), ref["ids"], routing_mode=mode, lengths=(tokens,),
+                                                experts=experts)
+    torch.testing.assert_close(aux.cpu(), aux_ref, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(psum.cpu(), psum_ref, rtol=1e-5, atol=1e-5)
+    assert torch.equal(grad_residual.cpu(), dy)
+    grad_logits = layer.routing_gradient(None, None, ref["grad_route_weights"], ref["weights"], ref["ids"],
+                                         logits.cpu(), counts_c, routing_mode=mode, lengths=(tokens,))
+    expected_h2 = ref["grad_h2"].float() + grad_logits.bfloat16().float() @ router.bfloat16().float()
+    _check(grad_h2, expected_h2, f"{name} grad_h2")
+    _check(grad_router, grad_logits.t() @ x.float(), f"{name} grad_router")
+    for e in keep:
+        if int(counts_c[e]) == 0:
+            assert int(torch.count_nonzero(grad_w13[e])) == 0 and int(torch.count_nonzero(grad_w2[e])) == 0
+        else:
+            _check(grad_w13[e], ref["grad_w13"][e], f"{name} grad_w13[{e}] ({int(counts_c[e])} rows)")
+            _check(grad_w2[e], ref["grad_w2"][e], f"{name} grad_w2[{e}] ({int(counts_c[e])} rows)")
+    if empty:  # every expert without rows has exactly zero gradients
+        idx = torch.tensor(empty, device=DEV)
+        assert int(torch.count_nonzero(grad_w13[idx])) == 0 and int(torch.count_nonzero(grad_w2[idx])) == 0
+    return dict(x=x, residual=residual, dy=dy, router=router, w13=w13, w2=w2, output=output, grad_h2=grad_h2)
+
+
+def test_deepseek_v3_geometry_with_group_routing_and_shared_expert():
+    from mlops_b200 import provider
+    from mlops_b200.weights import BlockFP8Weight
+
+    tokens, width, experts, inner = 96, 7168, 256, 2048
+    bias = torch.randn(experts, generator=torch.Generator().manual_seed(11)) * 0.1
+    routing = dict(top_k=8, mode="sigmoid_noaux_tc", bias=bias, n_group=8, topk_group=4, scaling=2.5)
+    case = _routed_case(tokens, width, experts, inner, **routing, seed=40)
+
+    # the shared expert through the provider: (layer with it) - (layer without it) against the
+    # reference's expression for the branch (src/mlops/kernels/moe_reference.py:93-107) in fp32
+    g = torch.Generator().manual_seed(41)
+    sw13 = (torch.randn(2 * inner, width, generator=g) * 0.02).bfloat16()
+    sw2 = (torch.randn(width, inner, generator=g) * 0.02).bfloat16()
+    x = case["x"].to(DEV).requires_grad_(True)
+    sw13_d, sw2_d = sw13.to(DEV).requires_grad_(True), sw2.to(DEV).requires_grad_(True)
+    w13 = BlockFP8Weight(*case["w13"])
+    w2 = BlockFP8Weight(*case["w2"])
+    kwargs = dict(top_k=8, routing_mode="sigmoid_noaux_tc", router_bias=bias.to(DEV), n_group=8, topk_group=4,
+                  routed_scaling=2.5)
+    residual, dy = case["residual"].to(DEV), case["dy"].to(DEV)
+    total, *_ = provider.apply(x, residual, case["router"].to(DEV), w13, w2, shared_w13=sw13_d, shared_w2=sw2_d,
+                               **kwargs)
+    gx, gs13, gs2 = torch.autograd.grad(total, [x, sw13_d, sw2_d], dy)
+    zero = torch.zeros_like(residual)
+    with_shared, *_ = provider.apply(x, zero, case["router"].to(DEV), w13, w2, shared_w13=sw13_d, shared_w2=sw2_d,
+                                     **kwargs)
+    routed_only, *_ = provider.apply(x, zero, case["router"].to(DEV), w13, w2, **kwargs)
+    def branch(h):  # the reference's shared branch evaluated by PyTorch on the device
+        h13 = torch.nn.functional.linear(h, sw13_d)
+        act = torch.nn.functional.silu(h13[:, :inner].float()).to(h.dtype) * h13[:, inner:]
+        return torch.nn.functional.linear(act, sw2_d)
+
+    x_ref = case["x"].to(DEV).requires_grad_(True)
+    shared = branch(x_ref)
+    ref_grads = torch.autograd.grad(shared, [x_ref, sw13_d, sw2_d], dy)
+    mx, mean = O.rel_errors((with_shared.float() - routed_only.float()).cpu(), shared.detach().float().cpu())
+    assert mx <= 3e-2 and mean <= 3e-3, (mx, mean)  # a bf16 sum and a bf16 difference apart
+    for actual, expected, what in ((gs13, ref_grads[1], "shared grad_w13"), (gs2, ref_grads[2], "shared grad_w2"),
+                                   (gx.float() - case["grad_h2"].float(), ref_grads[0], "shared grad_x")):
+        mx, mean = O.rel_errors(actual.float().cpu(), expected.float().cpu())
+        assert mx <= 3e-2 and mean <= 3e-3, (what, mx, mean)
+
+
+def test_mixtral_8x7b_geometry():
+    _routed_case(192, 4096, 8, 14336, 2, "softmax_then_topk", seed=50, kept=4)
+
+
+def test_qwen3_30b_a3b_geometry_with_lora_and_zipf_skew():
+    from mlops_b200 import ops
+    from mlops_b200.lora import expert_lora
+    from mlops_b200.weights import BlockFP8Weight
+
+    tokens, width, experts, inner, top_k, rank = 512, 2048, 128, 768, 8, 16
+    g = torch.Generator().manual_seed(60)
+    x = torch.randn(tokens, width, generator=g).bfloat16()
+    residual = torch.randn(tokens, width, generator=g).bfloat16()
+    dy = torch.randn(tokens, width, generator=g).bfloat16()
+    router = torch.randn(experts, width, generator=g) * 0.02
+    # the skew lives in the data: x[:, 0] = 1 and Wr[:, 0] = log p_e shift every logit by log p_e
+    popularity = torch.arange(1, experts + 1).float().pow(-1.2)
+    router[:, 0] = torch.log(popularity / popularity.sum())
+    x[:, 0] = 1.0
+    factors = [(torch.randn(experts, rank, width, generator=g) * 0.02).bfloat16(),
+               (torch.randn(experts, 2 * inner, rank, generator=g) * 0.01).bfloat16(),
+               (torch.randn(experts, rank, inner, generator=g) * 0.02).bfloat16(),
+               (torch.randn(experts, width, rank, generator=g) * 0.01).bfloat16()]
+    w13, w2 = _experts_on_device(experts, inner, width, 61)
+    x_d = x.to(DEV).requires_grad_(True)
+    f_d = [f.to(DEV).requires_grad_(True) for f in factors]
+    out, aux, counts, _psum = expert_lora(x_d, residual.to(DEV), router.to(DEV), BlockFP8Weight(*w13),
+                                          BlockFP8Weight(*w2), *f_d, top_k=top_k,
+                                          routing_mode="softmax_then_topk", scale=1.0)
+    grads = torch.autograd.grad(out, [x_d, *f_d], dy.to(DEV))
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    counts_c = counts.cpu()
+    assert int(counts_c.max()) > 8 * int(counts_c.float().mean())  # the load really is skewed
+
+    cpu = lambda pair: tuple(t.cpu() for t in pair)  # noqa: E731
+    logits = O.router_logits(x, router)
+    fwd = O.forward_lora_block_fp8(x, residual, logits, *cpu(w13), *cpu(w2), *factors, top_k=top_k,
+                                   routing_mode="softmax_then_topk", scale=1.0)
+    assert torch.equal(counts_c, torch.bincount(fwd["ids"].reshape(-1).long(), minlength=experts))
+    _check(out, fwd["output"], "E128-lora output")
+    bwd = O.backward_lora_block_fp8(dy, fwd, *cpu(w13), *cpu(w2), *factors, top_k=top_k, scale=1.0)
+    grad_logits_part = grads[0].float().cpu()  # expert part + router part; the oracle gives the former
+    from mlops_b200 import layer
+    grad_logits = layer.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"], logits,
+                                         counts_c, routing_mode="softmax_then_topk", lengths=(tokens,))
+    expected = bwd["grad_h2"].float() + grad_logits.bfloat16().float() @ router.bfloat16().float()
+    _check(grad_logits_part, expected, "E128-lora grad_x")
+    for name, actual in zip(("a13", "b13", "a2", "b2"), grads[1:]):
+        _check(actual, bwd["grad_" + name], f"E128-lora grad_{name}")

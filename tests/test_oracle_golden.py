@@ -194,3 +194,23 @@ def test_lora_restatement_against_reference_builtin(golden):
     same = O.forward_lora_block_fp8(lc["x"], lc["residual"], logits, *w13, *w2, lc["a13"], zero13, lc["a2"], zero2,
                                     top_k=lc["top_k"], routing_mode=lc["routing_mode"], scale=lc["scale"])
     assert torch.equal(same["output"], plain["output"])
+
+
+def test_expert_major_layer_equals_the_forward_backward_pair():
+    """`layer_expert_major` (one dequantisation per expert, for layers with hundreds of large
+    experts) is the same computation as `forward_block_fp8` + `backward_block_fp8`: bit-equal."""
+    c1 = inputs.config1()
+    w13, w2 = O.quantize_blocks(c1["w13"]), O.quantize_blocks(c1["w2"])
+    logits = O.router_logits(c1["x"], c1["router"])
+    kw = dict(top_k=2, routing_mode="softmax_then_topk")
+    fwd = O.forward_block_fp8(c1["x"], c1["residual"], logits, *w13, *w2, gemm_dtype=torch.float32, **kw)
+    bwd = O.backward_block_fp8(c1["dy"], c1["x"], fwd, *w13, *w2, top_k=2, gemm_dtype=torch.float32)
+    both = O.layer_expert_major(c1["x"], c1["residual"], c1["dy"], logits, *w13, *w2, keep_weight_grads=range(8), **kw)
+    for key in ("ids", "order", "offsets", "slots", "h13", "y", "output"):
+        assert torch.equal(both[key], fwd[key]), key
+    for key in ("r", "grad_rows", "grad_h2", "grad_route_weights"):
+        assert torch.equal(both[key], bwd[key]), key
+    for e in range(8):
+        assert torch.equal(both["grad_w13"][e], bwd["grad_w13"][e]) and torch.equal(both["grad_w2"][e], bwd["grad_w2"][e])
+    plain, share = O.plain_max_rel(fwd["output"].float() * (1 + 1e-3), fwd["output"].float())
+    assert abs(plain - 1e-3) < 1e-4 and share > 0.9

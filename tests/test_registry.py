@@ -1,22 +1,17 @@
-"""The provider against the reference's own registry (CPU, needs the reference's sources;
-skipped where they are absent, e.g. on the GPU machine). Mirrors the rules the reference
+"""The provider against the reference's own registry (CPU, needs the reference package, which
+`oracle/build_ref.py` puts at `oracle/_ref`, or `$MLOPS_REFERENCE_SRC`; skipped where absent). Mirrors the rules the reference
 tests in tests/test_implementation_registry.py: registration, duplicate ids, priority
 selection, refusal reasons, forced selection of an unsupported implementation."""
-
-import os
-import sys
-from pathlib import Path
 
 import pytest
 import torch
 
-REFERENCE_SRC = Path(os.environ.get("MLOPS_REFERENCE_SRC", "/root/reference/src"))
-if not (REFERENCE_SRC / "mlops").exists():
-    pytest.skip("reference sources not present", allow_module_level=True)
-sys.dont_write_bytecode = True
-sys.path.insert(0, str(REFERENCE_SRC))
+from oracle.build_ref import reference
 
-import mlops  # noqa: E402
+mlops = reference()
+if mlops is None:
+    pytest.skip("reference package not present", allow_module_level=True)
+
 from mlops.block_fp8 import BlockFP8Weight  # noqa: E402
 from mlops.dispatch import explain_implementation, resolve_implementation, use_implementation  # noqa: E402
 from mlops.dispatch.registry import implementations_for, register_implementation  # noqa: E402
