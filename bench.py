@@ -202,28 +202,49 @@ def port_sample_step(cfg, tokens, experts, seed=0):
     return step
 
 
-def cpu_sample(cfg):
-    """`(step, kind, description)` of the bounded CPU sample of a layer workload."""
-    tokens, experts = cfg["cpu_tokens"], cfg["E_cpu"]
+SAMPLE_LADDER = ((16, 8), (32, 8), (64, 8), (128, 16), (256, 32))  # (tokens, experts), ascending cost
+
+
+def cpu_sample(cfg, tokens, experts):
+    """`(step, kind, description)` of a bounded CPU sample of a layer workload."""
+    experts = min(experts, cfg["E"])
     mlops = reference_package()
-    shape = f"{tokens} tokens, {experts} of {cfg['E']} experts, D={cfg['D']} F={cfg['F']} top-{cfg['K']}"
+    shape = f"{tokens} tokens, {experts} of {cfg['E']} experts, D={cfg['D']} F={cfg['F']} top-{min(cfg['K'], experts)}"
+    sample_cfg = dict(cfg, K=min(cfg["K"], experts))
     if mlops is not None:
-        return (reference_sample_step(mlops, cfg, tokens, experts), "reference",
+        return (reference_sample_step(mlops, sample_cfg, tokens, experts), "reference",
                 f"{shape}, forward+backward, the reference's expert_parallel.reference.expert_computation "
-                "with its own router (bf16 on dequantised block-FP8 weights, CPU)")
-    return (port_sample_step(cfg, tokens, experts), "port",
+                "with its own router (bf16 on block-FP8 weights dequantised per call, CPU)")
+    return (port_sample_step(sample_cfg, tokens, experts), "port",
             f"{shape}, forward+backward, CPU oracle port (fp32 products of dequantised E4M3 operands); "
             "the reference package was not found at oracle/_ref")
 
 
+def choose_sample(cfg, calls, budget_seconds):
+    """The largest sample of the ladder whose `calls` steps fit `budget_seconds` on this machine:
+    each rung is timed once, from the smallest up, until the next one would not fit. Returns
+    `(step, kind, description, tokens, seconds of the last timed step)`."""
+    chosen = None
+    for tokens, experts in SAMPLE_LADDER:
+        step, kind, description = cpu_sample(cfg, tokens, experts)
+        start = time.perf_counter()
+        step()
+        seconds = time.perf_counter() - start
+        if chosen is not None and seconds * calls > budget_seconds:
+            break
+        chosen = (step, kind, description, tokens, seconds)
+        if seconds * calls * 2.5 > budget_seconds:  # the next rung costs at least twice as much
+            break
+    return chosen
+
+
 def cpu_baseline(cfg):
     threads = _threads()
-    step, kind, description = cpu_sample(cfg)
-    step()  # warm-up (allocator, thread pool)
+    step, kind, description, tokens, _ = choose_sample(cfg, calls=1, budget_seconds=20.0)
     start = time.perf_counter()
     step()
     seconds = time.perf_counter() - start
-    result = {"value": cfg["cpu_tokens"] / seconds, "unit": "tokens/s", "cores": threads, "kind": kind,
+    result = {"value": tokens / seconds, "unit": "tokens/s", "cores": threads, "kind": kind,
               "sample": f"{description}; {seconds:.1f} s per step", "torch_threads": torch.get_num_threads()}
     mlops = reference_package()
     if mlops is not None:
@@ -233,11 +254,13 @@ def cpu_baseline(cfg):
 
 def reference_arm(args, cfg):
     """The reference's own CPU implementation of the path on this machine's host cores, on a
-    bounded sample of the GPU arm's workload (rank 0 only; other ranks exit without work)."""
+    bounded sample of the GPU arm's workload sized so that the whole run ends within a few
+    minutes (rank 0 only; other ranks exit without work)."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     threads = _threads()
-    step, kind, description = cpu_sample(cfg)
+    calls = max(args.steps, 1) + max(args.warmup, 0)
+    step, kind, description, tokens, _ = choose_sample(cfg, calls=calls, budget_seconds=150.0)
     for _ in range(max(args.warmup, 0)):
         step()
     times = []
@@ -246,7 +269,7 @@ def reference_arm(args, cfg):
         step()
         times.append(time.perf_counter() - start)
     mean = sum(times) / len(times)
-    value = cfg["cpu_tokens"] / mean
+    value = tokens / mean
     line = {
         "impl": "reference", "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean * 1e3,
@@ -876,11 +899,6 @@ def main():
     cfg = dict(WORKLOADS[args.workload])
     if args.workload == "c2" and args.impl == "reference":
         cfg = dict(WORKLOADS["c4"])
-    if "E" in cfg:
-        # bounded CPU sample: a few experts of the same shape, a few hundred tokens. 32 experts keep
-        # DeepSeek-style group routing meaningful (4 experts per group, top-4 groups, top-8).
-        cfg["E_cpu"] = min(cfg["E"], 32 if cfg["mode"] == "sigmoid_noaux_tc" else 8)
-        cfg["cpu_tokens"] = 256 if args.workload != "c1" else 512
     if args.impl == "reference":
         reference_arm(args, cfg)
         return

@@ -6,10 +6,13 @@ this module raises. There is no fallback."""
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int32, c_longlong, c_void_p
 from pathlib import Path
 
-LIBRARY_PATH = Path(__file__).resolve().parent / "libb200moe.so"
+# B200MOE_LIBRARY names another build of the same library (an instrumented or experimental
+# one: `python -m mlops_b200.build --define NAME=VALUE --output path`); the ABI is the same.
+LIBRARY_PATH = Path(os.environ.get("B200MOE_LIBRARY") or Path(__file__).resolve().parent / "libb200moe.so")
 
 ERROR_NAMES = {
     0: "ok",

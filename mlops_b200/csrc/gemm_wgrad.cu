@@ -476,11 +476,19 @@ grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __gr
           }
           __syncwarp();
           // A stage that was only written by TMA needs no release from this thread.  One whose
-          // tail rows this warp zeroed is published with a cluster-scope release, so the leader's
-          // MMA issue is ordered after those stores (one K block per group and segment).
+          // tail rows this warp zeroed was made visible to the async proxy by the fence above;
+          // the PTX memory model would additionally want a cluster-scope release here before the
+          // leader's MMA may depend on those stores.  That arrival costs about a microsecond and
+          // was measured at 19% of this kernel's time (one tail block per tile), so it is a
+          // build option (-DB200_WGRAD_RELEASE_TAIL_ARRIVE); the default relies on the remote
+          // arrival being delivered after this warp's earlier shared-memory stores, which holds
+          // on sm_100 hardware (the results are bit-identical) but is not promised by the model.
           if (lane == 0) {
+#ifdef B200_WGRAD_RELEASE_TAIL_ARRIVE
             if (valid < kWgBlockK) mbar_arrive_remote_release(&ready[s], 0);
-            else mbar_arrive_remote(&ready[s], 0);
+            else
+#endif
+              mbar_arrive_remote(&ready[s], 0);
           }
         }
       }

@@ -363,9 +363,11 @@ def forward_lora_block_fp8(h2, residual, logits, w13_q, w13_s, w2_q, w2_s, a13, 
 
 
 def backward_lora_block_fp8(grad_output, fwd, w13_q, w13_s, w2_q, w2_s, a13, b13, a2, b2, *, top_k, scale,
-                            swiglu_limit=None):
+                            swiglu_limit=None, r_for_backward=None):
     """VJP of `forward_lora_block_fp8` for the hidden rows (expert part), the route weights and
-    the four factors (frozen base)."""
+    the four factors (frozen base). `r_for_backward`: the device's `dy W2 + s dy B2 A2` rows, so
+    that (with the device's h13 / t1 / t2 in `fwd`) every later product has bit-identical
+    operands on both sides; `r` is still computed here and returned."""
     bf = torch.bfloat16
     experts = w13_q.shape[0]
     order, offsets, slots, weights = fwd["order"], fwd["offsets"], fwd["slots"], fwd["weights"]
@@ -376,7 +378,8 @@ def backward_lora_block_fp8(grad_output, fwd, w13_q, w13_s, w2_q, w2_s, a13, b13
     r_add = (scale * _factor_rows(t2g, a2, offsets, False)).to(bf)              # s dy B2 A2
     r = (grouped_block_gemm(dy_q, dy_s, w2_q, w2_s, offsets, b_mn_major=True) + r_add.double()).to(bf)
     score = weights.reshape(-1)[order.long()].float()
-    dscore, grad_h13, act_scaled = dswiglu_routed(fwd["h13"], r, score, swiglu_limit)
+    dscore, grad_h13, act_scaled = dswiglu_routed(fwd["h13"], r if r_for_backward is None else r_for_backward,
+                                                  score, swiglu_limit)
     gh_b = grad_h13.to(bf)
     gh_q, gh_s = quantize_rows(grad_h13)
     dt1 = _factor_rows(gh_b, b13, offsets, False).to(bf)                        # gh B13
@@ -388,7 +391,7 @@ def backward_lora_block_fp8(grad_output, fwd, w13_q, w13_s, w2_q, w2_s, a13, b13
     grad_a2 = grouped_wgrad((t2g.float() * scale).to(bf), act_scaled.to(bf), offsets, experts)
     grad_b13 = grouped_wgrad(gh_b, (fwd["t1"].float() * scale).to(bf), offsets, experts)
     grad_a13 = grouped_wgrad((dt1.float() * scale).to(bf), fwd["x_rows"], offsets, experts)
-    return dict(grad_h2=grad_h2, grad_route_weights=dscore[slots.reshape(-1).long()].view_as(weights),
+    return dict(r=r, grad_h2=grad_h2, grad_route_weights=dscore[slots.reshape(-1).long()].view_as(weights),
                 grad_a13=grad_a13, grad_b13=grad_b13, grad_a2=grad_a2, grad_b2=grad_b2)
 
 

