@@ -57,6 +57,38 @@ int b200moe_route_topk(const float* logits, long long ld, int tokens, int expert
                        float* weights, int32_t* ids, void* stream);
 
 /*
+ * Column sums of the per-token routing probabilities of fp32 logits [tokens, experts] (row pitch
+ * ld): softmax of the logits (modes TOPK_THEN_SOFTMAX, SOFTMAX_THEN_TOPK) or sigmoid scores
+ * normalised per token (SIGMOID_NOAUX_TC) -> probability_sum fp32 [experts].  Formed in a fixed
+ * order (bitwise repeatable).  `workspace` holds
+ * b200moe_routing_probability_sum_workspace_bytes(...) bytes.  experts <= 1024.
+ * Reference: src/mlops/providers/moe_common.py:32-71 (`routing_statistics`: `probability_sum`;
+ * the auxiliary loss is [experts]-sized arithmetic on it and on the sort's counts).
+ */
+long long b200moe_routing_probability_sum_workspace_bytes(long long tokens, int experts);
+int b200moe_routing_probability_sum(const float* logits, long long ld, long long tokens, int experts, int mode,
+                                    void* workspace, float* probability_sum, void* stream);
+
+/*
+ * Gradient of the logits (fp32 [tokens, experts], pitch ldg) from the cotangents of
+ *   the route weights   grad_route_weights fp32 [tokens, top_k] (with ids and, except in mode
+ *                       SOFTMAX_THEN_TOPK, the route weights themselves),
+ *   the auxiliary loss  grad_aux (device scalar, NULL for none) with frequency fp32 [experts] and
+ *                       aux_scale: experts / tokens_total for the softmax modes, 1 / tokens of the
+ *                       sequence for the sigmoid mode (call once per sequence, with that sequence's
+ *                       rows and frequency),
+ *   the probability sum grad_probability_sum fp32 [experts] (NULL for none).
+ * Reference: src/mlops/providers/moe_common.py:74-124 (`routing_gradient`),
+ * src/mlops/kernels/moe_router.py:403-502 (`route_backward`, `add_aux_gradient_`,
+ * `add_sequence_aux_gradient_`).
+ */
+int b200moe_routing_gradient(const float* logits, long long ld, long long tokens, int experts, int top_k,
+                             int mode, const int32_t* ids, const float* route_weights,
+                             const float* grad_route_weights, const float* grad_aux, const float* frequency,
+                             float aux_scale, const float* grad_probability_sum, float* grad_logits,
+                             long long ldg, void* stream);
+
+/*
  * Stable sort of the flat ids [assignments] by expert:
  *   order [assignments] int32, offsets [experts + 1] int32, slots [assignments] int32,
  *   counts64 [experts] int64 (may be NULL).
@@ -102,6 +134,21 @@ int b200moe_quantize_rows(const void* x, long long ldx, long long src_rows, cons
                           int gather_div, long long rows, int width, void* q, long long ldq, float* scales,
                           long long scale_row_stride, long long scale_block_stride, int mode, void* copy,
                           long long ldc, int32_t* status, void* stream);
+
+/*
+ * The gathered quantisation from the token's side: row t of x [tokens, width] is quantised once
+ * (1x128 scales) and written to each of the `fanout` output rows slots[t * fanout + k]
+ * (k < fanout <= 32; a slot outside [0, rows_out) is reported in `status` and skipped).  With
+ * slots = the sort's inverse permutation this gives exactly the bytes and scales of
+ * b200moe_quantize_rows with gather = order, gather_div = fanout, for 1/fanout of the
+ * arithmetic and source reads.  `copy` (optional) receives the bf16 rows the same way.
+ * Reference: src/mlops/kernels/quack_moe/quantize_rows.py:140-207 (`quantize_rows_fp8` with
+ * `gather`), whose result it reproduces.
+ */
+int b200moe_quantize_rows_scatter(const void* x, long long ldx, long long tokens, const int32_t* slots,
+                                  int fanout, long long rows_out, int width, void* q, long long ldq,
+                                  float* scales, long long scale_row_stride, long long scale_block_stride,
+                                  void* copy, long long ldc, int32_t* status, void* stream);
 
 /*
  * SwiGLU of h13 = [gate | up] (bf16 [rows, 2*width]) computed in fp32 and rounded once
@@ -243,6 +290,19 @@ int b200moe_finish_combine(const float* sums, long long lds, const void* residua
  * way (src/mlops/expert_parallel/quack/config.py, `num_sms`).
  */
 int b200moe_set_cta_limit(int ctas);
+
+/*
+ * Which form of the wide-tile FP8 GEMM serves b200moe_grouped_gemm_fp8[_scatter]:
+ *   mode -1 (default), 0  the single-CTA form (tiles drawn from a counter: CTAs that start late,
+ *                         because a collective holds their SM, take fewer tiles)
+ *   mode  1               the CTA-pair form (clusters of two CTAs on a 256 x 256 tile,
+ *                         tcgen05.mma.cta_group::2, tiles assigned by pair index) whenever it can
+ *                         serve the call (block_n 256, no CTA limit)
+ * Both forms give bit-identical results; the single-CTA form measured faster at every shape tried,
+ * so the pair form is opt-in.  Process-wide, like b200moe_set_cta_limit.  The reference picks its
+ * tile shapes per token bucket in the same spirit (src/mlops/kernels/quack_moe/policy.py:52-150).
+ */
+int b200moe_set_gemm_pair(int mode);
 
 /*
  * Rank-r side products of expert LoRA on expert-sorted rows (rank <= 64, bf16, fp32 sums).

@@ -32,10 +32,14 @@ F = c_float
 # name -> (restype, argtypes); one entry per declaration in include/b200moe.h
 SIGNATURES = {
     "b200moe_route_topk": (I, [P, LL, I, I, I, I, P, I, I, F, P, P, P]),
+    "b200moe_routing_probability_sum_workspace_bytes": (LL, [LL, I]),
+    "b200moe_routing_probability_sum": (I, [P, LL, LL, I, I, P, P, P]),
+    "b200moe_routing_gradient": (I, [P, LL, LL, I, I, I, P, P, P, P, P, F, P, P, LL, P]),
     "b200moe_sort_assignments_workspace_bytes": (LL, [LL, I]),
     "b200moe_sort_assignments": (I, [P, LL, I, P, P, P, P, P, P, P]),
     "b200moe_sort_assignments_static": (I, [P, LL, I, P, P, P, P, P, P]),
     "b200moe_quantize_rows": (I, [P, LL, LL, P, I, LL, I, P, LL, P, LL, LL, I, P, LL, P, P]),
+    "b200moe_quantize_rows_scatter": (I, [P, LL, LL, P, I, LL, I, P, LL, P, LL, LL, P, LL, P, P]),
     "b200moe_swiglu_quantize": (I, [P, LL, LL, I, P, LL, P, LL, LL, P, LL, F, I, P]),
     "b200moe_dswiglu_routed": (
         I,
@@ -61,6 +65,7 @@ SIGNATURES = {
     "b200moe_finish_combine": (I, [P, LL, P, LL, P, LL, LL, I, P]),
     "b200moe_grouped_wgrad_bf16": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, P, P]),
     "b200moe_set_cta_limit": (I, [I]),
+    "b200moe_set_gemm_pair": (I, [I]),
     "b200moe_lora_project": (I, [P, LL, P, I, P, I, LL, I, I, P, LL, P]),
     "b200moe_lora_expand": (I, [P, LL, P, I, P, I, LL, I, I, F, P, LL, P]),
     "b200moe_combine": (I, [P, LL, LL, P, P, P, LL, P, LL, LL, I, I, P]),

@@ -281,6 +281,15 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                               uint32_t accumulate) {
   asm volatile(
@@ -324,18 +333,22 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 // TMA load with CU_TENSOR_MAP_SWIZZLE_128B produces; tile base 1024-byte aligned).
 //   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
 //   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1 (Blackwell)
-//   bits [61,64) layout type, 2 = SWIZZLE_128B
+//   bits [61,64) layout type, 2 = SWIZZLE_128B, 4 = SWIZZLE_64B
 // K-major tile (rows of 128 bytes along K): stride offset = 8 rows = 1024 bytes.
 // MN-major tile (rows of 128 bytes along M/N, one row per K index): stride offset =
 // 8 K-rows = 1024 bytes, leading offset = distance between 128-byte-wide column panels.
+// With SWIZZLE_64B the rows are 64 bytes (what a TMA load with CU_TENSOR_MAP_SWIZZLE_64B
+// produces; tile base 512-byte aligned) and 8 of them are 512 bytes.
+constexpr uint32_t kLayoutSwizzle128 = 2, kLayoutSwizzle64 = 4;
 __host__ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                            uint32_t sbo_bytes) {
+                                                            uint32_t sbo_bytes,
+                                                            uint32_t layout = kLayoutSwizzle128) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout << 61;
   return d;
 }
 

@@ -28,6 +28,7 @@
 #include "common.cuh"
 #include "host_util.h"
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -51,6 +52,25 @@ constexpr uint32_t kAccBarrierThreads = (8 + 1) * 32;  // eight epilogue warps a
 // the tiles by CTA index instead.
 constexpr int kSchedSlots = 64;
 __device__ int g_tile_counter[kSchedSlots][2];
+
+// In-kernel cycle counters (build with -DB200_GEMM_TRACE=1, see mlops_b200/build.py): CTA 0
+// writes clock64() stamps of its roles for K blocks [kTraceFirst, kTraceFirst + kTraceIts) into
+// a buffer handed over with b200moe_debug_set_gemm_trace: trace[slot][it - first][field].
+//   slot 0 / 1  issuer of the even / odd K blocks: 0 loop top, 1 operands seen, 2 slab 0 free,
+//               3 slab 0 issued, 4 slab 1 free, 5 slab 1 issued
+//   slot 2 / 3  epilogue warp 4 (columns 0-127) / warp 8 (128-255): 0 waiting for the slab,
+//               1 slab complete seen, 2 last TMEM load landed, 3 promoted and handed back
+//   slot 4      producer: 0 waiting for the stage, 1 stage free (loads issued next)
+#ifdef B200_GEMM_TRACE
+constexpr int kTraceFirst = 64, kTraceIts = 64, kTraceFields = 8, kTraceSlots = 5;
+#define B200_TRACE(slot, it, field)                                                                    \
+  do {                                                                                                 \
+    if (p.trace != nullptr && blockIdx.x == 0 && (int)(it) >= kTraceFirst && (int)(it) < kTraceFirst + kTraceIts) \
+      p.trace[(((slot) * kTraceIts) + ((int)(it) - kTraceFirst)) * kTraceFields + (field)] = clock64();  \
+  } while (0)
+#else
+#define B200_TRACE(slot, it, field) do {} while (0)
+#endif
 
 struct GemmFp8Params {
   const float* a_scale;
@@ -80,16 +100,24 @@ struct GemmFp8Params {
   long long out_rows;  // rows of d (row_map) or of out_f32 (row_token): targets outside are skipped
   int sched_slot;      // slot of g_tile_counter, or -1: tiles by CTA index
   int* status;
+#ifdef B200_GEMM_TRACE
+  long long* trace;
+#endif
 };
 
-template <int BLOCK_N>
+// PAIR: the two CTAs of a cluster share a 256-row x 256-column tile (tcgen05.mma.cta_group::2).
+// CTA r holds rows [128 r, 128 r + 128) of A and, of each 128-column half of B, the 64 columns
+// [64 r, 64 r + 64): every operand byte is written to shared memory once per pair (32 KB per
+// CTA and K block instead of 48 KB), and a CTA's half of B is read once for both tensor cores.
+template <int BLOCK_N, bool PAIR = false>
 struct GemmCfg {
-  static constexpr int kStages = BLOCK_N == 128 ? 6 : 4;
+  static constexpr int kStages = (PAIR || BLOCK_N == 128) ? 6 : 4;
+  static constexpr int kTileM = PAIR ? 2 * kBlockM : kBlockM;
   static constexpr int kABytes = kBlockM * kBlockK;
-  static constexpr int kBBytes = BLOCK_N * kBlockK;
+  static constexpr int kBBytes = (PAIR ? BLOCK_N / 2 : BLOCK_N) * kBlockK;
   static constexpr int kTmemCols = 2 * BLOCK_N;
   static constexpr int kTileBytes = kStages * (kABytes + kBBytes);
-  static constexpr int kBarBytes = 384;
+  static constexpr int kBarBytes = 512;
   static constexpr int kSchedBytes = (2 * (kMaxGroups + 1) * 4 + 15) / 16 * 16;
   static constexpr int kStoreBytes = 8 * 32 * 80;  // per-warp transpose buffers of the epilogue
   static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + kStoreBytes + 1024;
@@ -101,7 +129,7 @@ struct TileCoord {
 
 // m_tile_start[g] = number of M tiles in groups < g; offs[g] = first row of group g.
 __device__ __forceinline__ TileCoord locate_m_tile(int mt, const int* m_tile_start, const int* offs,
-                                                   int groups) {
+                                                   int groups, int tile_m = kBlockM) {
   int lo = 0, hi = groups - 1;
   while (lo < hi) {
     int mid = (lo + hi + 1) >> 1;
@@ -111,8 +139,8 @@ __device__ __forceinline__ TileCoord locate_m_tile(int mt, const int* m_tile_sta
   // the last group whose start <= mt, which is the one that owns the tile.
   TileCoord c;
   c.group = lo;
-  c.m0 = offs[lo] + (mt - m_tile_start[lo]) * kBlockM;
-  c.rows_valid = min(kBlockM, offs[lo + 1] - c.m0);
+  c.m0 = offs[lo] + (mt - m_tile_start[lo]) * tile_m;
+  c.rows_valid = min(tile_m, offs[lo + 1] - c.m0);
   return c;
 }
 
@@ -121,13 +149,24 @@ __device__ __forceinline__ TileCoord locate_m_tile(int mt, const int* m_tile_sta
 // mbarrier and its own hardware barrier for the release.  A half is drained by the four
 // epilogue warps that own its columns, so the retire -> drain -> release -> reissue loop of
 // one half runs beside the multiplication of the other three halves in flight.
-template <int BLOCK_N, bool B_MN_MAJOR, int EPI, bool SPLIT = false>
+//
+// PAIR (with SPLIT): a cluster of two CTAs works on a 256 x 256 tile.  The leader CTA (cluster
+// rank 0) issues every multiplication for both (tcgen05.mma.cta_group::2, M = 256, N = 128 per
+// half); each CTA loads its own operands, drains its own 128 rows of the four accumulator
+// slabs (2 buffers x 2 halves, all 512 TMEM columns) and stores them.  What crosses the pair:
+// "my stage has landed" (a remote mbarrier arrival by warp 2 of each CTA), "this slab is
+// drained" (remote arrivals by the epilogue warps on the leader's `tempty`), and the commits of
+// the multiplications, which arrive on the barriers of both CTAs.  Four slabs in flight hide the
+// retire -> drain -> release round trip behind the other three; half the B traffic per CTA
+// leaves shared-memory bandwidth for it.  Tiles are assigned by pair index (no shared counter).
+template <int BLOCK_N, bool B_MN_MAJOR, int EPI, bool SPLIT = false, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const __grid_constant__ CUtensorMap tmap_b, const GemmFp8Params p) {
-  using Cfg = GemmCfg<BLOCK_N>;
+  using Cfg = GemmCfg<BLOCK_N, PAIR>;
   constexpr int kStages = Cfg::kStages;
   static_assert(!SPLIT || (BLOCK_N == 256 && EPI != 1), "the split issue is for the plain 256-wide tile");
+  static_assert(!PAIR || (BLOCK_N == 256 && EPI == 0), "the pair form is the 256-wide tile with the plain store");
   constexpr int kHalves = SPLIT ? 2 : 1;  // separately released parts of an accumulator buffer
   // hardware barrier of (buffer, half); its participants: the warps that drain it and its issuer
   constexpr uint32_t kRelThreads = SPLIT ? (4 + 1) * 32 : kAccBarrierThreads;
@@ -146,7 +185,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* amax_bar = bars + 2 * kStages + 6;  // [4] row-quarter pairs of the fused SwiGLU epilogue
   uint64_t* sched_full = bars + 2 * kStages + 10;   // [4] ring of tile ids: slot published
   uint64_t* sched_empty = bars + 2 * kStages + 14;  // [4] ... and read by every consumer
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 18);
+  uint64_t* ready = bars + 2 * kStages + 18;        // [kStages] pair leader: both CTAs' stage landed
+  uint64_t* tempty = bars + 3 * kStages + 18;       // [4] pair leader: slab drained by both CTAs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 22);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* total_m_tiles_s = abort_flag + 1;
   int* sched_tile = total_m_tiles_s + 1;  // [4]
@@ -157,6 +198,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   const int groups = p.groups;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int rank = PAIR ? (int)cluster_ctarank() : 0;  // 0: the CTA that issues the multiplications
+  const bool leader = rank == 0;
   // EPI == 1: a tile is 128 gate columns and the 128 up columns that go with them
   const int half_n = p.N / 2;
   const int num_n_tiles = EPI == 1 ? half_n / 128 : (p.N + BLOCK_N - 1) / BLOCK_N;
@@ -173,7 +216,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int i = 0; i < 4; ++i) mbar_init(&amax_bar[i], 64);
     for (int i = 0; i < 4; ++i) {
       mbar_init(&sched_full[i], 1);
-      mbar_init(&sched_empty[i], 10);  // two issuer warps and eight epilogue warps
+      // the readers of a tile id: eight epilogue warps, the issuer warps (two; none in the
+      // pair's second CTA) and, in a pair, the warp that reports landed stages
+      mbar_init(&sched_empty[i], PAIR ? (leader ? 11 : 9) : 10);
+    }
+    if constexpr (PAIR) {
+      for (int s = 0; s < kStages; ++s) mbar_init(&ready[s], 2);  // one report per CTA
+      // the epilogue warps of both CTAs that drain a slab (a half: four each; a buffer: eight)
+      for (int i = 0; i < 4; ++i) mbar_init(&tempty[i], SPLIT ? 8 : 16);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -183,11 +233,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, Cfg::kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, Cfg::kTmemCols);
+      tmem_relinquish();
+    }
   }
   if (warp == 3) {
-    // Tile table: exclusive scan of ceil(M_g / 128) over the groups.
+    // Tile table: exclusive scan of ceil(M_g / tile rows) over the groups.
     int running = 0;
     bool bad = false;
     for (int base = 0; base < groups; base += 32) {
@@ -198,7 +253,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         hi = p.offsets[g + 1];
         if (lo < 0 || hi < lo || hi > p.rows_total) bad = true;
       }
-      int tiles = (g < groups && !bad) ? (hi - lo + kBlockM - 1) / kBlockM : 0;
+      int tiles = (g < groups && !bad) ? (hi - lo + Cfg::kTileM - 1) / Cfg::kTileM : 0;
       int incl = tiles;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -220,11 +275,21 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers exist before a remote arrival
+  else __syncthreads();
   tc_fence_after_sync();
 
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = (*total_m_tiles_s) * num_n_tiles;
+  // The 128 rows of M tile `mt` that this CTA loads, drains and stores.
+  auto locate = [&](int mt) {
+    TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups, Cfg::kTileM);
+    if constexpr (PAIR) {
+      c.m0 += rank * kBlockM;
+      c.rows_valid = max(0, min(kBlockM, c.rows_valid - rank * kBlockM));
+    }
+    return c;
+  };
 
   // Tiles are handed out by a global counter, not by stride: a CTA that becomes resident late
   // (its SM was busy with another kernel, e.g. a collective) simply takes fewer tiles, and no
@@ -256,8 +321,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       uint32_t drawn = 0;
       auto draw = [&]() {
-        const int t = p.sched_slot >= 0 ? atomicAdd(&g_tile_counter[p.sched_slot][0], 1)
-                                        : (int)(blockIdx.x + (drawn++) * gridDim.x);
+        int t;
+        if constexpr (PAIR) t = (int)((blockIdx.x >> 1) + (drawn++) * (gridDim.x >> 1));  // by pair
+        else t = p.sched_slot >= 0 ? atomicAdd(&g_tile_counter[p.sched_slot][0], 1)
+                                   : (int)(blockIdx.x + (drawn++) * gridDim.x);
         return t < total_tiles ? t : -1;
       };
       auto publish = [&](int t) {
@@ -275,15 +342,36 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!publish(t_next)) { ok = false; break; }  // the epilogue looks one tile ahead
         const int mt = t / num_n_tiles;
         const int n0 = (t - mt * num_n_tiles) * kTileStep;
-        const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
+        const TileCoord c = locate(mt);
         t = t_next;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
+          B200_TRACE(4, it, 0);
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          B200_TRACE(4, it, 1);
           mbar_arrive_expect_tx(&full[s], Cfg::kABytes + Cfg::kBBytes);
           tma_load_2d(sA + s * Cfg::kABytes, &tmap_a, &full[s], kb * kBlockK, c.m0);
-          if (EPI == 1) {
+          if constexpr (PAIR && SPLIT) {
+            // this CTA's 64 columns of each 128-column half (two loads of 8 KB)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col = n0 + h * 128 + rank * 64;
+              if (!B_MN_MAJOR)
+                tma_load_3d(sB + s * Cfg::kBBytes + h * (64 * kBlockK), &tmap_b, &full[s], kb * kBlockK, col,
+                            c.group % p.weights);
+              else
+                tma_load_3d(sB + s * Cfg::kBBytes + h * (64 * kBlockK), &tmap_b, &full[s], col, kb * kBlockK,
+                            c.group % p.weights);
+            }
+          } else if constexpr (PAIR) {
+            // this CTA's 128 of the tile's 256 columns (one load of 16 KB)
+            const int col = n0 + rank * 128;
+            if (!B_MN_MAJOR)
+              tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], kb * kBlockK, col, c.group % p.weights);
+            else
+              tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], col, kb * kBlockK, c.group % p.weights);
+          } else if (EPI == 1) {
             tma_load_3d(sB + s * Cfg::kBBytes, &tmap_b, &full[s], kb * kBlockK, n0, c.group % p.weights);
             tma_load_3d(sB + s * Cfg::kBBytes + 128 * kBlockK, &tmap_b, &full[s], kb * kBlockK, half_n + n0,
                         c.group % p.weights);
@@ -310,11 +398,28 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-  } else if (warp == 1 || warp == 3) {
+  } else if (PAIR && warp == 2) {
+    // ---- pair form: tell the leader CTA that this CTA's stage has landed.  The stage was
+    // written by the async proxy (TMA), so the remote arrival needs no cluster-scope release.
+    B200_REG_DEC();
+    uint32_t it = 0;
+    bool ok = true;
+    for (uint32_t tile_i = 0; ok; ++tile_i) {
+      const int t = tile_at(tile_i);
+      if (t == -2) ok = false;
+      else done_with(tile_i);
+      if (t < 0) break;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait_warp(&full[s], (it / kStages) & 1, abort_flag, p.status, 6)) { ok = false; break; }
+        if (lane == 0) mbar_arrive_remote(&ready[s], 0);
+      }
+    }
+  } else if ((warp == 1 || warp == 3) && (!PAIR || leader)) {
     // ------------------------------ UMMA issuers ------------------------------
     B200_REG_DEC();
     // The whole warp walks the loop (the hardware barrier counts warps); lane 0 issues.
-    constexpr uint32_t idesc = make_idesc(0, 0, 0, B_MN_MAJOR ? 1 : 0, kBlockM, BLOCK_N / kHalves);
+    constexpr uint32_t idesc = make_idesc(0, 0, 0, B_MN_MAJOR ? 1 : 0, Cfg::kTileM, BLOCK_N / kHalves);
     const uint32_t mine = warp == 1 ? 0u : 1u;  // parity of the K blocks (and the buffer) of this warp
     uint32_t it = 0;  // K blocks since the kernel started: stage it % kStages, buffer it & 1
     bool ok = true;
@@ -329,40 +434,67 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t ph = (it / kStages) & 1;
         // the operands first: they have usually landed long ago, so this check is off the
         // path from the epilogue's release to the next multiplication
-        if (!mbar_spin_warp(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
+        if (lane == 0) B200_TRACE(mine, it, 0);
+        if (!mbar_spin_warp(PAIR ? &ready[s] : &full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
+        if (lane == 0) B200_TRACE(mine, it, 1);
         // Everything the multiplications need is computed before the barrier: once the buffer
         // is free, the fewer instructions lane 0 still has to get through the scheduler (next
         // to epilogue warps that issue a multiply-add every cycle), the better.
         const uint64_t adesc = make_smem_desc(smem_u32(sA + s * Cfg::kABytes), 16, 1024);
         const uint32_t b_addr = smem_u32(sB + s * Cfg::kBBytes);
-        const uint64_t bdesc = B_MN_MAJOR ? make_smem_desc(b_addr, 128 * kBlockK, 1024)
-                                          : make_smem_desc(b_addr, 16, 1024);
+        // Pair form: this CTA's part of a half is 64 columns -- 64 K-major rows of 128 bytes, or
+        // 128 MN-major K-rows of 64 bytes (64-byte swizzle, 8 rows = 512 bytes).
+        constexpr bool kNarrowB = PAIR && SPLIT;  // 64 columns per CTA and multiplication
+        const uint64_t bdesc = !B_MN_MAJOR ? make_smem_desc(b_addr, 16, 1024)
+                               : kNarrowB  ? make_smem_desc(b_addr, 64 * kBlockK, 512, kLayoutSwizzle64)
+                                           : make_smem_desc(b_addr, 128 * kBlockK, 1024);
         // K-major: 32 bytes further along the 128-byte swizzled row per MMA.
-        // MN-major: 32 K-rows of 128 bytes further.
+        // MN-major: 32 K-rows (of 128 bytes, or of 64 in a split pair) further.
         constexpr uint64_t kStepA = (uint64_t)(32 >> 4);
-        constexpr uint64_t kStepB = (uint64_t)(B_MN_MAJOR ? ((32 * 128) >> 4) : (32 >> 4));
+        constexpr uint64_t kStepB = (uint64_t)(B_MN_MAJOR ? ((32 * (kNarrowB ? 64 : 128)) >> 4) : (32 >> 4));
+        // one half further: 128 columns of B (16 KB), of which a pair's CTA holds 64 (8 KB)
+        constexpr uint64_t kHalfB = (uint64_t)(((kNarrowB ? 64 : 128) * kBlockK) >> 4);
         const uint32_t empty_bar = smem_u32(&empty[s]);
 #pragma unroll
         for (int h = 0; h < kHalves; ++h) {
-          // 128 columns of B further: 128 K-major rows, or one MN-major panel -- 16 KB either way
-          const uint64_t bdesc_h = bdesc + (uint64_t)((h * 128 * kBlockK) >> 4);
+          const uint64_t bdesc_h = bdesc + (uint64_t)h * kHalfB;
           const uint32_t d_tmem = tmem_base + mine * BLOCK_N + h * 128;
           const uint32_t tfull_bar = smem_u32(&tfull[mine * kHalves + h]);
           if (it >= 2) {
             // this part of the buffer holds an earlier K block: its readers hand it back here.
-            // An epilogue warp that unwinds arrives once more, so this cannot wait forever.
-            named_sync(kAccBarrier + mine * kHalves + h, kRelThreads);
+            if constexpr (PAIR) {
+              // ... the epilogue warps of both CTAs, by remote arrivals on the leader's barrier
+              if (!mbar_spin_warp(&tempty[mine * kHalves + h], ((it >> 1) - 1) & 1, abort_flag, p.status, 3)) {
+                ok = false;
+                break;
+              }
+            } else {
+              // An epilogue warp that unwinds arrives once more, so this cannot wait forever.
+              named_sync(kAccBarrier + mine * kHalves + h, kRelThreads);
+            }
           }
           if (lane == 0) {
+            B200_TRACE(mine, it, 2 + 2 * h);
             tc_fence_after_sync();
-            umma_f8(d_tmem, adesc, bdesc_h, idesc, 0u);
-            umma_f8(d_tmem, adesc + kStepA, bdesc_h + kStepB, idesc, 1u);
-            umma_f8(d_tmem, adesc + 2 * kStepA, bdesc_h + 2 * kStepB, idesc, 1u);
-            umma_f8(d_tmem, adesc + 3 * kStepA, bdesc_h + 3 * kStepB, idesc, 1u);
-            umma_commit_addr(tfull_bar);
-            if (h == kHalves - 1) umma_commit_addr(empty_bar);
+            if constexpr (PAIR) {
+              umma_f8_pair(d_tmem, adesc, bdesc_h, idesc, 0u);
+              umma_f8_pair(d_tmem, adesc + kStepA, bdesc_h + kStepB, idesc, 1u);
+              umma_f8_pair(d_tmem, adesc + 2 * kStepA, bdesc_h + 2 * kStepB, idesc, 1u);
+              umma_f8_pair(d_tmem, adesc + 3 * kStepA, bdesc_h + 3 * kStepB, idesc, 1u);
+              umma_commit_pair(&tfull[mine * kHalves + h], 3);  // the epilogues of both CTAs
+              if (h == kHalves - 1) umma_commit_pair(&empty[s], 3);  // ... and both producers
+            } else {
+              umma_f8(d_tmem, adesc, bdesc_h, idesc, 0u);
+              umma_f8(d_tmem, adesc + kStepA, bdesc_h + kStepB, idesc, 1u);
+              umma_f8(d_tmem, adesc + 2 * kStepA, bdesc_h + 2 * kStepB, idesc, 1u);
+              umma_f8(d_tmem, adesc + 3 * kStepA, bdesc_h + 3 * kStepB, idesc, 1u);
+              umma_commit_addr(tfull_bar);
+              if (h == kHalves - 1) umma_commit_addr(empty_bar);
+            }
+            B200_TRACE(mine, it, 3 + 2 * h);
           }
         }
+        if (!ok) break;
         // one lane reads the flag so that the warp leaves the loop together (a warp that split
         // here would come back to the hardware barrier with lanes missing)
         int aborted = lane == 0 ? *abort_flag : 0;
@@ -371,7 +503,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     if (!ok && lane == 0) {
-      umma_commit(&drain[mine]);
+      if constexpr (PAIR) umma_commit_pair(&drain[mine], 1);
+      else umma_commit(&drain[mine]);
       const long long start = clock64();
       while (!mbar_try(&drain[mine], 0) && clock64() - start < 20000000LL) {}
     }
@@ -403,7 +536,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       EpiTile e;
       const int mt = t / num_n_tiles;
       const int n0 = (t - mt * num_n_tiles) * kTileStep;
-      const TileCoord c = locate_m_tile(mt, m_tile_start, offs, groups);
+      const TileCoord c = locate(mt);
       e.rows_valid = c.rows_valid;
       e.grow = c.m0 + row_in_tile;
       e.col0 = EPI == 1 ? n0 + half * 64 : n0 + half * kCols;
@@ -461,7 +594,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t aph = (ab >> 1) & 1;
           ++ab;
           const int part = SPLIT ? buf * 2 + half : buf;  // what this warp waits for and hands back
+          if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 0);
           if (!mbar_spin_warp(&tfull[part], aph, abort_flag, p.status, 4)) { ok = false; break; }
+          if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 1);
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N +
                                  (EPI == 1 ? half * 64 : half * kCols);
@@ -476,7 +611,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           auto release = [&]() {
             tc_fence_before_sync();
             __syncwarp();
-            named_arrive(kAccBarrier + part, kRelThreads);
+            if constexpr (PAIR) {
+              if (lane == 0) mbar_arrive_remote(&tempty[part], 0);  // the leader issues for both CTAs
+            } else {
+              named_arrive(kAccBarrier + part, kRelThreads);
+            }
           };
           uint32_t ra[32], rb[32];
           tmem_ld_32x32(taddr + tcol(0), ra);
@@ -493,6 +632,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             promote(rb, 1);
             tmem_ld_32x32(taddr + tcol(3), rb);
             tmem_ld_wait();
+            if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 2);
             // The buffer is handed back only after the last multiply-adds: released earlier,
             // the 64 FMAs that follow (one per cycle, from both epilogue warps of a
             // sub-partition) keep the issuer warp from being scheduled, and the next
@@ -500,6 +640,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             promote(ra, 2);
             promote(rb, 3);
             release();
+            if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 3);
           }
         }
 #pragma unroll
@@ -654,9 +795,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     if (!ok) {
-      // Unwinding: an issuer may be waiting on a hardware barrier for this warp.
-      named_arrive(kAccBarrier + (SPLIT ? half : 0), kRelThreads);
-      named_arrive(kAccBarrier + (SPLIT ? 2 + half : 1), kRelThreads);
+      // Unwinding: an issuer may be waiting on a hardware barrier for this warp.  (In the pair
+      // form the issuer's wait is an mbarrier wait with its own limit.)
+      if constexpr (!PAIR) {
+        named_arrive(kAccBarrier + (SPLIT ? half : 0), kRelThreads);
+        named_arrive(kAccBarrier + (SPLIT ? 2 + half : 1), kRelThreads);
+      }
     }
   }
 
@@ -667,14 +811,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #undef B200_REG_INC
 
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer may still be arriving on, or reading from, this CTA
+  else __syncthreads();
   if (warp == 2) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
   // The thread that drew this CTA's tiles reports the CTA finished; the last one in the grid
   // leaves the slot zeroed for a later launch.
-  if (threadIdx.x == 0 && p.sched_slot >= 0) {
+  if (!PAIR && threadIdx.x == 0 && p.sched_slot >= 0) {
     const int finished = atomicAdd(&g_tile_counter[p.sched_slot][1], 1);
     if (finished == (int)gridDim.x - 1) {
       g_tile_counter[p.sched_slot][0] = 0;
@@ -707,6 +853,37 @@ static int sched_slot_of(cudaStream_t stream) {
   return used[dev]++;
 }
 
+// The pair form: clusters of two CTAs, one 256 x 256 tile per pair at a time.
+template <bool B_MN, bool SPLIT>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp8Params& p,
+                            cudaStream_t stream) {
+  using Cfg = GemmCfg<256, true>;
+  auto kern = grouped_gemm_fp8_kernel<256, B_MN, 0, SPLIT, true>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+    return B200MOE_ERR_LAUNCH;
+  const long long m_tiles_bound = (p.rows_total + Cfg::kTileM - 1) / Cfg::kTileM + p.groups;
+  const long long tiles = m_tiles_bound * ((p.N + 255) / 256);
+  long long pairs = sm_count() / 2;
+  if (tiles < pairs) pairs = tiles;
+  if (pairs < 1) pairs = 1;
+  GemmFp8Params q = p;
+  q.sched_slot = -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, q) != cudaSuccess) return B200MOE_ERR_LAUNCH;
+  return launch_status();
+}
+
 template <int BLOCK_N, bool B_MN, int EPI = 0, bool SPLIT = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp8Params& p,
                        cudaStream_t stream) {
@@ -737,6 +914,35 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmF
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_GEMM_TRACE
+static long long* g_trace_buffer = nullptr;
+// Debug builds only: the device buffer (kTraceSlots * kTraceIts * kTraceFields int64) that CTA 0
+// of the next GEMM launches writes its cycle stamps into; NULL switches the stamps off.
+extern "C" int b200moe_debug_set_gemm_trace(long long* buffer) {
+  g_trace_buffer = buffer;
+  return B200MOE_OK;
+}
+extern "C" int b200moe_debug_gemm_trace_shape(int* slots, int* its, int* fields, int* first) {
+  *slots = kTraceSlots; *its = kTraceIts; *fields = kTraceFields; *first = kTraceFirst;
+  return B200MOE_OK;
+}
+#define B200_SET_TRACE(params) (params).trace = g_trace_buffer
+#else
+#define B200_SET_TRACE(params) do {} while (0)
+#endif
+
+// 1: the pair form whenever it can serve the call; -1 (default) and 0: the single-CTA form.
+static std::atomic<int> g_pair_mode{[] {
+  const char* v = getenv("B200MOE_GEMM_PAIR");
+  return v == nullptr ? -1 : (v[0] == '0' ? 0 : 1);
+}()};
+
+extern "C" int b200moe_set_gemm_pair(int mode) {
+  if (mode < -1 || mode > 1) return B200MOE_ERR_ARG;
+  g_pair_mode.store(mode, std::memory_order_relaxed);
+  return B200MOE_OK;
+}
 
 // Shared by the plain product (d != NULL) and the one with the combine fused into its store
 // (out_f32 != NULL).
@@ -801,11 +1007,22 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
   p.row_map = row_map;
   p.out_rows = fused ? tokens : rows_total;
   p.status = status;
+  B200_SET_TRACE(p);
+  // The pair form (two CTAs per 256 x 256 tile) serves the plain and the scattered store of the
+  // wide tile on request only (b200moe_set_gemm_pair(1) or B200MOE_GEMM_PAIR=1): it halves the
+  // B traffic through shared memory, but its hand-backs cross the pair through mbarriers, and
+  // measured 13-25% behind the single-CTA form, whose hand-backs are hardware barriers.
+  const int pair_mode = g_pair_mode.load(std::memory_order_relaxed);
+  static const bool pair_split = [] {  // B200MOE_GEMM_PAIR_SPLIT=1: each K block as two N=128 halves
+    const char* v = getenv("B200MOE_GEMM_PAIR_SPLIT");
+    return v != nullptr && v[0] == '1';
+  }();
+  const bool pair = !fused && block_n == 256 && pair_mode == 1 && sm_count() == sm_count_device();
   if (!b_mn_major) {
     // B is [groups, N, K], K contiguous; scales [groups, ceil(N/128), ceil(K/128)].
     uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)weights};
     uint64_t strides[2] = {(uint64_t)K, (uint64_t)K * (uint64_t)N};
-    uint32_t box[3] = {128, (uint32_t)block_n, 1};
+    uint32_t box[3] = {128, pair ? (pair_split ? 64u : 128u) : (uint32_t)block_n, 1};
     int r = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box,
                               CU_TENSOR_MAP_SWIZZLE_128B);
     if (r != B200MOE_OK) return r;
@@ -817,15 +1034,20 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
     // scales [groups, ceil(K/128), ceil(N/128)].
     uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)weights};
     uint64_t strides[2] = {(uint64_t)N, (uint64_t)K * (uint64_t)N};
-    uint32_t box[3] = {128, 128, 1};
+    // split pair form: 64 columns per CTA and half, as K-rows of 64 bytes (64-byte swizzle)
+    uint32_t box[3] = {pair && pair_split ? 64u : 128u, 128, 1};
     int r = encode_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box,
-                              CU_TENSOR_MAP_SWIZZLE_128B);
+                              pair && pair_split ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
     if (r != B200MOE_OK) return r;
     p.bs_group_stride = (long long)nblocks * kblocks;
     p.bs_n_stride = 1;
     p.bs_k_stride = nblocks;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (pair && pair_split)
+    return b_mn_major ? launch_gemm_pair<true, true>(ta, tb, p, s) : launch_gemm_pair<false, true>(ta, tb, p, s);
+  if (pair)
+    return b_mn_major ? launch_gemm_pair<true, false>(ta, tb, p, s) : launch_gemm_pair<false, false>(ta, tb, p, s);
   // the 256-wide tile issues each K block in two halves (B200MOE_GEMM_SPLIT=0: in one piece)
   static const bool split = [] {
     const char* v = getenv("B200MOE_GEMM_SPLIT");
@@ -959,6 +1181,7 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.row_map = nullptr;
   p.out_rows = rows_total;
   p.status = status;
+  B200_SET_TRACE(p);
   return launch_gemm<256, false, 1>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }
 

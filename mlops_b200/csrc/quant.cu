@@ -103,6 +103,58 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, long lo
   }
 }
 
+// The same quantisation, token-major: every token row is read and quantised ONCE and the
+// result is written to each of the `fanout` output rows `slots[t * fanout + k]` (the
+// expert-ordered rows of the token's assignments), instead of once per output row.  Same bytes
+// and scales as quantize_rows_kernel with gather = order / fanout; 1/fanout of its arithmetic
+// and source reads, so the pass is bound by its writes.  1x128 scales only.
+__global__ void __launch_bounds__(kRowWarps * 32)
+quantize_scatter_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, long long tokens,
+                        const int* __restrict__ slots, int fanout, long long rows_out, int D,
+                        uint8_t* __restrict__ q, long long ldq, float* __restrict__ scales,
+                        long long s_row, long long s_kb, __nv_bfloat16* __restrict__ copy, long long ldc,
+                        int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  // lane k < fanout holds destination k; a slot outside the output is reported and skipped
+  long long mine = -1;
+  if (lane < fanout) {
+    mine = slots[t * fanout + lane];
+    if (mine < 0 || mine >= rows_out) {
+      report_error(status, ERR_BAD_OFFSETS, 24, (int)t);
+      mine = -1;
+    }
+  }
+  const __nv_bfloat16* xr = x + t * ldx;
+  for (int c0 = 0; c0 < D; c0 += 512) {
+    const int ca = c0 + lane * 8, cb = ca + 256;
+    uint4 raw_a = make_uint4(0, 0, 0, 0), raw_b = make_uint4(0, 0, 0, 0);
+    if (ca < D) raw_a = *reinterpret_cast<const uint4*>(xr + ca);
+    if (cb < D) raw_b = *reinterpret_cast<const uint4*>(xr + cb);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = h == 0 ? ca : cb;
+      const uint4 raw = h == 0 ? raw_a : raw_b;
+      float v[8];
+      unpack8(raw, v);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = halfwarp_max(amax);
+      const float scale = fmaxf(amax * kInv448, 1e-12f);
+      const uint2 packed = quantize8(v, scale);
+      for (int k = 0; k < fanout; ++k) {
+        const long long dst = __shfl_sync(0xffffffffu, mine, k);
+        if (dst < 0 || c >= D) continue;
+        *reinterpret_cast<uint2*>(q + dst * ldq + c) = packed;
+        if ((lane & 15) == 0) scales[dst * s_row + (long long)(c >> 7) * s_kb] = scale;
+        if (copy != nullptr) *reinterpret_cast<uint4*>(copy + dst * ldc + c) = raw;
+      }
+    }
+  }
+}
+
 // act = silu(gate) * up computed in fp32 from h13 = [gate | up] (each F wide), rounded
 // once: to E4M3 with 1x128 scales (act_q / scales) and, when act_bf16 is given, to bf16.
 // Optional GLM clamp: gate capped at `limit`, up clipped to [-limit, limit].
@@ -304,6 +356,24 @@ extern "C" int b200moe_quantize_rows(const void* x, long long ldx, long long src
   quantize_rows_kernel<<<row_grid(rows), kRowWarps * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ldx, src_rows, gather, gather_div > 0 ? gather_div : 1, rows,
       width, reinterpret_cast<uint8_t*>(q), ldq, scales, scale_row_stride, scale_block_stride, mode,
+      reinterpret_cast<__nv_bfloat16*>(copy), ldc, status);
+  return launch_status();
+}
+
+extern "C" int b200moe_quantize_rows_scatter(const void* x, long long ldx, long long tokens, const int32_t* slots,
+                                             int fanout, long long rows_out, int width, void* q, long long ldq,
+                                             float* scales, long long scale_row_stride,
+                                             long long scale_block_stride, void* copy, long long ldc,
+                                             int32_t* status, void* stream) {
+  if (!x || !slots || !q || !scales || !status || tokens < 0 || rows_out < 0 || width <= 0) return B200MOE_ERR_ARG;
+  if (fanout <= 0 || fanout > 32) return B200MOE_ERR_LIMIT;
+  if (copy != nullptr && ((ldc % 8) || ((uintptr_t)copy & 15))) return B200MOE_ERR_ALIGN;
+  if ((width % 8) || (ldx % 8) || (ldq % 8) || ((uintptr_t)x & 15) || ((uintptr_t)q & 7))
+    return B200MOE_ERR_ALIGN;
+  if (tokens == 0) return B200MOE_OK;
+  quantize_scatter_kernel<<<row_grid(tokens), kRowWarps * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, tokens, slots, fanout, rows_out, width,
+      reinterpret_cast<uint8_t*>(q), ldq, scales, scale_row_stride, scale_block_stride,
       reinterpret_cast<__nv_bfloat16*>(copy), ldc, status);
   return launch_status();
 }

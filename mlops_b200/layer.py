@@ -44,33 +44,29 @@ def _router_weight_gradient(grad_logits, hidden, dtype):
 
 
 # ---------------------------------------------------------------- routing statistics
-def _probabilities(logits, routing_mode):
-    if routing_mode == "sigmoid_noaux_tc":
-        scores = torch.sigmoid(logits.float())
-        return scores, scores / scores.sum(-1, keepdim=True)
-    return None, torch.softmax(logits.float(), dim=-1)
-
-
 def routing_statistics(logits, route_ids, counts, *, routing_mode, lengths, experts):
     """`(aux, counts, probability_sum)` of one routing decision (reference:
-    src/mlops/providers/moe_common.py:32-71). `counts` is the int64 histogram the sort
-    kernel already produced."""
+    src/mlops/providers/moe_common.py:32-71). `counts` is the int64 histogram the sort kernel
+    already produced. The pass over the `[T, E]` logits is one kernel (column sums of the
+    probabilities, formed in a fixed order); what is left is `[E]`-sized arithmetic."""
     rows = logits.shape[0]
-    _scores, probabilities = _probabilities(logits, routing_mode)
-    probability_sum = probabilities.sum(0)
     if routing_mode == "sigmoid_noaux_tc":
         aux = torch.zeros((), dtype=torch.float32, device=logits.device)
+        probability_sum = None
         start = 0
-        for length in lengths:
+        for length in lengths:  # the auxiliary loss of this mode is per sequence
             stop = start + int(length)
+            segment_sum = ops.routing_probability_sum(logits[start:stop], routing_mode)
             if len(lengths) == 1:
-                segment = counts
+                segment_counts = counts
             else:
-                segment = torch.bincount(route_ids[start:stop].reshape(-1).long(), minlength=experts)
-            frequency = segment.float() * experts / (route_ids.shape[1] * int(length))
-            aux = aux + (frequency * probabilities[start:stop].mean(0)).sum()
+                segment_counts = torch.bincount(route_ids[start:stop].reshape(-1).long(), minlength=experts)
+            frequency = segment_counts.float() * experts / (route_ids.shape[1] * int(length))
+            aux = aux + (frequency * (segment_sum / int(length))).sum()
+            probability_sum = segment_sum if probability_sum is None else probability_sum + segment_sum
             start = stop
     else:
+        probability_sum = ops.routing_probability_sum(logits, routing_mode)
         frequency = counts.float() / route_ids.numel()
         aux = experts * (frequency * (probability_sum / rows)).sum()
     return aux, counts, probability_sum
@@ -80,57 +76,32 @@ def routing_gradient(grad_aux, grad_probability_sum, grad_route_weights, route_w
                      logits, counts, *, routing_mode, lengths):
     """fp32 gradient of the logits from the cotangents of the route weights, the auxiliary
     loss and the probability sum (reference: src/mlops/providers/moe_common.py:74-124,
-    src/mlops/kernels/moe_router.py:403-502)."""
+    src/mlops/kernels/moe_router.py:403-502): one kernel per sequence for the sigmoid mode's
+    per-sequence auxiliary loss, one kernel otherwise."""
     tokens, experts = logits.shape
-    selected = route_ids.long()
-    grad_w = grad_route_weights.float()
-    scores, probabilities = _probabilities(logits, routing_mode)
-    grad_logits = torch.zeros_like(logits, dtype=torch.float32)
-    if routing_mode == "sigmoid_noaux_tc":
-        weights = route_weights.float()
-        picked = scores.gather(1, selected)
-        picked_sum = picked.sum(-1, keepdim=True)
-        scaling = weights.sum(-1, keepdim=True)
-        dot = (grad_w * weights).sum(-1, keepdim=True)
-        grad_logits.scatter_(1, selected, ((scaling * grad_w - dot) / picked_sum) * picked * (1.0 - picked))
-    elif routing_mode == "topk_then_softmax":
-        weights = route_weights.float()
-        grad_logits.scatter_(1, selected, weights * (grad_w - (grad_w * weights).sum(-1, keepdim=True)))
-    else:
-        top = probabilities.gather(1, selected)
-        dot = (grad_w * top).sum(-1, keepdim=True)
-        grad_logits.copy_(-probabilities * dot)
-        grad_logits.scatter_add_(1, selected, grad_w * top)
-
-    if grad_aux is not None:
-        if routing_mode == "sigmoid_noaux_tc":
-            row_sum = scores.sum(-1, keepdim=True)
-            start = 0
-            for length in lengths:
-                stop = start + int(length)
-                if len(lengths) == 1:
-                    segment = counts.float()
-                else:
-                    segment = torch.bincount(
-                        route_ids[start:stop].reshape(-1).long(), minlength=experts
-                    ).float()
-                frequency = segment * experts / (route_ids.shape[1] * int(length))
-                coefficient = grad_aux.float() / (int(length) * row_sum[start:stop])
-                part = probabilities[start:stop]
-                score_gradient = coefficient * (frequency.unsqueeze(0) - (part @ frequency).unsqueeze(1))
-                grad_logits[start:stop].add_(score_gradient * scores[start:stop] * (1.0 - scores[start:stop]))
-                start = stop
-        else:
-            frequency = counts.float() / route_ids.numel()
-            coefficient = grad_aux.float() * experts / tokens
-            grad_logits.add_(
-                coefficient * probabilities * (frequency.unsqueeze(0) - (probabilities @ frequency).unsqueeze(1))
-            )
-
-    if grad_probability_sum is not None:
-        jacobian_scale = probabilities if scores is None else (1.0 - scores) * probabilities
-        grad_sum = grad_probability_sum.float()
-        grad_logits.add_(jacobian_scale * (grad_sum.unsqueeze(0) - (probabilities @ grad_sum).unsqueeze(1)))
+    if routing_mode != "sigmoid_noaux_tc" or grad_aux is None or len(lengths) == 1:
+        frequency, aux_scale = None, 0.0
+        if grad_aux is not None:
+            if routing_mode == "sigmoid_noaux_tc":
+                frequency = counts.float() * experts / (route_ids.shape[1] * tokens)
+                aux_scale = 1.0 / tokens
+            else:
+                frequency = counts.float() / route_ids.numel()
+                aux_scale = experts / tokens
+        return ops.routing_gradient(logits, route_ids, route_weights, grad_route_weights, routing_mode,
+                                    grad_aux=grad_aux, frequency=frequency, aux_scale=aux_scale,
+                                    grad_probability_sum=grad_probability_sum)
+    grad_logits = torch.empty((tokens, experts), dtype=torch.float32, device=logits.device)
+    start = 0
+    for length in lengths:
+        stop = start + int(length)
+        segment = torch.bincount(route_ids[start:stop].reshape(-1).long(), minlength=experts).float()
+        frequency = segment * experts / (route_ids.shape[1] * int(length))
+        ops.routing_gradient(logits[start:stop], route_ids[start:stop], route_weights[start:stop],
+                             grad_route_weights[start:stop], routing_mode, grad_aux=grad_aux, frequency=frequency,
+                             aux_scale=1.0 / int(length), grad_probability_sum=grad_probability_sum,
+                             out=grad_logits[start:stop])
+        start = stop
     return grad_logits
 
 
@@ -199,7 +170,8 @@ def forward_routed(
             # the sort reported ids outside [0, experts) and placed them on the nearest expert;
             # the residual handed to the statistics and to the backward pass says the same
             route_ids = route_ids.clamp(0, experts - 1)
-        x_q, x_s = ops.quantize_rows(h2_flat, gather=order, gather_div=int(top_k))
+        # every token quantised once, its E4M3 row written to each of its K expert-ordered rows
+        x_q, x_s = ops.quantize_rows_scatter(h2_flat, slots)
         if fuse_swiglu and w2_data.shape[2] % 128 == 0:
             h13, a_q, a_s = ops.grouped_gemm_fp8_swiglu(x_q, x_s, w13_data, w13_scale, offsets, limit=swiglu_limit)
         else:
@@ -265,9 +237,9 @@ def backward_routed(
         # one pass over dy: E4M3 rows for the input gradient and, when the down weight's gradient
         # is wanted, the same rows in bf16 as its operand
         if need_w2:
-            dy_q, dy_s, dy_rows = ops.quantize_rows(grad_flat, gather=order, gather_div=int(top_k), with_copy=True)
+            dy_q, dy_s, dy_rows = ops.quantize_rows_scatter(grad_flat, slots, with_copy=True)
         else:
-            dy_q, dy_s = ops.quantize_rows(grad_flat, gather=order, gather_div=int(top_k))
+            dy_q, dy_s = ops.quantize_rows_scatter(grad_flat, slots)
         r = ops.grouped_gemm_fp8(dy_q, dy_s, w2_data, w2_scale, offsets, b_mn_major=True, block_n=block_n)
         dscore, gh_q, gh_s, gh_b, act_scaled = ops.dswiglu_routed(
             h13, r, route_weights, order, limit=swiglu_limit, quantized=True, rounded=need_w13,

@@ -77,6 +77,12 @@ def set_cta_limit(ctas: int) -> None:
     check(lib.b200moe_set_cta_limit(int(ctas)), "set_cta_limit")
 
 
+def set_gemm_pair(mode: int) -> None:
+    """1: the CTA-pair form of the wide FP8 GEMM (cta_group::2, 256 x 256 tiles); -1 (default)
+    and 0: the single-CTA form. Bit-identical results either way."""
+    check(lib.b200moe_set_gemm_pair(int(mode)), "set_gemm_pair")
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -150,6 +156,57 @@ def route_topk(logits, top_k, mode, *, bias=None, n_group=1, topk_group=1, route
     )
     _count()
     return weights, ids
+
+
+@_on_tensor_device
+def routing_probability_sum(logits, mode):
+    """fp32 `[E]`: column sums of softmax(logits) (or of the per-token normalised sigmoid scores
+    for mode "sigmoid_noaux_tc") over the rows of fp32 `logits [T, E]`; bitwise repeatable."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise NativeError("logits must be fp32 [tokens, experts] with unit inner stride")
+    tokens, experts = logits.shape
+    out = torch.empty(experts, dtype=torch.float32, device=logits.device)
+    nbytes = lib.b200moe_routing_probability_sum_workspace_bytes(tokens, experts)
+    workspace = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=logits.device)
+    check(
+        lib.b200moe_routing_probability_sum(logits.data_ptr(), logits.stride(0), tokens, experts,
+                                            ROUTING_MODES[mode], workspace.data_ptr(), out.data_ptr(), _stream()),
+        "routing_probability_sum",
+    )
+    _count(2)
+    return out
+
+
+@_on_tensor_device
+def routing_gradient(logits, route_ids, route_weights, grad_route_weights, mode, *, grad_aux=None, frequency=None,
+                     aux_scale=0.0, grad_probability_sum=None, out=None):
+    """fp32 gradient of `logits [T, E]` (see `b200moe_routing_gradient`); `out` receives it when
+    given (a row slice of a larger gradient, for per-sequence calls)."""
+    device = _need_cuda(logits, route_ids, route_weights, grad_route_weights, grad_aux, frequency,
+                        grad_probability_sum, out)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise NativeError("logits must be fp32 [tokens, experts] with unit inner stride")
+    tokens, experts = logits.shape
+    top_k = route_ids.shape[1]
+    if out is None:
+        out = torch.empty((tokens, experts), dtype=torch.float32, device=device)
+    as_f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()  # noqa: E731
+    ids = route_ids if route_ids.dtype == torch.int32 and route_ids.is_contiguous() else \
+        route_ids.to(torch.int32).contiguous()
+    weights, grads = as_f32(route_weights), as_f32(grad_route_weights)
+    grad_aux, frequency, grad_probability_sum = as_f32(grad_aux), as_f32(frequency), as_f32(grad_probability_sum)
+    if tokens:
+        check(
+            lib.b200moe_routing_gradient(
+                logits.data_ptr(), logits.stride(0), tokens, experts, top_k, ROUTING_MODES[mode], ids.data_ptr(),
+                _ptr(weights), grads.data_ptr(), _ptr(grad_aux), _ptr(frequency), float(aux_scale),
+                _ptr(grad_probability_sum), out.data_ptr(), out.stride(0), _stream(),
+            ),
+            "routing_gradient",
+        )
+        _count()
+    return out
 
 
 @_on_tensor_device
@@ -239,6 +296,36 @@ def quantize_rows(x, *, gather=None, gather_div=1, mode="1x128", with_copy=False
         "quantize_rows",
     )
     _count()
+    return (q, scales, copy) if with_copy else (q, scales)
+
+
+@_on_tensor_device
+def quantize_rows_scatter(x, slots, *, with_copy=False):
+    """`quantize_rows(x, gather=order, gather_div=K)` computed from the token's side: every row
+    of bf16 `x [T, D]` is quantised once (1x128 scales) and written to the K rows `slots[t, :]`
+    (the sort's inverse permutation, int32 `[T, K]`). Returns `(q [T*K, D], scales [T*K, blocks])`
+    and, with `with_copy`, the bf16 rows in the same order."""
+    _need_cuda(x, slots)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise NativeError("x must be bf16 [rows, width] with unit inner stride")
+    if slots.dtype != torch.int32 or slots.dim() != 2 or slots.shape[0] != x.shape[0] or not slots.is_contiguous():
+        raise NativeError("slots must be contiguous int32 [rows of x, fan-out]")
+    tokens, width = x.shape
+    fanout = slots.shape[1]
+    rows = tokens * fanout
+    q = torch.empty((rows, width), dtype=FP8, device=x.device)
+    scales = _scale_buffer(rows, (width + 127) // 128, x.device)
+    copy = torch.empty((rows, width), dtype=torch.bfloat16, device=x.device) if with_copy else None
+    if rows:
+        check(
+            lib.b200moe_quantize_rows_scatter(
+                x.data_ptr(), x.stride(0), tokens, slots.data_ptr(), fanout, rows, width, q.data_ptr(), q.stride(0),
+                scales.data_ptr(), scales.stride(0), scales.stride(1), _ptr(copy),
+                width if copy is None else copy.stride(0), status_block(x.device).data_ptr(), _stream(),
+            ),
+            "quantize_rows_scatter",
+        )
+        _count()
     return (q, scales, copy) if with_copy else (q, scales)
 
 

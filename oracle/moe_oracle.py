@@ -102,6 +102,73 @@ def routing_statistics(logits, route_ids, *, routing_mode, lengths, experts):
     return aux, counts, probability_sum
 
 
+def _probabilities(logits, routing_mode):
+    if routing_mode == "sigmoid_noaux_tc":
+        scores = torch.sigmoid(logits.float())
+        return scores, scores / scores.sum(-1, keepdim=True)
+    return None, torch.softmax(logits.float(), dim=-1)
+
+
+def routing_gradient(grad_aux, grad_probability_sum, grad_route_weights, route_weights, route_ids,
+                     logits, counts, *, routing_mode, lengths):
+    """fp32 gradient of the logits from the cotangents of the route weights, the auxiliary
+    loss and the probability sum. Follows src/mlops/providers/moe_common.py:74-124 and
+    src/mlops/kernels/moe_router.py:403-502 (`route_backward`, `add_aux_gradient_`,
+    `add_sequence_aux_gradient_`); pinned against the reference's `routing_gradient` fixture.
+    `counts` is the int64 histogram of `route_ids` over the experts."""
+    tokens, experts = logits.shape
+    selected = route_ids.long()
+    grad_w = grad_route_weights.float()
+    scores, probabilities = _probabilities(logits, routing_mode)
+    grad_logits = torch.zeros_like(logits, dtype=torch.float32)
+    if routing_mode == "sigmoid_noaux_tc":
+        weights = route_weights.float()
+        picked = scores.gather(1, selected)
+        picked_sum = picked.sum(-1, keepdim=True)
+        scaling = weights.sum(-1, keepdim=True)
+        dot = (grad_w * weights).sum(-1, keepdim=True)
+        grad_logits.scatter_(1, selected, ((scaling * grad_w - dot) / picked_sum) * picked * (1.0 - picked))
+    elif routing_mode == "topk_then_softmax":
+        weights = route_weights.float()
+        grad_logits.scatter_(1, selected, weights * (grad_w - (grad_w * weights).sum(-1, keepdim=True)))
+    else:
+        top = probabilities.gather(1, selected)
+        dot = (grad_w * top).sum(-1, keepdim=True)
+        grad_logits.copy_(-probabilities * dot)
+        grad_logits.scatter_add_(1, selected, grad_w * top)
+
+    if grad_aux is not None:
+        if routing_mode == "sigmoid_noaux_tc":
+            row_sum = scores.sum(-1, keepdim=True)
+            start = 0
+            for length in lengths:
+                stop = start + int(length)
+                if len(lengths) == 1:
+                    segment = counts.float()
+                else:
+                    segment = torch.bincount(
+                        route_ids[start:stop].reshape(-1).long(), minlength=experts
+                    ).float()
+                frequency = segment * experts / (route_ids.shape[1] * int(length))
+                coefficient = grad_aux.float() / (int(length) * row_sum[start:stop])
+                part = probabilities[start:stop]
+                score_gradient = coefficient * (frequency.unsqueeze(0) - (part @ frequency).unsqueeze(1))
+                grad_logits[start:stop].add_(score_gradient * scores[start:stop] * (1.0 - scores[start:stop]))
+                start = stop
+        else:
+            frequency = counts.float() / route_ids.numel()
+            coefficient = grad_aux.float() * experts / tokens
+            grad_logits.add_(
+                coefficient * probabilities * (frequency.unsqueeze(0) - (probabilities @ frequency).unsqueeze(1))
+            )
+
+    if grad_probability_sum is not None:
+        jacobian_scale = probabilities if scores is None else (1.0 - scores) * probabilities
+        grad_sum = grad_probability_sum.float()
+        grad_logits.add_(jacobian_scale * (grad_sum.unsqueeze(0) - (probabilities @ grad_sum).unsqueeze(1)))
+    return grad_logits
+
+
 # ---------------------------------------------------------------------- quantisation
 def _blocks(width):
     return -(-width // BLOCK)

@@ -338,3 +338,65 @@ def test_scattered_store_places_rows_by_the_map(mn_major):
     ops.grouped_gemm_fp8(*dev, b_mn_major=mn_major, out=out, row_map=row_map)
     ops.check_status(DEV)
     assert torch.equal(out[row_map.long()], plain)
+
+
+# ------------------------------------------------------------ the CTA-pair form of the GEMM
+@pytest.fixture
+def pair_form():
+    """Forces the CTA-pair form of the wide tile (normally chosen by shape) for one test."""
+    ops = _ops()
+    ops.set_gemm_pair(1)
+    yield ops
+    ops.set_gemm_pair(-1)
+
+
+@pytest.mark.parametrize("mn_major", [False, True])
+@pytest.mark.parametrize(
+    "counts,n,k",
+    [
+        ([256, 512], 256, 512),
+        ([0, 70, 131, 15, 260, 300], 384, 640),   # empty expert, tiles whose second CTA has no rows
+        ([1, 0, 0, 513], 128, 128),               # one column half beyond N
+        ([700], 2048, 7168),                      # the DeepSeek-shaped K loop (56 blocks)
+        ([130, 70], 200, 192),                    # K and N that are not multiples of 128
+    ],
+)
+def test_pair_form_matches_float64_and_the_single_cta_form(pair_form, counts, n, k, mn_major):
+    if mn_major and n % 16:
+        pytest.skip("an input gradient needs N % 16 == 0")
+    a_q, a_s, b_q, b_s, offs = _case(counts, n, k, seed=n + k + 1, mn_major=mn_major)
+    out = _run(a_q, a_s, b_q, b_s, offs, mn_major, 256)
+    ref = O.grouped_block_gemm(a_q, a_s, b_q, b_s, offs, b_mn_major=mn_major)
+    assert not torch.isnan(out.float()).any()
+    mx, mean = O.rel_errors(out.float().cpu(), ref)
+    assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+    pair_form.set_gemm_pair(0)
+    single = _run(a_q, a_s, b_q, b_s, offs, mn_major, 256)
+    assert torch.equal(out, single)  # the same sums in the same order: bit-identical
+
+
+@pytest.mark.parametrize("mn_major", [False, True])
+def test_pair_form_integer_operands_scatter_and_addend(pair_form, mn_major):
+    ops = pair_form
+    g = torch.Generator().manual_seed(12)
+    counts, n, k = [300, 212], 512, 384
+    rows = sum(counts)
+    a = torch.randint(-3, 4, (rows, k), generator=g).float()
+    b = torch.randint(-3, 4, (2, n, k), generator=g).float()
+    a_q, b_q = a.to(FP8), b.to(FP8)
+    a_s, b_s = torch.ones(rows, 3), torch.ones(2, 4, 3)
+    offs = _offsets(counts)
+    ref = O.grouped_block_gemm(a_q, a_s, b_q, b_s, offs)
+    if mn_major:
+        b_q = b_q.view(torch.uint8).transpose(1, 2).contiguous().view(FP8)
+        b_s = b_s.transpose(1, 2).contiguous()
+    out = _run(a_q, a_s, b_q, b_s, offs, mn_major, 256)
+    assert torch.equal(out.cpu(), ref.float().bfloat16())
+    addend = torch.randint(-8, 9, (rows, n), generator=g).bfloat16()
+    row_map = torch.randperm(rows, generator=g).to(torch.int32)
+    scattered = ops.grouped_gemm_fp8(a_q.to(DEV), a_s.to(DEV), b_q.to(DEV), b_s.to(DEV), offs.to(DEV),
+                                     b_mn_major=mn_major, addend=addend.to(DEV), row_map=row_map.to(DEV))
+    ops.check_status(DEV)
+    expected = torch.empty_like(ref)
+    expected[row_map.long()] = ref + addend.double()
+    assert torch.equal(scattered.cpu(), expected.float().bfloat16())

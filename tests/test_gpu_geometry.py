@@ -110,7 +110,7 @@ def _routed_case(tokens, width, experts, inner, top_k, mode, *, bias=None, n_gro
     torch.testing.assert_close(aux.cpu(), aux_ref, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(psum.cpu(), psum_ref, rtol=1e-5, atol=1e-5)
     assert torch.equal(grad_residual.cpu(), dy)
-    grad_logits = layer.routing_gradient(None, None, ref["grad_route_weights"], ref["weights"], ref["ids"],
+    grad_logits = O.routing_gradient(None, None, ref["grad_route_weights"], ref["weights"], ref["ids"],
                                          logits.cpu(), counts_c, routing_mode=mode, lengths=(tokens,))
     expected_h2 = ref["grad_h2"].float() + grad_logits.bfloat16().float() @ router.bfloat16().float()
     _check(grad_h2, expected_h2, f"{name} grad_h2")
@@ -245,7 +245,7 @@ def test_qwen3_30b_a3b_geometry_with_lora_and_zipf_skew():
     _check(r_dev, bwd["r"].float(), "E128-lora dy.W2 + LoRA term")
     grad_logits_part = grads[0].float().cpu()  # expert part + router part; the oracle gives the former
     from mlops_b200 import layer
-    grad_logits = layer.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"], logits,
+    grad_logits = O.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"], logits,
                                          counts_c, routing_mode="softmax_then_topk", lengths=(tokens,))
     expected = bwd["grad_h2"].float() + grad_logits.bfloat16().float() @ router.bfloat16().float()
     _check(grad_logits_part, expected, "E128-lora grad_x")

@@ -69,7 +69,7 @@ def _run_case(x, residual, router, w13, w2, dy, *, top_k, mode, bias=None, n_gro
     fwd_dev = dict(fwd, h13=h13.cpu())
     bwd = O.backward_block_fp8(dy, x, fwd_dev, w13_q, w13_s, w2_q, w2_s, top_k=top_k, swiglu_limit=limit)
     assert torch.equal(grad_residual.cpu(), dy)
-    grad_logits = layer.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"],
+    grad_logits = O.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"],
                                          logits.cpu(), counts.cpu(), routing_mode=mode, lengths=(x.shape[0],))
     expected_h2 = bwd["grad_h2"].float() + grad_logits.bfloat16().float() @ router.bfloat16().float()
     _check(grad_h2, expected_h2, "grad_h2")

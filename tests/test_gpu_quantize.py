@@ -136,3 +136,29 @@ def test_combine_matches_reference_fixture_and_oracle(golden):
     x = torch.randn(tokens, width, generator=g).bfloat16()
     rows = ops.dispatch(x.to(DEV), order.to(DEV), top_k)
     assert torch.equal(rows.cpu(), x[order.long() // top_k])
+
+
+def test_scatter_quantiser_equals_the_gathered_quantiser_bit_for_bit():
+    """Quantising every token once and writing its row to its K expert-ordered rows gives the
+    bytes, the scales and the bf16 copies of the per-output-row gather (which is pinned above
+    against the reference's `quantize_rows_fp8_reference`), including a width that is not a
+    multiple of 128 and a slot outside the output, which is reported and skipped."""
+    from mlops_b200 import ops
+    from mlops_b200._lib import NativeError
+
+    g = torch.Generator().manual_seed(31)
+    tokens, top_k, experts = 700, 8, 64
+    for width in (7168, 1000):
+        x = torch.randn(tokens, width, generator=g).bfloat16().to(DEV)
+        ids = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(tokens)]).to(torch.int32).to(DEV)
+        order, _offsets, slots, _counts = ops.sort_assignments(ids, experts)
+        q_ref, s_ref, c_ref = ops.quantize_rows(x, gather=order, gather_div=top_k, with_copy=True)
+        q, s, c = ops.quantize_rows_scatter(x, slots, with_copy=True)
+        assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+        assert torch.equal(s, s_ref) and torch.equal(c, c_ref)
+    ops.check_status(DEV)
+    bad = slots.clone()
+    bad[3, 2] = tokens * top_k + 5
+    ops.quantize_rows_scatter(x, bad)
+    with pytest.raises(NativeError):
+        ops.check_status(DEV)

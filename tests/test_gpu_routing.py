@@ -144,3 +144,55 @@ def test_nan_and_infinite_logits_still_give_valid_ids(mode):
     finite = torch.isfinite(w_ref).all(-1)
     torch.testing.assert_close(w.cpu()[finite], w_ref[finite], rtol=2e-6, atol=1e-7)
     assert torch.equal(torch.isnan(w.cpu()), torch.isnan(w_ref))
+
+
+def test_routing_statistics_and_gradient_kernels_match_the_reference_fixture(golden):
+    """`probability_sum`, `aux` and the gradient of the logits for every routing mode, with and
+    without the auxiliary-loss and probability-sum cotangents and with several sequences:
+    against the reference's own `routing_statistics` / `routing_gradient` outputs (fixture)."""
+    from mlops_b200 import layer
+
+    for case in golden("routing.pt"):
+        experts = case["logits"].shape[1]
+        dev = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+        aux, counts, psum = layer.routing_statistics(dev["logits"], dev["ids"], dev["counts"],
+                                                     routing_mode=case["mode"], lengths=case["lengths"],
+                                                     experts=experts)
+        torch.testing.assert_close(aux.cpu(), case["aux"], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(psum.cpu(), case["psum"], rtol=1e-5, atol=1e-5)
+        assert counts.dtype == torch.int64
+        again = layer.routing_statistics(dev["logits"], dev["ids"], dev["counts"], routing_mode=case["mode"],
+                                         lengths=case["lengths"], experts=experts)
+        assert torch.equal(again[2], psum)  # a fixed summation order: bitwise repeatable
+        grad = layer.routing_gradient(dev["grad_aux"], dev["grad_psum"], dev["grad_w"], dev["weights"], dev["ids"],
+                                      dev["logits"], dev["counts"], routing_mode=case["mode"],
+                                      lengths=case["lengths"])
+        torch.testing.assert_close(grad.cpu(), case["grad_logits"], rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("mode,experts,top_k", [("sigmoid_noaux_tc", 256, 8), ("softmax_then_topk", 128, 8),
+                                                 ("topk_then_softmax", 40, 3)])
+def test_routing_gradient_kernel_against_the_oracle_at_size(mode, experts, top_k):
+    from mlops_b200 import layer
+
+    g = torch.Generator().manual_seed(experts)
+    tokens = 3000
+    logits = torch.randn(tokens, experts, generator=g) * 2
+    kwargs = dict(bias=torch.randn(experts, generator=g) * 0.1, n_group=8, topk_group=4, routed_scaling=2.5) \
+        if mode == "sigmoid_noaux_tc" else {}
+    weights, ids = O.route(logits, top_k, mode, **kwargs)
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=experts)
+    grad_w = torch.randn(tokens, top_k, generator=g)
+    grad_aux, grad_psum = torch.tensor(0.7), torch.randn(experts, generator=g)
+    lengths = (1000, 1500, 500)
+    for ga, gp, ln in ((None, None, (tokens,)), (grad_aux, grad_psum, (tokens,)), (grad_aux, grad_psum, lengths)):
+        ref = O.routing_gradient(ga, gp, grad_w, weights, ids, logits, counts, routing_mode=mode, lengths=ln)
+        dev = lambda t: None if t is None else t.to(DEV)  # noqa: E731
+        out = layer.routing_gradient(dev(ga), dev(gp), dev(grad_w), dev(weights), dev(ids), dev(logits), dev(counts),
+                                     routing_mode=mode, lengths=ln)
+        torch.testing.assert_close(out.cpu(), ref, rtol=2e-5, atol=2e-6)
+        aux_ref, _, psum_ref = O.routing_statistics(logits, ids, routing_mode=mode, lengths=ln, experts=experts)
+        aux, _, psum = layer.routing_statistics(dev(logits), dev(ids), dev(counts), routing_mode=mode, lengths=ln,
+                                                experts=experts)
+        torch.testing.assert_close(aux.cpu(), aux_ref, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(psum.cpu(), psum_ref, rtol=1e-5, atol=1e-4)

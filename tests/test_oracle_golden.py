@@ -126,12 +126,9 @@ def test_layer_restatement_against_reference_config1(golden):
     bwd = O.backward_block_fp8(c1["dy"], c1["x"], fwd, w13_q, w13_s, w2_q, w2_s, top_k=c1["top_k"])
     assert frob(bwd["grad_w13"][:, ::16, ::8], fixture["grad_w13_sample"]) < 6e-2
     assert frob(bwd["grad_w2"][:, ::8, ::16], fixture["grad_w2_sample"]) < 6e-2
-    # grad_x = expert path + router path (the package's host-side routing VJP, which is
-    # plain PyTorch and runs on CPU)
-    from mlops_b200.layer import routing_gradient
-
-    grad_logits = routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"],
-                                   logits, counts, routing_mode=c1["routing_mode"], lengths=(512,))
+    # grad_x = expert path + router path
+    grad_logits = O.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"],
+                                     logits, counts, routing_mode=c1["routing_mode"], lengths=(512,))
     grad_x = bwd["grad_h2"].float() + grad_logits @ c1["router"]
     assert frob(grad_x, fixture["grad_x"]) < 8e-2
     grad_router = grad_logits.t() @ c1["x"].float()
