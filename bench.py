@@ -444,6 +444,9 @@ class Layer:
         # assignment.
         dedup = os.environ.get("B200MOE_EP_DEDUP", "1" if cfg["n_group"] > 1 else "0") == "1"
         expert_map = os.environ.get("B200MOE_EP_MAP", "contiguous" if dedup else "strided")
+        # one pre-weighted row per token copy on the way back (the reference's layers return
+        # pre-weighted rows too); B200MOE_EP_PRESUM=0 returns one row per assignment
+        presum = dedup and os.environ.get("B200MOE_EP_PRESUM", "1") == "1"
         lora = None
         if self.factors is not None:
             lora = dict(zip(("a13", "b13", "a2", "b2"), self.factors), scale=1.0)
@@ -451,7 +454,7 @@ class Layer:
             ep_module.ExpertParallelConfig(hidden=cfg["D"], experts=cfg["E"], intermediate=cfg["F"], top_k=cfg["K"],
                                            routing_mode=cfg["mode"], n_group=cfg["n_group"],
                                            topk_group=cfg["topk_group"], routed_scaling=cfg["scaling"],
-                                           expert_map=expert_map, dedup=dedup),
+                                           expert_map=expert_map, dedup=dedup, presum=presum),
             group, router_weight=self.router, router_bias=self.bias, w13=self.w13, w2=self.w2, shared=self.shared,
             device=self.device,
             chunks=int(os.environ["B200MOE_EP_CHUNKS"]) if "B200MOE_EP_CHUNKS" in os.environ else None,
@@ -714,7 +717,8 @@ def gpu_arm(args, cfg):
         # gathered weights (a small case of the workload's routing), asserted on every rank
         ep_check = ep_module.parity_check(group, device, routing_mode=cfg["mode"], n_group=cfg["n_group"],
                                           topk_group=cfg["topk_group"], routed_scaling=cfg["scaling"],
-                                          shared=cfg["shared"])
+                                          shared=cfg["shared"],
+                                          presum=os.environ.get("B200MOE_EP_PRESUM", "1") == "1")
     if args.workload == "c2":
         peaks, peak_kind = measured_peaks()
         fp8_peak = measure_fp8_peak(device)
@@ -839,6 +843,7 @@ def gpu_arm(args, cfg):
                    if not distributed else "ExpertParallelMoE.forward_backward",
                    "expert_parallel": world, "expert_map": layer.ep.config.expert_map if distributed else "local",
                    "dedup_dispatch": bool(distributed and layer.ep.config.dedup),
+                   "presum_return": bool(distributed and layer.ep.config.presum),
                    "rows_per_rank": per_rank_rows, "weights": "block-FP8 e4m3 128x128, random N(0,0.02)",
                    "activations": "e4m3 1x128 blocks", "weight_grads": "bf16 operands, fp32 sums, bf16 out",
                    "l2": "inputs exceed L2 (no flush needed)" if T * D * 2 > (126 << 20) else "inputs fit L2"},

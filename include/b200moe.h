@@ -335,7 +335,8 @@ int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const void* x, long
 
 /*
  * out[t] = residual[t] + sum_k weights[t,k] * src[slots[t,k]] (fp32 sums, k ascending, one
- * rounding).  weights NULL = 1, residual NULL = 0.  All row tensors bf16.
+ * rounding).  weights NULL = 1, residual NULL = 0.  All row tensors bf16.  A negative slot adds
+ * nothing (the expert-parallel layer's "this assignment lives on another rank").
  * Reference: src/mlops/kernels/moe_dispatch.py:136-196 (`combine`, `dispatch_backward`).
  */
 int b200moe_combine(const void* src, long long lds, long long src_rows, const int32_t* slots,

@@ -34,7 +34,8 @@ combine_kernel(const __nv_bfloat16* __restrict__ src, long long lds, long long s
     }
     for (int k = 0; k < K; ++k) {
       long long slot = st[k];
-      slot = slot < 0 ? 0 : (slot >= src_rows ? src_rows - 1 : slot);
+      if (slot < 0) continue;  // "no row here": a token copy whose assignment lives on another rank
+      slot = slot >= src_rows ? src_rows - 1 : slot;
       const float w = wt != nullptr ? wt[k] : 1.0f;
       const uint4 raw = *reinterpret_cast<const uint4*>(src + slot * lds + c);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);

@@ -113,7 +113,14 @@ def _dedup_case(rank, world):
     expected_rows, _ = ep.exchange(rows, plan, dist.group.WORLD)
     expected_w, _ = ep.exchange(row_w, plan, dist.group.WORLD)
     # de-duplicated
-    token, copy_ids, copy_w = ep.build_copies(mask, ids, weights, local, sum(plan.send_copies))
+    token, copy_ids, copy_w, token_copies = ep.build_copies(mask, ids, weights, local, sum(plan.send_copies))
+    # every token finds its copy for every rank that holds one of its experts, and only there
+    for t in range(mask.shape[0]):
+        for r in range(mask.shape[1]):
+            position = int(token_copies[t, r])
+            assert (position >= 0) == bool(mask[t, r])
+            if position >= 0:
+                assert int(token[position]) == t
     got_rows, _ = ep.exchange(x[token.long()], plan, dist.group.WORLD, copies=True)
     got_meta, _ = ep.exchange(torch.cat([copy_ids, copy_w.view(torch.int32)], dim=1), plan, dist.group.WORLD,
                               copies=True)

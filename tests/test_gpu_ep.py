@@ -37,3 +37,18 @@ def test_two_rank_expert_lora_matches_single_gpu():
     done = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
     assert "ep lora worker ok" in done.stdout
+
+
+def test_two_rank_parity_check_with_and_without_presummed_returns():
+    """`ep.parity_check` (what bench.py runs before its timed region at N > 1): group-limited
+    sigmoid routing with the de-duplicated dispatch, returning one pre-weighted row per token
+    copy (within the bf16 tolerance of the single-GPU output) or one row per assignment
+    (bit-equal), and plain softmax routing."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29615", str(ROOT / "tests" / "ep_check_worker.py")]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+    assert "ep check worker ok" in done.stdout

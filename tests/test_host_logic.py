@@ -77,7 +77,9 @@ def test_deduplicated_dispatch_reproduces_the_row_per_assignment_layout(world, l
     for s in range(world):
         mask = copy_mask(keys[s], world, local)
         counts = mask.sum(0)
-        token, ids, weight = build_copies(mask, keys[s], weights[s], local, int(counts.sum()))
+        token, ids, weight, token_copies = build_copies(mask, keys[s], weights[s], local, int(counts.sum()))
+        assert torch.equal(token_copies >= 0, mask)
+        assert torch.equal(token[token_copies[mask].long()].long(), mask.nonzero()[:, 0])
         sent.append((token, ids, weight, counts.tolist()))
         assert all(int(n) <= tokens[s] for n in counts)
     for d in range(world):
