@@ -103,6 +103,9 @@ struct GemmFp8Params {
 #ifdef B200_GEMM_TRACE
   long long* trace;
 #endif
+#ifdef B200_WAIT_TEST
+  int withhold_loads;  // test builds only: the producer issues no load, so every consumer's wait runs out
+#endif
 };
 
 // PAIR: the two CTAs of a cluster share a 256-row x 256-column tile (tcgen05.mma.cta_group::2).
@@ -350,6 +353,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           B200_TRACE(4, it, 0);
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           B200_TRACE(4, it, 1);
+#ifdef B200_WAIT_TEST
+          if (p.withhold_loads) continue;  // nothing is loaded and nothing arrives on full[s]
+#endif
           mbar_arrive_expect_tx(&full[s], Cfg::kABytes + Cfg::kBBytes);
           tma_load_2d(sA + s * Cfg::kABytes, &tmap_a, &full[s], kb * kBlockK, c.m0);
           if constexpr (PAIR && SPLIT) {
@@ -388,7 +394,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) {
         // Unwinding: give the copies that were issued a bounded chance to land before
         // this CTA's shared memory is released.
+#ifdef B200_WAIT_TEST
+        const uint32_t issued = p.withhold_loads ? 0u : it;
+#else
         const uint32_t issued = it;
+#endif
         for (int s = 0; s < kStages; ++s) {
           if (issued <= (uint32_t)s) continue;
           const uint32_t last = ((issued - 1 - s) / kStages) * kStages + s;
@@ -915,6 +925,21 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmF
 
 using namespace b200;
 
+#ifdef B200_WAIT_TEST
+// Test builds only (-DB200_WAIT_TEST=1, with a short -DB200_WAIT_LIMIT_CYCLES): when set, the
+// producers of the next GEMM launches load nothing, so the bounded waits of the other roles run
+// out, the kernel reports ERR_WAIT_TIMEOUT in the status block and returns.  Nothing traps,
+// faults or spins without a limit; a launch after the flag is cleared runs normally.
+static int g_withhold_loads = 0;
+extern "C" int b200moe_debug_withhold_loads(int on) {
+  g_withhold_loads = on ? 1 : 0;
+  return B200MOE_OK;
+}
+#define B200_SET_WITHHOLD(params) (params).withhold_loads = g_withhold_loads
+#else
+#define B200_SET_WITHHOLD(params) do {} while (0)
+#endif
+
 #ifdef B200_GEMM_TRACE
 static long long* g_trace_buffer = nullptr;
 // Debug builds only: the device buffer (kTraceSlots * kTraceIts * kTraceFields int64) that CTA 0
@@ -1008,6 +1033,7 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
   p.out_rows = fused ? tokens : rows_total;
   p.status = status;
   B200_SET_TRACE(p);
+  B200_SET_WITHHOLD(p);
   // The pair form (two CTAs per 256 x 256 tile) serves the plain and the scattered store of the
   // wide tile on request only (b200moe_set_gemm_pair(1) or B200MOE_GEMM_PAIR=1): it halves the
   // B traffic through shared memory, but its hand-backs cross the pair through mbarriers, and
@@ -1182,6 +1208,7 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.out_rows = rows_total;
   p.status = status;
   B200_SET_TRACE(p);
+  B200_SET_WITHHOLD(p);
   return launch_gemm<256, false, 1>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }
 

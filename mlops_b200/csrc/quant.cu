@@ -209,13 +209,16 @@ swiglu_quant_kernel(const __nv_bfloat16* __restrict__ h13, long long ldh, long l
 //   grad_h13     = [dgate | dup]  -> E4M3 with 1x128 scales (and bf16 when asked)
 //   act_scaled   = score * act    (bf16; operand of the down weight's gradient)
 // (reference: src/mlops/kernels/quack_moe/swiglu_rows.py:100-199)
+// gh_bf16 may alias h13 (the gradient written over the saved pre-activation): each thread reads
+// the sixteen h13 values of an iteration before it stores the sixteen gradients to the same
+// addresses, and no other thread touches them.
 __global__ void __launch_bounds__(kRowWarps * 32)
-dswiglu_routed_kernel(const __nv_bfloat16* __restrict__ h13, long long ldh,
+dswiglu_routed_kernel(const __nv_bfloat16* h13, long long ldh,  // may be the same buffer as gh_bf16
                       const __nv_bfloat16* __restrict__ rmat, long long ldr,
                       const float* __restrict__ route_weights, long long n_weights,
                       const int* __restrict__ order, long long rows, int F, float* __restrict__ dscore,
                       uint8_t* __restrict__ gh_q, long long ldq, float* __restrict__ gh_scales,
-                      long long s_row, long long s_kb, __nv_bfloat16* __restrict__ gh_bf16,
+                      long long s_row, long long s_kb, __nv_bfloat16* gh_bf16,
                       long long ldg, __nv_bfloat16* __restrict__ act_scaled, long long lda, float limit,
                       int limited, int* status) {
   const int lane = threadIdx.x & 31;

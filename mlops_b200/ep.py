@@ -781,3 +781,114 @@ def parity_check(group, device, *, routing_mode="softmax_then_topk", n_group=1, 
     assert result["grad_x_max_rel"] <= 2e-2 and result["grad_router_max_rel"] <= 2e-3, result
     assert result["grad_w13_max_rel"] <= 1e-3 and result["grad_w2_max_rel"] <= 1e-3, result
     return result
+
+
+# ---------------------------------------------------------------- the module contract
+class _ExpertParallelFunction(torch.autograd.Function):
+    """Autograd node of one expert-parallel layer call: forward and backward are the runtime's
+    own (collectives included); the saved plan travels in the context."""
+
+    @staticmethod
+    def forward(ctx, runtime, x, residual, expert_ids, routing_weights, router_weight, w13, w2, *shared):
+        output, aux, counts, psum, saved = runtime.forward(x, residual, expert_ids, routing_weights)
+        ctx.runtime, ctx.saved, ctx.shared = runtime, saved, len(shared)
+        ctx.mark_non_differentiable(counts)
+        return output, aux, counts, psum
+
+    @staticmethod
+    def backward(ctx, grad_output, grad_aux, _grad_counts, grad_psum):
+        need = ctx.needs_input_grad  # runtime, x, residual, ids, weights, router, w13, w2, shared...
+        if grad_output is None:
+            grad_output = torch.zeros(ctx.saved["shape"], dtype=ctx.saved["flat"].dtype,
+                                      device=ctx.saved["flat"].device)
+        grads = ctx.runtime.backward(ctx.saved, grad_output, grad_aux, grad_psum, need_router=bool(need[5]),
+                                     need_experts=bool(need[6] or need[7] or any(need[8:])))
+        ctx.saved = None  # the plan and the saved rows are released with the first backward
+        shared = [grads["grad_shared_w13"], grads["grad_shared_w2"]][:ctx.shared]
+        return (None, grads["grad_x"] if need[1] else None, grad_output if need[2] else None, None, None,
+                grads["grad_router"] if need[5] else None, grads["grad_w13"] if need[6] else None,
+                grads["grad_w2"] if need[7] else None, *[g if n else None for g, n in zip(shared, need[8:])])
+
+
+class ExpertParallelLayer(torch.nn.Module):
+    """`ExpertParallelMoE` as a module with ordinary autograd, the contract of the reference's
+    layer (`src/mlops/expert_parallel/quack/layer.py:28-59, 107-155, 219-246, 267-281`):
+
+    * `forward(x[, expert_ids, routing_weights])` with `x` bf16 `[tokens_per_rank, D]` (or any
+      leading shape) on the module's device returns the layer output; supplying both routing
+      tensors bypasses the layer's router (how externally routed models compose with it);
+      `last_statistics` holds `(aux, counts, probability_sum)` of the last call, `aux` and
+      `probability_sum` differentiable.
+    * `expert_parameters()` yields this rank's shard (`gate_up_weight [E/G, 2F, D]`,
+      `down_weight [E/G, D, F]` block-FP8 containers), `replicated_parameters()` the router and
+      the shared expert; `synchronize_replicated_parameters()` broadcasts the latter from rank 0
+      and `synchronize_replicated_gradients()` SUM-all-reduces their gradients (called by the
+      owner of the accumulation window; expert shards are never reduced over the group).
+    * `close()` releases the runtime; a closed layer refuses calls.
+    """
+
+    def __init__(self, config: ExpertParallelConfig, ep_group, *, gate_up_weight, down_weight, router_weight,
+                 router_bias=None, shared=None, device=None, weight_grad_dtype=None, chunks=None):
+        super().__init__()
+        from .weights import holds_blocks, split
+
+        if not (holds_blocks(gate_up_weight) and holds_blocks(down_weight)):
+            raise ValueError("gate_up_weight and down_weight must be block-FP8 containers of this rank's experts")
+        self.config, self.ep_group = config, ep_group
+        self.gate_up_weight = torch.nn.Parameter(gate_up_weight, requires_grad=gate_up_weight.requires_grad)
+        self.down_weight = torch.nn.Parameter(down_weight, requires_grad=down_weight.requires_grad)
+        self.router_weight = torch.nn.Parameter(router_weight, requires_grad=router_weight.requires_grad)
+        self.router_bias = router_bias
+        self.shared_w13 = self.shared_w2 = None
+        if shared is not None:
+            self.shared_w13 = torch.nn.Parameter(shared[0], requires_grad=shared[0].requires_grad)
+            self.shared_w2 = torch.nn.Parameter(shared[1], requires_grad=shared[1].requires_grad)
+        grad_dtype = weight_grad_dtype or gate_up_weight.dtype
+        self._runtime = ExpertParallelMoE(
+            config, ep_group, router_weight=self.router_weight.detach(), router_bias=router_bias,
+            w13=split(gate_up_weight), w2=split(down_weight),
+            shared=None if shared is None else (self.shared_w13.detach(), self.shared_w2.detach()),
+            device=device, weight_grad_dtype=grad_dtype, chunks=chunks)
+        self._closed = False
+        self.last_statistics = None
+        self.synchronize_replicated_parameters()
+
+    def expert_parameters(self):
+        yield self.gate_up_weight
+        yield self.down_weight
+
+    def replicated_parameters(self):
+        yield self.router_weight
+        if self.shared_w13 is not None:
+            yield self.shared_w13
+            yield self.shared_w2
+
+    def synchronize_replicated_parameters(self):
+        with torch.no_grad():
+            for parameter in self.replicated_parameters():
+                dist.broadcast(parameter.data, src=dist.get_global_rank(self.ep_group, 0), group=self.ep_group)
+            if self.router_bias is not None:
+                dist.broadcast(self.router_bias, src=dist.get_global_rank(self.ep_group, 0), group=self.ep_group)
+
+    def synchronize_replicated_gradients(self):
+        ExpertParallelMoE.synchronize_replicated_gradients(
+            [p.grad for p in self.replicated_parameters()], self.ep_group)
+
+    def forward(self, x, expert_ids=None, routing_weights=None):
+        if self._closed:
+            raise RuntimeError("Layer is closed")
+        if x.dtype != torch.bfloat16 or x.device != self._runtime.device or x.shape[-1] != self.config.hidden:
+            raise ValueError("Expected BF16 input on the configured CUDA device")
+        if (expert_ids is None) != (routing_weights is None):
+            raise ValueError("Supply both routing tensors or neither")
+        shared = () if self.shared_w13 is None else (self.shared_w13, self.shared_w2)
+        output, aux, counts, psum = _ExpertParallelFunction.apply(
+            self._runtime, x, torch.zeros_like(x), expert_ids, routing_weights, self.router_weight,
+            self.gate_up_weight, self.down_weight, *shared)
+        self.last_statistics = (aux, counts, psum)
+        return output
+
+    def close(self):
+        if not self._closed:
+            self._runtime.close()
+            self._closed = True

@@ -11,6 +11,7 @@ Names follow the reference's raw kernel functions (`route`, `sort_assignments`,
 from __future__ import annotations
 
 import functools
+import os
 
 import torch
 
@@ -52,6 +53,13 @@ class _Timed:
         return False
 
 
+# B200MOE_NVTX=1 brackets every wrapper call with an NVTX range named after it, so a timeline
+# shows the phases of a step as the reference's expert-parallel runtime marks its own
+# (src/mlops/expert_parallel/quack/streams.py:36-71). Off by default: a range costs a few
+# hundred nanoseconds on the host per launch.
+NVTX = os.environ.get("B200MOE_NVTX", "0") == "1"
+
+
 def _on_tensor_device(fn):
     """Runs `fn` with the device of its first CUDA tensor argument current, so the kernels are
     launched on that device and on ITS current stream whatever device the caller had selected
@@ -59,7 +67,7 @@ def _on_tensor_device(fn):
     current device; the wrappers therefore never rely on the caller having set it."""
 
     @functools.wraps(fn)
-    def guarded(*args, **kwargs):
+    def on_device(*args, **kwargs):
         for value in (*args, *kwargs.values()):
             if isinstance(value, torch.Tensor) and value.is_cuda:
                 if value.device.index == torch.cuda.current_device():
@@ -68,7 +76,18 @@ def _on_tensor_device(fn):
                     return fn(*args, **kwargs)
         return fn(*args, **kwargs)
 
-    return guarded
+    if not NVTX:
+        return on_device
+
+    @functools.wraps(fn)
+    def ranged(*args, **kwargs):
+        torch.cuda.nvtx.range_push("b200moe." + fn.__name__)
+        try:
+            return on_device(*args, **kwargs)
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+    return ranged
 
 
 def set_cta_limit(ctas: int) -> None:

@@ -219,3 +219,113 @@ def test_reference_contexts_reach_the_operator():
     assert torch.equal(out, out_wide)
     assert wide[1].dtype == torch.float32 and wide[0].dtype == router.dtype
     assert torch.equal(wide[1].bfloat16(), plain[1])  # the same fp32 sums, rounded later
+
+
+# ------------------------------------------------------------- the two-region composition
+def _containers(requires_grad=True):
+    from mlops_b200.weights import BlockFP8Weight
+
+    c1 = inputs.config1()
+    x = c1["x"].to(DEV).requires_grad_(requires_grad)
+    router = c1["router"].to(DEV).requires_grad_(requires_grad)
+    w13 = BlockFP8Weight.quantize(c1["w13"].to(DEV)).requires_grad_(requires_grad)
+    w2 = BlockFP8Weight.quantize(c1["w2"].to(DEV)).requires_grad_(requires_grad)
+    return c1, x, router, w13, w2
+
+
+def test_composed_regions_agree_with_the_fused_operator():
+    """`prepare` + `finish` give the fused operator's forward results bit for bit (the same
+    kernels in the same order); the gradients downstream of the `h13` gradient differ by its
+    bf16 rounding where it crosses the two regions."""
+    from mlops_b200 import composed, ops, provider
+
+    c1, x, router, w13, w2 = _containers()
+    dy, residual = c1["dy"].to(DEV), torch.randn_like(c1["x"]).to(DEV)
+    kwargs = dict(top_k=2, routing_mode="softmax_then_topk")
+    g_aux, g_psum = torch.tensor(0.3, device=DEV), torch.randn(8, device=DEV)
+    fused = provider.apply(x, residual, router, w13, w2, **kwargs)
+    fused_grads = torch.autograd.grad([fused[0], fused[1], fused[3]], [x, router, w13, w2], [dy, g_aux, g_psum])
+    split = composed.apply(x, residual, router, w13, w2, **kwargs)
+    split_grads = torch.autograd.grad([split[0], split[1], split[3]], [x, router, w13, w2], [dy, g_aux, g_psum])
+    ops.check_status(DEV)
+    for a, b in zip(fused, split):
+        assert torch.equal(a, b)
+    assert split[2].dtype == torch.int64 and not split[2].requires_grad
+    assert torch.equal(fused_grads[3], split_grads[3])  # grad_w2 never sees the crossing
+    # The h13 gradient is quantised to E4M3 from fp32 in the fused operator and from its bf16
+    # rounding here; a few percent of its elements land on the neighbouring E4M3 value, so what is
+    # computed from it agrees to E4M3 quantisation noise (about 1% in the Frobenius norm), not bits
+    for name, a, b in zip(("grad_x", "grad_router", "grad_w13"), fused_grads, split_grads):
+        frob = ((b.double() - a.double()).norm() / a.double().norm()).item()
+        assert frob <= 2e-2, (name, frob)
+    # frozen weights: no gradient, the rest unchanged
+    c1, x2, router2, w13f, w2f = _containers(requires_grad=False)
+    x2.requires_grad_(True)
+    launches = ops.LAUNCHES
+    out, *_ = composed.apply(x2, residual, router2, w13f, w2f, **kwargs)
+    (gx,) = torch.autograd.grad(out, [x2], dy)
+    frozen_launches = ops.LAUNCHES - launches
+    launches = ops.LAUNCHES
+    out, *_ = composed.apply(x, residual, router, w13, w2, **kwargs)
+    trainable = torch.autograd.grad(out, [x, router, w13, w2], dy)
+    assert (ops.LAUNCHES - launches) - frozen_launches == 3  # two weight gradients and the gather of x
+    assert torch.equal(gx, trainable[0])  # what is still computed is bit-identical
+
+
+def test_opcheck_of_the_region_operators_and_the_donating_backward():
+    from mlops_b200 import composed, ops
+
+    args = _plain_args()
+    x, _res, router, w13_q, w2_q, bias = args[:6]
+    w13_s, w2_s = args[-1]
+    utilities = ("test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic")
+    prepare_args = (x, router, w13_q, bias, 2, "softmax_then_topk", 1, 1, 1.0, [128], "float32", None, [w13_s])
+    results = torch.library.opcheck(composed.prepare_fwd, prepare_args, test_utils=utilities)
+    assert set(results.values()) == {"SUCCESS"}, results
+    with torch.no_grad():
+        aux, counts, psum, logits, weights, ids, order, offsets, slots, h13 = composed.prepare_fwd(*prepare_args)
+    h13 = h13.requires_grad_(True)
+    weights = weights.requires_grad_(True)
+    residual = torch.randn_like(x).detach().requires_grad_(True)
+    finish_args = (h13, w2_q, weights, order, offsets, slots, residual, 2, None, None, [w2_s])
+    results = torch.library.opcheck(composed.finish_fwd, finish_args, test_utils=utilities)
+    assert set(results.values()) == {"SUCCESS"}, results
+
+    dy = torch.randn_like(x).detach()
+    plain = composed.finish_bwd(dy, h13.detach(), w2_q, weights.detach(), order, offsets, slots, 2, None, None, True,
+                                [w2_s])
+    donated = h13.detach().clone()
+    rest = composed.finish_bwd_donate_h13(dy, donated, w2_q, weights.detach(), order, offsets, slots, 2, None, None,
+                                          True, [w2_s])
+    ops.check_status(DEV)
+    assert torch.equal(donated, plain[0])  # the gradient now sits where h13 was
+    for a, b in zip(rest, plain[1:]):
+        assert torch.equal(a, b)
+    schema = torch.ops.b200moe.moe_finish_bwd_donate_h13.default._schema
+    assert "!" in str(schema)  # the one mutating overload says so
+
+
+def test_reference_dispatch_can_select_the_composition():
+    mlops = _reference_or_skip()
+    from mlops.block_fp8 import BlockFP8Weight as ReferenceWeight
+    from mlops.dispatch import capture_dispatch, use_implementation
+
+    from mlops_b200 import composed, provider
+
+    provider.register()
+    composed.register()
+    c1 = inputs.config1()
+    x = c1["x"].to(DEV).requires_grad_(True)
+    w13c, w2c = ReferenceWeight.quantize(c1["w13"]), ReferenceWeight.quantize(c1["w2"])
+    w13 = ReferenceWeight(w13c._data.to(DEV), w13c._scale.to(DEV), dtype=w13c.dtype).requires_grad_(True)
+    w2 = ReferenceWeight(w2c._data.to(DEV), w2c._scale.to(DEV), dtype=w2c.dtype).requires_grad_(True)
+    router = c1["router"].to(DEV)
+    kwargs = dict(top_k=2, routing_mode="softmax_then_topk")
+    with capture_dispatch() as trace:
+        default_out, *_ = mlops.moe(x, torch.zeros_like(x), router, w13, w2, **kwargs)
+        with use_implementation("moe", "b200.moe.composed"):
+            out, *_ = mlops.moe(x, torch.zeros_like(x), router, w13, w2, **kwargs)
+    assert trace["moe"] == {"b200.moe": 1, "b200.moe.composed": 1}, trace
+    assert torch.equal(out, default_out)
+    grads = torch.autograd.grad(out, [x, w13, w2], c1["dy"].to(DEV))
+    assert grads[1].shape == w13.shape and grads[2].shape == w2.shape

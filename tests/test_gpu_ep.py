@@ -52,3 +52,16 @@ def test_two_rank_parity_check_with_and_without_presummed_returns():
     done = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
     assert "ep check worker ok" in done.stdout
+
+
+def test_two_rank_module_with_autograd():
+    """`ExpertParallelLayer`: nn.Module parameters, autograd through `forward`, caller-supplied
+    routes, replicated-parameter broadcast and gradient reduction, `close()`."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29616", str(ROOT / "tests" / "ep_module_worker.py")]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+    assert "ep module worker ok" in done.stdout
