@@ -71,7 +71,7 @@ NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_BF16_SUSTAINED = 1400.0
 BALANCED_BIAS_STD = 0.001
-SURVEY_BIAS_STD = 0.1
+SKEWED_BIAS_STD = 0.1
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the four FP8 GEMM launches of
 # one step, from the ncu capture of `python bench.py --workload c4p --steps 1 --warmup 1
@@ -155,7 +155,7 @@ def reference_sample_step(mlops, cfg, tokens, experts, seed=0):
     router = torch.randn(experts, D, generator=g) * 0.02
     w13 = BlockFP8Weight.quantize((torch.randn(experts, 2 * F, D, generator=g) * 0.02).bfloat16())
     w2 = BlockFP8Weight.quantize((torch.randn(experts, D, F, generator=g) * 0.02).bfloat16())
-    bias = torch.randn(experts, generator=g) * SURVEY_BIAS_STD if cfg["mode"] == "sigmoid_noaux_tc" else None
+    bias = torch.randn(experts, generator=g) * SKEWED_BIAS_STD if cfg["mode"] == "sigmoid_noaux_tc" else None
     n_group = cfg["n_group"] if experts % cfg["n_group"] == 0 and experts // cfg["n_group"] >= 2 else 1
     topk_group = cfg["topk_group"] if n_group > 1 else 1
     shared = ()
@@ -188,7 +188,7 @@ def port_sample_step(cfg, tokens, experts, seed=0):
     router = torch.randn(experts, D, generator=g) * 0.02
     w13 = O.quantize_blocks((torch.randn(experts, 2 * F, D, generator=g) * 0.02).bfloat16())
     w2 = O.quantize_blocks((torch.randn(experts, D, F, generator=g) * 0.02).bfloat16())
-    bias = torch.randn(experts, generator=g) * SURVEY_BIAS_STD if cfg["mode"] == "sigmoid_noaux_tc" else None
+    bias = torch.randn(experts, generator=g) * SKEWED_BIAS_STD if cfg["mode"] == "sigmoid_noaux_tc" else None
     n_group = cfg["n_group"] if experts % cfg["n_group"] == 0 and experts // cfg["n_group"] >= 2 else 1
 
     def step():
@@ -667,7 +667,7 @@ def extras(device, peaks, fp8_peak):
     """The configurations the headline does not cover, three timed steps each."""
     out = {}
     out["c2"] = run_c2(device, peaks, fp8_peak)
-    for key, bias_std in (("c3", BALANCED_BIAS_STD), ("c5", BALANCED_BIAS_STD), ("c4_skewed", SURVEY_BIAS_STD)):
+    for key, bias_std in (("c3", BALANCED_BIAS_STD), ("c5", BALANCED_BIAS_STD), ("c4_skewed", SKEWED_BIAS_STD)):
         cfg = dict(WORKLOADS["c4" if key == "c4_skewed" else key])
         gc.collect()
         torch.cuda.empty_cache()
@@ -683,7 +683,7 @@ def extras(device, peaks, fp8_peak):
         if fp8_peak.get("sustained"):
             entry["fp8_frac_of_measured_fp8_sustained"] = (gemms["fp8_tflops"] or 0.0) / fp8_peak["sustained"]
         if key == "c4_skewed":
-            entry["router_bias"] = f"N(0, {SURVEY_BIAS_STD}): the survey's figure, skewed load"
+            entry["router_bias"] = f"N(0, {SKEWED_BIAS_STD}): skewed load"
         out[key] = entry
         del layer
     gc.collect()

@@ -334,6 +334,20 @@ int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const void* x, long
                                int M, int N, void* out, int out_is_fp32, int32_t* status, void* stream);
 
 /*
+ * The same product written into a gradient buffer the caller keeps across calls:
+ *   out[g] = out[g] + scale * G[rows of g]^T @ X[rows of g]      (fp32, one rounding)
+ * so the gradients of several micro-batches accumulate in place, with an explicit gradient
+ * scale folded into the GEMM's store, and no separate add pass runs.  Groups without rows
+ * leave their block untouched.
+ * Reference: src/mlops/providers/sonicmoe/lora_destinations.py:28-432 (destinations for
+ * parameter-gradient products: accumulate in the GEMM epilogue, explicit gradient scale).
+ */
+int b200moe_grouped_wgrad_bf16_accumulate(const void* g, long long ldg, const void* x, long long ldx,
+                                          const int32_t* offsets, int groups, int segments,
+                                          long long rows_total, int M, int N, void* out, int out_is_fp32,
+                                          float scale, int32_t* status, void* stream);
+
+/*
  * out[t] = residual[t] + sum_k weights[t,k] * src[slots[t,k]] (fp32 sums, k ascending, one
  * rounding).  weights NULL = 1, residual NULL = 0.  All row tensors bf16.  A negative slot adds
  * nothing (the expert-parallel layer's "this assignment lives on another rank").

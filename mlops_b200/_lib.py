@@ -64,6 +64,7 @@ SIGNATURES = {
     ),
     "b200moe_finish_combine": (I, [P, LL, P, LL, P, LL, LL, I, P]),
     "b200moe_grouped_wgrad_bf16": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, P, P]),
+    "b200moe_grouped_wgrad_bf16_accumulate": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, F, P, P]),
     "b200moe_set_cta_limit": (I, [I]),
     "b200moe_set_gemm_pair": (I, [I]),
     "b200moe_lora_project": (I, [P, LL, P, I, P, I, LL, I, I, P, LL, P]),

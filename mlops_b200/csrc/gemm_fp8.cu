@@ -72,6 +72,15 @@ constexpr int kTraceFirst = 64, kTraceIts = 64, kTraceFields = 8, kTraceSlots = 
 #define B200_TRACE(slot, it, field) do {} while (0)
 #endif
 
+// Ablation builds (-DB200_GEMM_ABLATE=<bits>) take one part of the kernel's work out to show
+// what the others cost; their results are wrong on purpose and the shipped library is built
+// without them.  Bit 0: the epilogue hands an accumulator part back without reading it.
+// Bit 1: it reads the part but skips the multiply-adds.  Bit 2: after the first fill of the
+// stages the producer only signals them (no TMA traffic; the MMAs run on stale operands).
+#ifndef B200_GEMM_ABLATE
+#define B200_GEMM_ABLATE 0
+#endif
+
 struct GemmFp8Params {
   const float* a_scale;
   long long as_row_stride, as_kb_stride;
@@ -356,6 +365,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #ifdef B200_WAIT_TEST
           if (p.withhold_loads) continue;  // nothing is loaded and nothing arrives on full[s]
 #endif
+          if ((B200_GEMM_ABLATE & 4) && it >= (uint32_t)kStages) {
+            mbar_arrive(&full[s]);
+            continue;
+          }
           mbar_arrive_expect_tx(&full[s], Cfg::kABytes + Cfg::kBBytes);
           tma_load_2d(sA + s * Cfg::kABytes, &tmap_a, &full[s], kb * kBlockK, c.m0);
           if constexpr (PAIR && SPLIT) {
@@ -615,6 +628,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           auto tcol = [&](int cc) { return EPI == 1 ? (cc & 1) * 32 + (cc >> 1) * 128 : cc * 32; };
           auto promote = [&](const uint32_t (&r)[32], int cc) {
             const float sc = (EPI == 1 && cc >= 2) ? s_up : s;
+            if constexpr ((B200_GEMM_ABLATE & 2) != 0) {
+              acc[cc * 32] += sc * __uint_as_float(r[0]);
+              return;
+            }
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(sc, __uint_as_float(r[j]), acc[cc * 32 + j]);
           };
@@ -627,6 +644,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
               named_arrive(kAccBarrier + part, kRelThreads);
             }
           };
+          if constexpr ((B200_GEMM_ABLATE & 1) != 0) {
+            acc[0] += s + s_up;
+            release();
+            continue;
+          }
           uint32_t ra[32], rb[32];
           tmem_ld_32x32(taddr + tcol(0), ra);
           tmem_ld_32x32(taddr + tcol(1), rb);

@@ -38,6 +38,8 @@ struct WgradParams {
   int groups, M, N, rows_total;
   int segments;  // offsets holds segments*groups+1 entries; group g owns segment ranges s*groups+g
   int* status;
+  float scale;     // out = scale * product (+ what out held, when accumulate)
+  int accumulate;  // a caller's gradient buffer is updated in place, in fp32, with one rounding
 };
 
 template <typename OutT>
@@ -55,6 +57,42 @@ template <>
 __device__ __forceinline__ void store8<float>(float* dst, const float (&v)[8]) {
   *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
   *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+template <typename OutT>
+__device__ __forceinline__ void load8(const OutT* src, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* src, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* src, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// The store of eight sums: scaled, and added to what the destination holds when the caller
+// accumulates gradients over several calls (micro-batches) in one buffer.
+template <typename OutT>
+__device__ __forceinline__ void finish8(OutT* dst, float (&v)[8], float scale, int accumulate) {
+  if (accumulate) {
+    float old[8];
+    load8<OutT>(dst, old);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = fmaf(scale, v[i], old[i]);
+  } else if (scale != 1.0f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] *= scale;
+  }
+  store8<OutT>(dst, v);
 }
 
 template <typename OutT>
@@ -287,7 +325,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
               float v[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
-              store8<OutT>(orow + cc * 32 + j, v);
+              finish8<OutT>(orow + cc * 32 + j, v, p.scale, p.accumulate);
             }
           }
         }
@@ -582,7 +620,7 @@ grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __gr
               float v[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
-              store8<OutT>(orow + cc * 32 + j, v);
+              finish8<OutT>(orow + cc * 32 + j, v, p.scale, p.accumulate);
             }
           }
         }
@@ -633,10 +671,32 @@ static int launch_pair(const CUtensorMap& tg, const CUtensorMap& tx, const Wgrad
 
 using namespace b200;
 
+static int grouped_wgrad_impl(const void* g, long long ldg, const void* x, long long ldx, const int32_t* offsets,
+                              int groups, int segments, long long rows_total, int M, int N, void* out,
+                              int out_is_fp32, float scale, int accumulate, int32_t* status, void* stream);
+
 extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const void* x, long long ldx,
                                           const int32_t* offsets, int groups, int segments,
                                           long long rows_total, int M, int N, void* out, int out_is_fp32,
                                           int32_t* status, void* stream) {
+  return grouped_wgrad_impl(g, ldg, x, ldx, offsets, groups, segments, rows_total, M, N, out, out_is_fp32, 1.0f, 0,
+                            status, stream);
+}
+
+// out[g] += scale * G[rows of g]^T @ X[rows of g]: the gradient written into a buffer the caller
+// keeps across calls (a parameter's .grad over the micro-batches of an accumulation window).
+extern "C" int b200moe_grouped_wgrad_bf16_accumulate(const void* g, long long ldg, const void* x, long long ldx,
+                                                     const int32_t* offsets, int groups, int segments,
+                                                     long long rows_total, int M, int N, void* out,
+                                                     int out_is_fp32, float scale, int32_t* status,
+                                                     void* stream) {
+  return grouped_wgrad_impl(g, ldg, x, ldx, offsets, groups, segments, rows_total, M, N, out, out_is_fp32, scale, 1,
+                            status, stream);
+}
+
+static int grouped_wgrad_impl(const void* g, long long ldg, const void* x, long long ldx, const int32_t* offsets,
+                              int groups, int segments, long long rows_total, int M, int N, void* out,
+                              int out_is_fp32, float scale, int accumulate, int32_t* status, void* stream) {
   if (!g || !x || !offsets || !out || !status) return B200MOE_ERR_ARG;
   if (groups <= 0 || segments <= 0 || M <= 0 || N <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
   if (groups > kWgMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
@@ -646,6 +706,7 @@ extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const vo
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const size_t esz = out_is_fp32 ? 4 : 2;
   if (rows_total == 0) {
+    if (accumulate) return B200MOE_OK;  // nothing to add
     return cudaMemsetAsync(out, 0, (size_t)groups * M * N * esz, s) == cudaSuccess ? B200MOE_OK
                                                                                    : B200MOE_ERR_LAUNCH;
   }
@@ -675,6 +736,8 @@ extern "C" int b200moe_grouped_wgrad_bf16(const void* g, long long ldg, const vo
   p.rows_total = (int)rows_total;
   p.segments = segments;
   p.status = status;
+  p.scale = scale;
+  p.accumulate = accumulate;
   // Wide outputs go to the CTA-pair kernel (256-row tiles); narrow ones (LoRA factors) and the
   // B200MOE_WGRAD_SINGLE=1 escape hatch use the single-CTA kernel.
   static const bool force_single = [] {

@@ -20,6 +20,8 @@ operators (`docs/PROVIDERS.md:86-112`).
 
 from __future__ import annotations
 
+import math
+
 import torch
 from torch.utils.flop_counter import register_flop_formula
 
@@ -63,10 +65,14 @@ def moe_lora_fwd(hidden: torch.Tensor, residual: torch.Tensor, router_weight: to
                  down: torch.Tensor, a13: torch.Tensor, b13: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor,
                  router_bias: torch.Tensor, top_k: int, routing_mode: str, scale: float, n_group: int,
                  topk_group: int, routed_scaling: float, lengths: list[int], swiglu_limit: float | None,
+                 gradient_destinations: list[torch.Tensor], gradient_scale: float,
                  weight_components: list[torch.Tensor]) -> _THIRTEEN:
     """`(output, aux, counts, probability_sum, logits, route_weights, route_ids, order, offsets,
     slots, h13, t1, t2)`: the plain layer's results and residuals plus the two rank-r
-    intermediates `t1 = x A13^T`, `t2 = act A2^T` the factor gradients need."""
+    intermediates `t1 = x A13^T`, `t2 = act A2^T` the factor gradients need.
+    `gradient_destinations` (none, or four buffers for a13, b13, a2, b2) and `gradient_scale`
+    are not read here: they name where the backward pass accumulates the factor gradients."""
+    del gradient_destinations, gradient_scale
     w13, w2 = provider._with_scales(gate_up, down, weight_components)
     experts = gate_up.shape[0]
     with torch.no_grad(), torch.cuda.device(hidden.device):
@@ -96,7 +102,7 @@ def moe_lora_fwd(hidden: torch.Tensor, residual: torch.Tensor, router_weight: to
 @moe_lora_fwd.register_fake
 def _moe_lora_fwd_fake(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, router_bias, top_k,
                        routing_mode, scale, n_group, topk_group, routed_scaling, lengths, swiglu_limit,
-                       weight_components):
+                       gradient_destinations, gradient_scale, weight_components):
     rows = hidden.numel() // hidden.shape[-1]
     experts, assignments = router_weight.shape[0], rows * int(top_k)
     padded = -(-a13.shape[1] // 8) * 8
@@ -112,18 +118,13 @@ def _moe_lora_fwd_fake(hidden, residual, router_weight, gate_up, down, a13, b13,
     )
 
 
-@torch.library.custom_op("b200moe::moe_lora_bwd", mutates_args=())
-def moe_lora_bwd(grad_output: torch.Tensor, grad_aux: torch.Tensor, grad_probability_sum: torch.Tensor,
-                 hidden: torch.Tensor, router_weight: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
-                 a13: torch.Tensor, b13: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor, logits: torch.Tensor,
-                 route_weights: torch.Tensor, route_ids: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor,
-                 slots: torch.Tensor, h13: torch.Tensor, t1: torch.Tensor, t2: torch.Tensor, top_k: int,
-                 routing_mode: str, scale: float, lengths: list[int], weight_grad_dtype: torch.dtype | None,
-                 swiglu_limit: float | None, need_router: bool, need_w13: bool, need_w2: bool,
-                 need_factors: bool, weight_components: list[torch.Tensor]) -> _NINE:
-    """`(grad_hidden, grad_residual, grad_router, grad_w13, grad_w2, grad_a13, grad_b13, grad_a2,
-    grad_b2)`; gradients whose flag is false are empty placeholders and are not computed (a
-    frozen base launches no base-weight gradient: `tests/test_sonicmoe_lora.py:209-233`)."""
+def _lora_backward(grad_output, grad_aux, grad_probability_sum, hidden, router_weight, gate_up, down, a13, b13, a2,
+                   b2, logits, route_weights, route_ids, order, offsets, slots, h13, t1, t2, top_k, routing_mode,
+                   scale, lengths, weight_grad_dtype, swiglu_limit, need_router, need_w13, need_w2, need_factors,
+                   weight_components, destinations=None, gradient_scale=1.0):
+    """The backward pass of both operators below. With `destinations` (buffers for a13, b13, a2,
+    b2) the factor gradients are added, times `gradient_scale`, into those buffers by the
+    weight-gradient GEMMs' own stores and empty placeholders are returned in their place."""
     (w13_d, w13_s), (w2_d, w2_s) = provider._with_scales(gate_up, down, weight_components)
     experts = w13_d.shape[0]
     wdtype = torch.bfloat16 if weight_grad_dtype is None else weight_grad_dtype
@@ -150,14 +151,19 @@ def moe_lora_bwd(grad_output: torch.Tensor, grad_aux: torch.Tensor, grad_probabi
         grad_a13 = grad_b13 = grad_a2 = grad_b2 = empty(fdtype)
         if need_factors:
             row_weight = weights.reshape(-1)[order.long()].float()[:, None]
-            grad_b2 = ops.grouped_wgrad(dy_rows, (t2.float() * (row_weight * scale)).to(t2.dtype), offsets,
-                                        experts, fdtype)[:, :, :rank].contiguous()
-            grad_a2 = ops.grouped_wgrad((t2g.float() * scale).to(t2g.dtype), act_scaled, offsets, experts,
-                                        fdtype)[:, :rank].contiguous()
-            grad_b13 = ops.grouped_wgrad(gh_b, (t1.float() * scale).to(t1.dtype), offsets, experts,
-                                         fdtype)[:, :, :rank].contiguous()
-            grad_a13 = ops.grouped_wgrad((dt1.float() * scale).to(dt1.dtype), x_rows, offsets, experts,
-                                         fdtype)[:, :rank].contiguous()
+            into = dict(zip(("a13", "b13", "a2", "b2"), destinations)) if destinations else {}
+            product = lambda name, left, right: ops.grouped_wgrad(  # noqa: E731
+                left, right, offsets, experts, fdtype, accumulate_into=into.get(name),
+                scale=gradient_scale if into else 1.0)
+            grad_b2 = product("b2", dy_rows, (t2.float() * (row_weight * scale)).to(t2.dtype))
+            grad_a2 = product("a2", (t2g.float() * scale).to(t2g.dtype), act_scaled)
+            grad_b13 = product("b13", gh_b, (t1.float() * scale).to(t1.dtype))
+            grad_a13 = product("a13", (dt1.float() * scale).to(dt1.dtype), x_rows)
+            if into:  # the buffers hold the gradients; nothing is handed back
+                grad_a13 = grad_b13 = grad_a2 = grad_b2 = empty(fdtype)
+            else:
+                grad_b2, grad_b13 = grad_b2[:, :, :rank].contiguous(), grad_b13[:, :, :rank].contiguous()
+                grad_a2, grad_a13 = grad_a2[:, :rank].contiguous(), grad_a13[:, :rank].contiguous()
         dx_add = ops.lora_expand(dt1, a13p, offsets, wide_major=False, scale=scale)
         grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, w13_d, w13_s, offsets, b_mn_major=True, addend=dx_add)
         grad_h2 = ops.dispatch_backward(grad_rows, slots)
@@ -175,6 +181,70 @@ def moe_lora_bwd(grad_output: torch.Tensor, grad_aux: torch.Tensor, grad_probabi
         grad_h2.addmm_(grad_logits.to(flat.dtype), getattr(router_weight, "_data", router_weight).to(flat.dtype))
     return (grad_h2.reshape(hidden.shape), grad_output.clone(), grad_router, grad_w13, grad_w2, grad_a13, grad_b13,
             grad_a2, grad_b2)
+
+
+
+
+@torch.library.custom_op("b200moe::moe_lora_bwd", mutates_args=())
+def moe_lora_bwd(grad_output: torch.Tensor, grad_aux: torch.Tensor, grad_probability_sum: torch.Tensor,
+                 hidden: torch.Tensor, router_weight: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
+                 a13: torch.Tensor, b13: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor, logits: torch.Tensor,
+                 route_weights: torch.Tensor, route_ids: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor,
+                 slots: torch.Tensor, h13: torch.Tensor, t1: torch.Tensor, t2: torch.Tensor, top_k: int,
+                 routing_mode: str, scale: float, lengths: list[int], weight_grad_dtype: torch.dtype | None,
+                 swiglu_limit: float | None, need_router: bool, need_w13: bool, need_w2: bool,
+                 need_factors: bool, weight_components: list[torch.Tensor]) -> _NINE:
+    """`(grad_hidden, grad_residual, grad_router, grad_w13, grad_w2, grad_a13, grad_b13, grad_a2,
+    grad_b2)`; gradients whose flag is false are empty placeholders and are not computed (a
+    frozen base launches no base-weight gradient: `tests/test_sonicmoe_lora.py:209-233`)."""
+    return _lora_backward(grad_output, grad_aux, grad_probability_sum, hidden, router_weight, gate_up, down, a13, b13,
+                          a2, b2, logits, route_weights, route_ids, order, offsets, slots, h13, t1, t2, top_k,
+                          routing_mode, scale, lengths, weight_grad_dtype, swiglu_limit, need_router, need_w13,
+                          need_w2, need_factors, weight_components)
+
+
+_FIVE = tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]
+
+
+@torch.library.custom_op("b200moe::moe_lora_bwd_into",
+                         mutates_args=("dest_a13", "dest_b13", "dest_a2", "dest_b2"))
+def moe_lora_bwd_into(grad_output: torch.Tensor, grad_aux: torch.Tensor, grad_probability_sum: torch.Tensor,
+                      hidden: torch.Tensor, router_weight: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
+                      a13: torch.Tensor, b13: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor,
+                      logits: torch.Tensor, route_weights: torch.Tensor, route_ids: torch.Tensor,
+                      order: torch.Tensor, offsets: torch.Tensor, slots: torch.Tensor, h13: torch.Tensor,
+                      t1: torch.Tensor, t2: torch.Tensor, dest_a13: torch.Tensor, dest_b13: torch.Tensor,
+                      dest_a2: torch.Tensor, dest_b2: torch.Tensor, gradient_scale: float, top_k: int,
+                      routing_mode: str, scale: float, lengths: list[int], weight_grad_dtype: torch.dtype | None,
+                      swiglu_limit: float | None, need_router: bool, need_w13: bool, need_w2: bool,
+                      weight_components: list[torch.Tensor]) -> _FIVE:
+    """The backward pass with explicit destinations for the factor gradients:
+    `dest += gradient_scale * gradient`, formed in the store of each weight-gradient GEMM, so the
+    micro-batches of an accumulation window add up in the caller's buffers with no pass of their
+    own. Returns `(grad_hidden, grad_residual, grad_router, grad_w13, grad_w2)`. The form of the
+    reference's accumulating operators (src/mlops/providers/sonicmoe/lora_destinations.py:1-16)."""
+    result = _lora_backward(grad_output, grad_aux, grad_probability_sum, hidden, router_weight, gate_up, down, a13,
+                            b13, a2, b2, logits, route_weights, route_ids, order, offsets, slots, h13, t1, t2, top_k,
+                            routing_mode, scale, lengths, weight_grad_dtype, swiglu_limit, need_router, need_w13,
+                            need_w2, True, weight_components, destinations=(dest_a13, dest_b13, dest_a2, dest_b2),
+                            gradient_scale=gradient_scale)
+    return result[:5]
+
+
+@moe_lora_bwd_into.register_fake
+def _moe_lora_bwd_into_fake(grad_output, grad_aux, grad_probability_sum, hidden, router_weight, gate_up, down, a13,
+                            b13, a2, b2, logits, route_weights, route_ids, order, offsets, slots, h13, t1, t2,
+                            dest_a13, dest_b13, dest_a2, dest_b2, gradient_scale, top_k, routing_mode, scale,
+                            lengths, weight_grad_dtype, swiglu_limit, need_router, need_w13, need_w2,
+                            weight_components):
+    wdtype = torch.bfloat16 if weight_grad_dtype is None else weight_grad_dtype
+    rdtype = router_weight.dtype if weight_grad_dtype is None else weight_grad_dtype
+    new = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=hidden.device)  # noqa: E731
+    return (torch.empty_like(hidden, memory_format=torch.contiguous_format),
+            torch.empty_like(grad_output, memory_format=torch.contiguous_format),
+            new(tuple(router_weight.shape), rdtype) if need_router else new((0,), router_weight.dtype),
+            new(tuple(gate_up.shape), wdtype) if need_w13 else new((0,), wdtype),
+            new(tuple(down.shape), wdtype) if need_w2 else new((0,), wdtype))
 
 
 @moe_lora_bwd.register_fake
@@ -224,10 +294,12 @@ def _moe_lora_bwd_flops(grad_output, grad_aux, grad_probability_sum, hidden, rou
 
 def _setup_context(ctx, inputs, output):
     (hidden, _residual, router_weight, gate_up, down, a13, b13, a2, b2, _bias, top_k, routing_mode, scale,
-     _n_group, _topk_group, _scaling, lengths, swiglu_limit, weight_components) = inputs
+     _n_group, _topk_group, _scaling, lengths, swiglu_limit, gradient_destinations, gradient_scale,
+     weight_components) = inputs
     (_out, _aux, counts, _psum, logits, weights, ids, order, offsets, slots, h13, t1, t2) = output
     ctx.save_for_backward(hidden, router_weight, gate_up, down, a13, b13, a2, b2, logits, weights, ids, order,
                           offsets, slots, h13, t1, t2, *weight_components)
+    ctx.destinations, ctx.gradient_scale = list(gradient_destinations), float(gradient_scale)
     ctx.top_k, ctx.routing_mode, ctx.scale = int(top_k), routing_mode, float(scale)
     ctx.lengths, ctx.swiglu_limit, ctx.components = list(lengths), swiglu_limit, len(weight_components)
     ctx.weight_grad_dtype = provider._context_weight_gradient_dtype()
@@ -249,28 +321,44 @@ def _autograd_backward(ctx, grad_output, grad_aux, _g_counts, grad_probability_s
     wdtype = ctx.weight_grad_dtype
     if wdtype is None and ctx.logical != torch.bfloat16:
         wdtype = ctx.logical
-    grads = moe_lora_bwd(
-        grad_output, grad_aux, grad_probability_sum, *tensors, ctx.top_k, ctx.routing_mode, ctx.scale, ctx.lengths,
-        wdtype, ctx.swiglu_limit, bool(need[2]), bool(need[3]), bool(need[4]), bool(any(need[5:9])), components)
+    if ctx.destinations:
+        grads = (*moe_lora_bwd_into(
+            grad_output, grad_aux, grad_probability_sum, *tensors, *ctx.destinations, ctx.gradient_scale, ctx.top_k,
+            ctx.routing_mode, ctx.scale, ctx.lengths, wdtype, ctx.swiglu_limit, bool(need[2]), bool(need[3]),
+            bool(need[4]), components), None, None, None, None)  # the factors' gradients sit in the buffers
+    else:
+        grads = moe_lora_bwd(
+            grad_output, grad_aux, grad_probability_sum, *tensors, ctx.top_k, ctx.routing_mode, ctx.scale,
+            ctx.lengths, wdtype, ctx.swiglu_limit, bool(need[2]), bool(need[3]), bool(need[4]),
+            bool(any(need[5:9])), components)
     grad_router = grads[2]
     if ctx.weight_grad_dtype is None and need[2] and grad_router.dtype != router_weight.dtype:
         grad_router = grad_router.to(router_weight.dtype)
     picked = [grads[0], grads[1], grad_router, *grads[3:]]
-    return (*[g if n else None for g, n in zip(picked, need[:9])], *([None] * 9), [None] * ctx.components)
+    return (*[g if (n and g is not None) else None for g, n in zip(picked, need[:9])], *([None] * 9),
+            [None] * len(ctx.destinations), None, [None] * ctx.components)
 
 
 moe_lora_fwd.register_autograd(_autograd_backward, setup_context=_setup_context)
-provider._CONTAINER_OPERATORS.extend([moe_lora_fwd, moe_lora_bwd])
+provider._CONTAINER_OPERATORS.extend([moe_lora_fwd, moe_lora_bwd, moe_lora_bwd_into])
 for _cls in list(provider._DISPATCH_REGISTERED):  # containers registered before this module loaded
-    moe_lora_fwd.register_torch_dispatch(_cls, provider._unwrap_containers)
-    moe_lora_bwd.register_torch_dispatch(_cls, provider._unwrap_containers)
+    for _op in (moe_lora_fwd, moe_lora_bwd, moe_lora_bwd_into):
+        _op.register_torch_dispatch(_cls, provider._unwrap_containers)
 
 
 def expert_lora(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, *, top_k, routing_mode, scale,
                 router_bias=None, n_group=1, topk_group=1, routed_scaling=1.0, lengths=None, swiglu_limit=None,
-                implementation="b200", compute_precision=None):
+                implementation="b200", compute_precision=None, gradient_destinations=None, gradient_scale=1.0):
     """Returns `(output, aux, counts, probability_sum)`, differentiable in `hidden`, `residual`,
-    `router_weight`, the four factors and (when they ask for it) the base containers."""
+    `router_weight`, the four factors and (when they ask for it) the base containers.
+
+    `gradient_destinations` (a dict with buffers for all of `a13`, `b13`, `a2`, `b2`: each the
+    factor's shape, contiguous, bf16 or fp32, not overlapping) makes the backward pass ADD
+    `gradient_scale` times each factor's gradient into its buffer, inside the weight-gradient
+    GEMM's store, instead of returning it: the gradients of an accumulation window's
+    micro-batches sum in place (the factors' own `.grad` stays untouched). Ranks must be
+    multiples of 8 for this form (no padded rank to crop). Reference:
+    src/mlops/providers/sonicmoe/lora_destinations.py:28-432."""
     if implementation not in ("auto", "b200"):
         raise ValueError(f"mlops_b200.expert_lora serves implementation 'b200' (or 'auto'), not {implementation!r}")
     if compute_precision not in (None, "fp8_block"):
@@ -290,6 +378,26 @@ def expert_lora(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2
             raise ValueError(f"{name} must be bf16 with shape {expected[name]}")
     if rank > 64:
         raise ValueError("ranks up to 64 are supported")
+    destinations = []
+    if gradient_destinations is not None:
+        if sorted(gradient_destinations) != ["a13", "a2", "b13", "b2"]:
+            raise ValueError("gradient_destinations names a buffer for each of a13, b13, a2, b2")
+        if rank % 8:
+            raise ValueError("gradient destinations need a rank that is a multiple of 8")
+        destinations = [gradient_destinations[name] for name in ("a13", "b13", "a2", "b2")]
+        spans = []
+        for name, buffer in zip(("a13", "b13", "a2", "b2"), destinations):
+            if tuple(buffer.shape) != expected[name] or not buffer.is_contiguous() or \
+                    buffer.dtype not in (torch.bfloat16, torch.float32) or buffer.device != hidden.device:
+                raise ValueError(f"destination {name}: a contiguous bf16 or fp32 {expected[name]} tensor on the "
+                                 "layer's device is needed")
+            first = buffer.data_ptr()
+            last = first + buffer.numel() * buffer.element_size()
+            if any(first < stop and start < last for start, stop in spans):
+                raise ValueError("gradient destinations must not overlap")
+            spans.append((first, last))
+        if not math.isfinite(float(gradient_scale)):
+            raise ValueError("gradient_scale must be finite")
     for weight in (gate_up, down):
         if type(weight) not in provider._DISPATCH_REGISTERED:
             provider.register_container(type(weight))
@@ -298,5 +406,5 @@ def expert_lora(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2
     bias = router_bias if router_bias is not None else torch.empty(0, dtype=torch.float32, device=hidden.device)
     outputs = moe_lora_fwd(hidden, residual, router_weight, gate_up, down, a13, b13, a2, b2, bias, int(top_k),
                            str(routing_mode), float(scale), int(n_group), int(topk_group), float(routed_scaling),
-                           normalized, swiglu_limit, [])
+                           normalized, swiglu_limit, destinations, float(gradient_scale), [])
     return outputs[:4]

@@ -588,14 +588,33 @@ def grouped_gemm_fp8_swiglu(a_q, a_scale, w13_q, w13_scale, offsets, *, limit=No
 
 
 @_on_tensor_device
-def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
+def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16, *, accumulate_into=None, scale=1.0):
     """`[G, M, N]` with `out[e] = g[rows_e].T @ x[rows_e]` (bf16 operands, fp32 sums).
     `offsets` has `segments * groups + 1` entries; expert e sums over the ranges
-    `offsets[s*groups+e] .. offsets[s*groups+e+1]`."""
-    device = _need_cuda(g, x, offsets)
+    `offsets[s*groups+e] .. offsets[s*groups+e+1]`. With `accumulate_into` (a contiguous bf16 or
+    fp32 `[G, M, N]` buffer, e.g. a parameter's `.grad`) the product, times `scale`, is added to
+    the buffer in the GEMM's store and the buffer is returned."""
+    device = _need_cuda(g, x, offsets, accumulate_into)
     rows, m = g.shape
     n = x.shape[1]
     segments = (offsets.numel() - 1) // groups
+    if accumulate_into is not None:
+        out = accumulate_into
+        if tuple(out.shape) != (groups, m, n) or not out.is_contiguous() or \
+                out.dtype not in (torch.bfloat16, torch.float32):
+            raise NativeError(f"accumulate_into must be a contiguous bf16 or fp32 [{groups}, {m}, {n}] tensor")
+        if rows:
+            with _Timed("wgrad_bf16", 2.0 * rows * m * n):
+                check(
+                    lib.b200moe_grouped_wgrad_bf16_accumulate(
+                        g.data_ptr(), g.stride(0), x.data_ptr(), x.stride(0), offsets.data_ptr(), groups, segments,
+                        rows, m, n, out.data_ptr(), 1 if out.dtype == torch.float32 else 0, float(scale),
+                        status_block(device).data_ptr(), _stream(),
+                    ),
+                    "grouped_wgrad_accumulate",
+                )
+            _count()
+        return out
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise NativeError("weight gradients are written as bf16 or fp32")
     if rows == 0:
@@ -611,6 +630,8 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16):
             "grouped_wgrad",
         )
     _count()
+    if scale != 1.0:
+        out.mul_(scale)
     return out
 
 

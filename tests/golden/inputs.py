@@ -19,7 +19,7 @@ def checksum(*tensors) -> torch.Tensor:
 
 
 def config1():
-    """BASELINE config 1: T=512, D=256, 8 experts, top-2 softmax routing, F=512, seed 0."""
+    """Benchmark configuration 1 (the CPU-runnable case): T=512, D=256, 8 experts, top-2 softmax routing, F=512, seed 0."""
     torch.manual_seed(0)
     T, D, E, K, F = 512, 256, 8, 2, 512
     x = torch.randn(T, D).bfloat16()
@@ -69,7 +69,7 @@ def ep_case():
 
 def lora_case(rank=16):
     """A small expert-LoRA layer: T=96, D=128, 4 experts, top-2, F=128; factors as in
-    BASELINE config 5 (A ~ N(0, 0.02), B = 0.01 N(0, 1), bf16), alpha = rank (scale 1)."""
+    benchmark configuration 5 (A ~ N(0, 0.02), B = 0.01 N(0, 1), bf16), alpha = rank (scale 1)."""
     torch.manual_seed(23)
     T, D, E, K, F = 96, 128, 4, 2, 128
     x = torch.randn(T, D).bfloat16()

@@ -77,7 +77,7 @@ def test_opcheck_of_the_lora_operator():
                (torch.randn(8, 12, 512, generator=g) * 0.02), (torch.randn(8, 256, 12, generator=g) * 0.01)]
     factors = [f.bfloat16().to(DEV).requires_grad_(True) for f in factors]
     op_args = (x, residual, router, w13_q, w2_q, *factors, bias, 2, "softmax_then_topk", 1.0, 1, 1, 1.0, [128],
-               None, args[-1])
+               None, [], 1.0, args[-1])
     results = torch.library.opcheck(
         lora.moe_lora_fwd, op_args,
         test_utils=("test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic"))
@@ -87,7 +87,10 @@ def test_opcheck_of_the_lora_operator():
 def test_operator_schemas_are_functional_and_outside_the_reference_namespace():
     from mlops_b200 import lora, provider  # noqa: F401
 
-    for name in ("moe_fwd", "moe_bwd", "moe_lora_fwd", "moe_lora_bwd", "swiglu", "swiglu_bwd"):
+    from mlops_b200 import composed  # noqa: F401
+
+    for name in ("moe_fwd", "moe_bwd", "moe_lora_fwd", "moe_lora_bwd", "swiglu", "swiglu_bwd", "moe_prepare_fwd",
+                 "moe_prepare_bwd", "moe_finish_fwd", "moe_finish_bwd"):
         schema = getattr(torch.ops.b200moe, name).default._schema
         assert all(argument.alias_info is None for argument in schema.arguments)
         assert all(result.alias_info is None for result in schema.returns)

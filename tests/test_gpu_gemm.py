@@ -151,7 +151,7 @@ def test_repeatable_bitwise():
 
 
 def test_config2_shape_linearity_and_sampled_parity():
-    """BASELINE config 2 at full size (32 groups, Zipf split of 65536 rows, K=4096, N=2048):
+    """Benchmark configuration 2 (the standalone grouped GEMM) at full size (32 groups, Zipf split of 65536 rows, K=4096, N=2048):
     sampled rows against float64, plus linearity in the activation scales
     (gemm(2 * a_scale) == 2 * gemm(a_scale) exactly, a power-of-two factor)."""
     ops = _ops()

@@ -218,7 +218,7 @@ def test_qwen3_30b_a3b_geometry_with_lora_and_zipf_skew():
     with torch.no_grad():
         res = lora_module.moe_lora_fwd(x.to(DEV), residual.to(DEV), router.to(DEV), w13[0], w2[0],
                                        *[f.detach() for f in f_d], torch.empty(0, device=DEV), top_k,
-                                       "softmax_then_topk", 1.0, 1, 1, 1.0, [tokens], None, [w13[1], w2[1]])
+                                       "softmax_then_topk", 1.0, 1, 1, 1.0, [tokens], None, [], 1.0, [w13[1], w2[1]])
         assert torch.equal(res[0], out.detach())
         logits_d, order_d, offsets_d, h13_d, t1_d, t2_d = res[4], res[7], res[8], res[10], res[11], res[12]
         _a13p, _b13t, a2p, b2t, _rank = _kernel_factors(*[f.detach() for f in f_d])

@@ -92,8 +92,8 @@ def test_config1_against_oracle_and_reference_fixture(golden):
         return ((a.double().cpu() - e.double()).norm() / e.double().norm()).item()
 
     # vs the reference's bf16-on-dequantised-weights provider: its FP8 tests' bounds
-    # (output 4e-2 [5e-2 here, see tests/test_oracle_golden.py], dh2 8e-2, drouter 8e-2, dw 6e-2)
-    assert frob(result[0], fixture["output"]) < 5e-2
+    # (output 4e-2 [4.5e-2 here, see tests/test_oracle_golden.py], dh2 8e-2, drouter 8e-2, dw 6e-2)
+    assert frob(result[0], fixture["output"]) < 4.5e-2
     assert frob(grads[0], fixture["grad_x"]) < 8e-2
     assert frob(grads[2], fixture["grad_router"]) < 8e-2
     assert frob(grads[3][:, ::16, ::8], fixture["grad_w13_sample"]) < 6e-2

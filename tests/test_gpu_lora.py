@@ -141,3 +141,40 @@ def test_zero_b_factors_equal_the_plain_layer_and_frozen_base_launches_no_base_w
     grads = torch.autograd.grad(out2, [dev2["x"], t13, t2, *(dev2[n] for n in FACTORS)], dev2["dy"])
     assert ops.LAUNCHES - before == frozen + 2
     assert grads[1].shape == t13.shape and grads[2].shape == t2.shape
+
+
+def test_gradient_destinations_accumulate_in_the_gemm_store():
+    """Two micro-batches with explicit destinations: each factor's buffer ends up holding
+    `start + scale * (g1 + g2)` (the sums formed in fp32 inside the weight-gradient GEMMs'
+    stores), the factors' own `.grad` stays empty, and the input gradient is unchanged
+    (reference contract: src/mlops/providers/sonicmoe/lora_destinations.py:1-16)."""
+    from mlops_b200 import ops
+    from mlops_b200.lora import expert_lora
+
+    lc, dev, g13, g2 = _setup(16)
+    expected, grad_x = None, []
+    for seed in (1, 2):
+        x = (dev["x"].detach() * (1.0 + 0.25 * seed)).requires_grad_(True)
+        out, *_ = _call(dict(dev, x=x), g13, g2)
+        grads = torch.autograd.grad(out, [x, *(dev[n] for n in FACTORS)], dev["dy"])
+        grad_x.append(grads[0])
+        expected = [g.float() for g in grads[1:]] if expected is None else [e + g.float() for e, g in zip(expected, grads[1:])]
+    start = {name: torch.randn(dev[name].shape, device=DEV) for name in FACTORS}
+    buffers = {name: value.clone() for name, value in start.items()}
+    for i, seed in enumerate((1, 2)):
+        x = (dev["x"].detach() * (1.0 + 0.25 * seed)).requires_grad_(True)
+        out, *_ = expert_lora(x, dev["residual"], dev["router"], g13, g2, *(dev[n] for n in FACTORS),
+                              top_k=dev["top_k"], routing_mode=dev["routing_mode"], scale=dev["scale"],
+                              gradient_destinations=buffers, gradient_scale=0.5)
+        (gx,) = torch.autograd.grad(out, [x], dev["dy"], allow_unused=False)
+        assert torch.equal(gx, grad_x[i])
+    ops.check_status(DEV)
+    for name, total in zip(FACTORS, expected):
+        assert dev[name].grad is None
+        want = start[name] + 0.5 * total
+        torch.testing.assert_close(buffers[name], want, rtol=2e-2, atol=2e-2 * float(total.abs().mean()))
+        assert not torch.equal(buffers[name], start[name])
+    with pytest.raises(ValueError):
+        expert_lora(dev["x"], dev["residual"], dev["router"], g13, g2, *(dev[n] for n in FACTORS),
+                    top_k=dev["top_k"], routing_mode=dev["routing_mode"], scale=dev["scale"],
+                    gradient_destinations={"a13": buffers["a13"]})

@@ -118,8 +118,9 @@ def test_layer_restatement_against_reference_config1(golden):
 
     # The reference accepts 4e-2 for its row-scaled recipe on its own test shapes; on this
     # config E4M3 activations (row-scaled: 4.6e-2, 1x128: 4.4e-2) sit just above it, so the
-    # bound here is 5e-2 and the row-scaled figure is checked to be no better.
-    assert frob(fwd["output"], fixture["output"]) < 5e-2
+    # bound here is the measured 1x128 figure as a regression bound, 4.5e-2, and the row-scaled
+    # figure is checked to be no better.
+    assert frob(fwd["output"], fixture["output"]) < 4.5e-2
     row = O.forward_block_fp8(c1["x"], c1["residual"], logits, w13_q, w13_s, w2_q, w2_s,
                               top_k=c1["top_k"], routing_mode=c1["routing_mode"], act_scale="row")
     assert frob(fwd["output"], fixture["output"]) <= frob(row["output"], fixture["output"]) * 1.02

@@ -1,6 +1,8 @@
 """The allocation-free sort entry point (`b200moe_sort_assignments_static`), for hosts that
 cannot call the CUDA allocator: it must give exactly what `b200moe_sort_assignments` gives,
-call after call, although every call reuses the same built-in scratch array.
+call after call, although every call reuses the same built-in scratch array. The comparator,
+the workspace sort, is itself pinned: `tests/test_gpu_routing.py` holds it bit-exact against
+the stored outputs of the reference's `sort_assignments` and against the CPU restatement.
 
 Collected last on purpose (file name), so a failure here cannot hide another test's."""
 
