@@ -77,6 +77,24 @@ constexpr int kTraceFirst = 64, kTraceIts = 64, kTraceFields = 8, kTraceSlots = 
 // without them.  Bit 0: the epilogue hands an accumulator part back without reading it.
 // Bit 1: it reads the part but skips the multiply-adds.  Bit 2: after the first fill of the
 // stages the producer only signals them (no TMA traffic; the MMAs run on stale operands).
+// -DB200_GEMM_FMA2=0 builds the scalar form of the promotion (one fmaf per element) for comparison.
+#ifndef B200_GEMM_FMA2
+#define B200_GEMM_FMA2 1
+#endif
+// (a0, a1) += s * (r0, r1), each element rounded like a scalar fmaf.
+__device__ __forceinline__ void fma2(float& a0, float& a1, uint32_t r0, uint32_t r1, float s) {
+  asm("{\n\t.reg .b64 a, r, sc;\n\t"
+      "mov.b64 a, {%0, %1};\n\t"
+      "mov.b64 r, {%2, %3};\n\t"
+      "mov.b64 sc, {%4, %4};\n\t"
+      "fma.rn.f32x2 a, r, sc, a;\n\t"
+      "mov.b64 {%0, %1}, a;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "r"(r0), "r"(r1), "f"(s));
+}
+#ifndef B200_GEMM_VARIANT
+#define B200_GEMM_VARIANT 0
+#endif
 #ifndef B200_GEMM_ABLATE
 #define B200_GEMM_ABLATE 0
 #endif
@@ -123,7 +141,11 @@ struct GemmFp8Params {
 // CTA and K block instead of 48 KB), and a CTA's half of B is read once for both tensor cores.
 template <int BLOCK_N, bool PAIR = false>
 struct GemmCfg {
+#ifdef B200_GEMM_STAGES
+  static constexpr int kStages = B200_GEMM_STAGES;  // sensitivity builds only
+#else
   static constexpr int kStages = (PAIR || BLOCK_N == 128) ? 6 : 4;
+#endif
   static constexpr int kTileM = PAIR ? 2 * kBlockM : kBlockM;
   static constexpr int kABytes = kBlockM * kBlockK;
   static constexpr int kBBytes = (PAIR ? BLOCK_N / 2 : BLOCK_N) * kBlockK;
@@ -458,7 +480,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // the operands first: they have usually landed long ago, so this check is off the
         // path from the epilogue's release to the next multiplication
         if (lane == 0) B200_TRACE(mine, it, 0);
-        if (!mbar_spin_warp(PAIR ? &ready[s] : &full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
+        if (!((B200_GEMM_VARIANT & 4) ? mbar_wait_warp(PAIR ? &ready[s] : &full[s], ph, abort_flag, p.status, 2)
+                                      : mbar_spin_warp(PAIR ? &ready[s] : &full[s], ph, abort_flag, p.status, 2))) {
+          ok = false;
+          break;
+        }
         if (lane == 0) B200_TRACE(mine, it, 1);
         // Everything the multiplications need is computed before the barrier: once the buffer
         // is free, the fewer instructions lane 0 still has to get through the scheduler (next
@@ -520,9 +546,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!ok) break;
         // one lane reads the flag so that the warp leaves the loop together (a warp that split
         // here would come back to the hardware barrier with lanes missing)
-        int aborted = lane == 0 ? *abort_flag : 0;
-        aborted = __shfl_sync(0xffffffffu, aborted, 0);
-        if (aborted) { ok = false; break; }
+        if (!(B200_GEMM_VARIANT & 1) || (it & 15u) == mine) {
+          int aborted = lane == 0 ? *abort_flag : 0;
+          aborted = __shfl_sync(0xffffffffu, aborted, 0);
+          if (aborted) { ok = false; break; }
+        }
       }
     }
     if (!ok && lane == 0) {
@@ -618,7 +646,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ++ab;
           const int part = SPLIT ? buf * 2 + half : buf;  // what this warp waits for and hands back
           if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 0);
-          if (!mbar_spin_warp(&tfull[part], aph, abort_flag, p.status, 4)) { ok = false; break; }
+          if (!((B200_GEMM_VARIANT & 2) ? mbar_wait_warp(&tfull[part], aph, abort_flag, p.status, 4)
+                                        : mbar_spin_warp(&tfull[part], aph, abort_flag, p.status, 4))) {
+            ok = false;
+            break;
+          }
           if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 1);
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N +
@@ -632,8 +664,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
               acc[cc * 32] += sc * __uint_as_float(r[0]);
               return;
             }
+#if B200_GEMM_FMA2
+            // two multiply-adds per instruction (fma.rn.f32x2): same roundings, half the issue slots
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) fma2(acc[cc * 32 + j], acc[cc * 32 + j + 1], r[j], r[j + 1], sc);
+#else
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(sc, __uint_as_float(r[j]), acc[cc * 32 + j]);
+#endif
           };
           auto release = [&]() {
             tc_fence_before_sync();
@@ -669,9 +707,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // the 64 FMAs that follow (one per cycle, from both epilogue warps of a
             // sub-partition) keep the issuer warp from being scheduled, and the next
             // multiplication starts later than if the release had simply waited for them.
-            promote(ra, 2);
-            promote(rb, 3);
-            release();
+            if constexpr ((B200_GEMM_VARIANT & 8) != 0) {
+              release();
+              promote(ra, 2);
+              promote(rb, 3);
+            } else {
+              promote(ra, 2);
+              promote(rb, 3);
+              release();
+            }
             if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 3);
           }
         }
