@@ -17,7 +17,7 @@ Prints ONE JSON line (rank 0).
   workloads     (N = 1) the other configurations, three timed steps each: the standalone
                 grouped GEMM (c2, beside the reference's Triton kernel when it runs), the
                 Mixtral-shaped layer (c3), the Qwen3-shaped layer with LoRA and skew (c5), and the
-                headline layer with the survey's skewed selection bias (c4_skewed)
+                headline layer with a skewed selection bias, N(0, 0.1) (c4_skewed)
   hbm_kernels   (N = 1) GB/s of the routing / sort / quantise / SwiGLU / combine kernels
   ep_check      (N > 1) the expert-parallel layer against the single-GPU layer on the gathered
                 weights, on a small case, before the timed region
@@ -78,7 +78,7 @@ SKEWED_BIAS_STD = 0.1
 # --no-cpu --no-extras` (forward up, forward down, input gradient of down, input gradient of
 # up). Traffic is operands once + output once, so the full-size layer (8x the rows and
 # experts) scales by 8.
-GEMM_DRAM_BYTES_C4P = (1.264e9 + 0.279e9, 0.539e9 + 0.439e9, 0.720e9 + 0.129e9, 1.094e9 + 0.461e9)
+GEMM_DRAM_BYTES_C4P = (1.480e9 + 0.282e9, 0.539e9 + 0.440e9, 0.753e9 + 0.131e9, 1.095e9 + 0.462e9)
 
 
 def measured_peaks():
@@ -389,9 +389,9 @@ class Layer:
         self.dy_host = torch.randn(T, D, generator=torch.Generator().manual_seed(1000 + rank)).bfloat16().pin_memory()
         self.router = torch.randn(E, D, device=device, generator=gw) * 0.02
         # The selection bias of a trained DeepSeek-style router is the correction that BALANCES
-        # expert load; a random bias of the survey's scale (0.1) does the opposite at the sigmoid's
+        # expert load; a random bias of scale 0.1 does the opposite at the sigmoid's
         # tail (experts between 0 and ~8500 rows for a mean of 1024). The headline uses 0.001
-        # (bias path exercised, load near uniform); `c4_skewed` reports the survey's 0.1 beside it.
+        # (bias path exercised, load near uniform); `c4_skewed` reports 0.1 beside it.
         self.bias_std = bias_std
         self.bias = (torch.randn(E, device=device, generator=gw) * bias_std
                      if cfg["mode"] == "sigmoid_noaux_tc" else None)
@@ -589,6 +589,13 @@ def hbm_kernels(cfg, device, peaks):
     cases = {
         "route_topk": (route, 4.0 * T * E + 8.0 * T * K),
         "sort_assignments": (lambda: ops.sort_assignments(ids, E), 4.0 * R * 2 + 8.0 * R),
+        # forward: every token quantised once and written to its K rows (what the layer runs)
+        "quantize_rows_scatter": (lambda: ops.quantize_rows_scatter(x, slots),
+                                  2.0 * T * D + R * D + 4.0 * R * D / 128),
+        # backward: the same pass also writes the bf16 rows in expert order for the weight gradient
+        "quantize_rows_scatter_with_copy": (lambda: ops.quantize_rows_scatter(x, slots, with_copy=True),
+                                            2.0 * T * D + R * D + 4.0 * R * D / 128 + 2.0 * R * D),
+        # row-major form (one warp per output row), used where rows arrive in another order
         "quantize_rows_gather": (lambda: ops.quantize_rows(x, gather=order, gather_div=K),
                                  2.0 * T * D + R * D + 4.0 * R * D / 128),
         "swiglu_quantize": (lambda: ops.swiglu_quantize(h13), 4.0 * R * F + R * F + 4.0 * R * F / 128),
@@ -837,7 +844,7 @@ def gpu_arm(args, cfg):
         "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": cfg["name"], "tokens_per_gpu": T, "hidden": D, "experts": E, "intermediate": F,
                    "top_k": K, "routing": cfg["mode"],
-                   "router_bias": (f"N(0, {layer.bias_std}), balanced load (the survey's N(0, 0.1) is reported as "
+                   "router_bias": (f"N(0, {layer.bias_std}), balanced load (N(0, 0.1), skewed, is reported as "
                                    "workloads.c4_skewed)") if layer.bias is not None else None,
                    "shared_expert": bool(cfg["shared"]), "call": "provider.apply + torch.autograd.grad"
                    if not distributed else "ExpertParallelMoE.forward_backward",
@@ -877,8 +884,8 @@ def gpu_arm(args, cfg):
         del layer, buffers
         gc.collect()
         torch.cuda.empty_cache()
-        fp8_peak = measure_fp8_peak(device)
-        line["roofline"]["peak_measured_fp8"] = fp8_peak
+        fp8_peak = {} if args.no_extras else measure_fp8_peak(device)  # (a profiling run leaves it out)
+        line["roofline"]["peak_measured_fp8"] = fp8_peak or None
         if fp8_peak.get("sustained"):
             line["roofline"]["frac_of_measured_fp8_sustained"] = achieved / fp8_peak["sustained"]
         if not args.no_extras and args.workload == "c4":
@@ -899,7 +906,7 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    parser.add_argument("--no-extras", action="store_true", help="skip the other workloads and the HBM kernels")
+    parser.add_argument("--no-extras", action="store_true", help="skip the other workloads, the HBM kernels and the FP8 peak measurement")
     args = parser.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     if args.workload == "c2" and args.impl == "reference":
