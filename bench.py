@@ -491,7 +491,7 @@ class Layer:
 
 def gemm_summary(timings, steps):
     fp8 = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind == "fp8"]
-    wg = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind == "wgrad_bf16"]
+    wg = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind in ("wgrad_bf16", "wgrad_fp8")]
     fp8_ms, fp8_flops = sum(t for t, _ in fp8), sum(f for _, f in fp8)
     return {
         "fp8_tflops": fp8_flops / (fp8_ms * 1e-3) / 1e12 if fp8_ms > 0 else None,
@@ -674,12 +674,20 @@ def extras(device, peaks, fp8_peak):
     """The configurations the headline does not cover, three timed steps each."""
     out = {}
     out["c2"] = run_c2(device, peaks, fp8_peak)
-    for key, bias_std in (("c3", BALANCED_BIAS_STD), ("c5", BALANCED_BIAS_STD), ("c4_skewed", SKEWED_BIAS_STD)):
-        cfg = dict(WORKLOADS["c4" if key == "c4_skewed" else key])
+    from mlops_b200 import provider
+
+    for key, bias_std in (("c3", BALANCED_BIAS_STD), ("c5", BALANCED_BIAS_STD), ("c4_skewed", SKEWED_BIAS_STD),
+                          ("c4_fp8_weight_gradients", BALANCED_BIAS_STD)):
+        cfg = dict(WORKLOADS["c4" if key.startswith("c4_") else key])
         gc.collect()
         torch.cuda.empty_cache()
         layer = Layer(cfg, device, bias_std=bias_std)
-        ms, _launches, gemms = run_layer(layer, 3, 2, device)
+        # the optional recipe with E4M3 operands for the expert weight gradients (not the headline's)
+        previous = provider.set_weight_gradient_operands("fp8" if key == "c4_fp8_weight_gradients" else "bf16")
+        try:
+            ms, _launches, gemms = run_layer(layer, 3, 2, device)
+        finally:
+            provider.set_weight_gradient_operands(previous)
         _out, _gx, _aux, counts = layer.step(layer.x, layer.dy)
         routed, shared = layer.flops()
         entry = {"workload": cfg["name"], "ms_per_step": ms, "tokens_per_s": cfg["T"] / (ms * 1e-3),
@@ -691,6 +699,9 @@ def extras(device, peaks, fp8_peak):
             entry["fp8_frac_of_measured_fp8_sustained"] = (gemms["fp8_tflops"] or 0.0) / fp8_peak["sustained"]
         if key == "c4_skewed":
             entry["router_bias"] = f"N(0, {SKEWED_BIAS_STD}): skewed load"
+        if key == "c4_fp8_weight_gradients":
+            entry["weight_grads"] = ("E4M3 operands, one scale per expert and column (quantised per step), fp32 sums; "
+                                     "wgrad_tflops counts the GEMMs only, ms_per_step includes the quantisation")
         out[key] = entry
         del layer
     gc.collect()

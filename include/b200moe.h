@@ -348,6 +348,34 @@ int b200moe_grouped_wgrad_bf16_accumulate(const void* g, long long ldg, const vo
                                           float scale, int32_t* status, void* stream);
 
 /*
+ * E4M3 rows of x [rows, width] (bf16, token-major) with ONE SCALE PER (GROUP, COLUMN):
+ *   scales[g, c] = max(max over the rows of group g of |x[r, c]| * fp32(1/448), 1e-12)
+ *   q[r, c]      = e4m3_rn(clamp(x[r, c] / scales[g(r), c], -448, 448))     (RN division)
+ * `offsets` holds segments * groups + 1 ascending row boundaries; range i belongs to group
+ * i % groups (segments = 1: the sort's offsets).  The output stays token-major: the FP8 weight
+ * gradient reads it MN-major, no transpose is stored.  A group without rows gets scale 1e-12.
+ * Reference: src/mlops/kernels/quack_moe/quantize_transpose.py:126-133 (per-feature scales of an
+ * expert's token block, the row quantiser's equations applied to a column); the reference's
+ * implementation is a Triton kernel that also stores the transpose.
+ */
+int b200moe_quantize_columns(const void* x, long long ldx, long long rows, int width, const int32_t* offsets,
+                             int groups, int segments, void* q, long long ldq, float* scales, void* stream);
+
+/*
+ * Weight gradient from E4M3 operands:
+ *   out[g] (M x N) (+)= scale * (g_scale[g, :, None] * x_scale[g, None, :]) * (Gq[rows of g]^T @ Xq[rows of g])
+ * Gq [rows_total, M] and Xq [rows_total, N] are column-scaled E4M3 (b200moe_quantize_columns),
+ * multiplied on the tensor cores at the FP8 rate with fp32 sums over ALL rows of the group (the
+ * scales do not vary along the contraction, so nothing is promoted in between); accumulate != 0
+ * adds to what `out` holds.  M, N and both pitches are multiples of 16.
+ * Reference: src/mlops/kernels/quack_moe/wgrad.py:30-69 (`expert_weight_gradient`).
+ */
+int b200moe_grouped_wgrad_fp8(const void* g, long long ldg, const float* g_scale, const void* x, long long ldx,
+                              const float* x_scale, const int32_t* offsets, int groups, int segments,
+                              long long rows_total, int M, int N, void* out, int out_is_fp32, float scale,
+                              int accumulate, int32_t* status, void* stream);
+
+/*
  * out[t] = residual[t] + sum_k weights[t,k] * src[slots[t,k]] (fp32 sums, k ascending, one
  * rounding).  weights NULL = 1, residual NULL = 0.  All row tensors bf16.  A negative slot adds
  * nothing (the expert-parallel layer's "this assignment lives on another rank").

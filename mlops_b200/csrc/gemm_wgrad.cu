@@ -28,7 +28,7 @@ constexpr int kWgPanelBytes = kWgBlockK * 128;            // 64 K-rows x 64 bf16
 constexpr int kWgABytes = (kWgBlockM / 64) * kWgPanelBytes;  // 16 KB
 constexpr int kWgBBytes = (kWgBlockN / 64) * kWgPanelBytes;  // 32 KB
 constexpr int kWgTileBytes = kWgStages * (kWgABytes + kWgBBytes);
-constexpr int kWgSmemBytes = 1024 + kWgTileBytes + 256 + 4 * 4104;
+constexpr int kWgSmemBytes = 1024 + kWgTileBytes + 256 + 4 * 4104;  // (the same for E4M3: 128-row stages of 48 KB)
 constexpr int kWgTmemCols = 2 * kWgBlockN;
 constexpr int kWgMaxOffsets = 4097;  // segments * groups + 1 entries are cached in shared memory
 
@@ -40,6 +40,25 @@ struct WgradParams {
   int* status;
   float scale;     // out = scale * product (+ what out held, when accumulate)
   int accumulate;  // a caller's gradient buffer is updated in place, in fp32, with one rounding
+  // E4M3 operands (FP8 kernel only): one fp32 scale per group and column of G ([groups, M]) and of
+  // X ([groups, N]); the product of a group is multiplied by g_scale[m] * x_scale[n] at the store.
+  const float* g_scale;
+  const float* x_scale;
+};
+
+// Geometry of a K block in shared memory.  A panel is 128 bytes of an operand's columns for every
+// K-row of the block: 64 bf16 columns x 64 rows, or 128 E4M3 columns x 128 rows -- 16 KB of G and
+// 32 KB of X per stage either way.
+template <bool FP8>
+struct WgGeom {
+  static constexpr int kBlockK = FP8 ? 128 : 64;               // K-rows per stage
+  static constexpr int kPanelCols = FP8 ? 128 : 64;            // columns in 128 bytes
+  static constexpr int kPanelBytes = kBlockK * 128;
+  static constexpr int kAPanels = kWgBlockM / kPanelCols;
+  static constexpr int kBPanels = kWgBlockN / kPanelCols;
+  static constexpr int kABytes = kAPanels * kPanelBytes;
+  static constexpr int kBBytes = kBPanels * kPanelBytes;
+  static constexpr int kMmaK = FP8 ? 32 : 16;                  // K-rows per tcgen05.mma
 };
 
 template <typename OutT>
@@ -95,14 +114,17 @@ __device__ __forceinline__ void finish8(OutT* dst, float (&v)[8], float scale, i
   store8<OutT>(dst, v);
 }
 
-template <typename OutT>
+template <typename OutT, bool FP8>
 __global__ void __launch_bounds__(kWgThreads, 1)
 grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_x,
                      const WgradParams p) {
+  using Geo = WgGeom<FP8>;
+  constexpr int kBlockK = Geo::kBlockK;
+  constexpr int kABytes = Geo::kABytes, kBBytes = Geo::kBBytes, kPanelBytes = Geo::kPanelBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + kWgStages * kWgABytes;
+  uint8_t* sB = smem + kWgStages * kABytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWgTileBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kWgStages;
@@ -184,19 +206,19 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
         for (int seg = 0; seg < p.segments && ok; ++seg) {
           int lo, hi;
           group_range(g, seg, lo, hi);
-          const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+          const int num_kb = (hi - lo + kBlockK - 1) / kBlockK;
           for (int kb = 0; kb < num_kb; ++kb, ++it) {
             const int s = it % kWgStages;
             const uint32_t ph = (it / kWgStages) & 1;
             if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
-            mbar_arrive_expect_tx(&full[s], kWgABytes + kWgBBytes);
-            const int krow = lo + kb * kWgBlockK;
+            mbar_arrive_expect_tx(&full[s], kABytes + kBBytes);
+            const int krow = lo + kb * kBlockK;
 #pragma unroll
-            for (int pnl = 0; pnl < kWgBlockM / 64; ++pnl)
-              tma_load_2d(sA + s * kWgABytes + pnl * kWgPanelBytes, &tmap_g, &full[s], m0 + pnl * 64, krow);
+            for (int pnl = 0; pnl < Geo::kAPanels; ++pnl)
+              tma_load_2d(sA + s * kABytes + pnl * kPanelBytes, &tmap_g, &full[s], m0 + pnl * Geo::kPanelCols, krow);
 #pragma unroll
-            for (int pnl = 0; pnl < kWgBlockN / 64; ++pnl)
-              tma_load_2d(sB + s * kWgBBytes + pnl * kWgPanelBytes, &tmap_x, &full[s], n0 + pnl * 64, krow);
+            for (int pnl = 0; pnl < Geo::kBPanels; ++pnl)
+              tma_load_2d(sB + s * kBBytes + pnl * kPanelBytes, &tmap_x, &full[s], n0 + pnl * Geo::kPanelCols, krow);
           }
         }
       }
@@ -213,7 +235,8 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
     }
   } else if (warp == 1) {
     // All 32 lanes stay in the loop: they zero the K tail together; lane 0 issues.
-    constexpr uint32_t idesc = make_idesc(1, 1, 1, 1, kWgBlockM, kWgBlockN);
+    constexpr uint32_t idesc = FP8 ? make_idesc(0, 0, 1, 1, kWgBlockM, kWgBlockN)   // E4M3 x E4M3, both MN-major
+                                   : make_idesc(1, 1, 1, 1, kWgBlockM, kWgBlockN);  // bf16 x bf16
     uint32_t it = 0, tb = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -222,7 +245,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
       for (int seg = 0; seg < p.segments; ++seg) {
         int lo, hi;
         group_range(g, seg, lo, hi);
-        total_kb += (hi - lo + kWgBlockK - 1) / kWgBlockK;
+        total_kb += (hi - lo + kBlockK - 1) / kBlockK;
       }
       if (total_kb == 0) continue;
       const int buf = tb & 1;
@@ -233,20 +256,20 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
       for (int seg = 0; seg < p.segments && ok; ++seg) {
         int lo, hi;
         group_range(g, seg, lo, hi);
-        const int num_kb = (hi - lo + kWgBlockK - 1) / kWgBlockK;
+        const int num_kb = (hi - lo + kBlockK - 1) / kBlockK;
         for (int kb = 0; kb < num_kb; ++kb, ++it, ++done_kb) {
           const int s = it % kWgStages;
           const uint32_t ph = (it / kWgStages) & 1;
           if (!mbar_wait_warp(&full[s], ph, abort_flag, p.status, 22)) { ok = false; break; }
-          const int valid = hi - lo - kb * kWgBlockK;
-          if (valid < kWgBlockK) {
-            // rows [valid, 64) of every panel of BOTH operands: 128 bytes each, 16 bytes per
+          const int valid = hi - lo - kb * kBlockK;
+          if (valid < kBlockK) {
+            // rows [valid, kBlockK) of every panel of BOTH operands: 128 bytes each, 16 bytes per
             // lane-step.  (Zeroing one operand would leave 0 x Inf = NaN when the next group's
             // rows hold an Inf or a NaN: groups must stay isolated.)
-            const int nbytes = (kWgBlockK - valid) * 128;
-            for (int pnl = 0; pnl < kWgBlockM / 64 + kWgBlockN / 64; ++pnl) {
-              uint8_t* base = (pnl < kWgBlockM / 64 ? sA + s * kWgABytes + pnl * kWgPanelBytes
-                                                    : sB + s * kWgBBytes + (pnl - kWgBlockM / 64) * kWgPanelBytes) +
+            const int nbytes = (kBlockK - valid) * 128;
+            for (int pnl = 0; pnl < Geo::kAPanels + Geo::kBPanels; ++pnl) {
+              uint8_t* base = (pnl < Geo::kAPanels ? sA + s * kABytes + pnl * kPanelBytes
+                                                   : sB + s * kBBytes + (pnl - Geo::kAPanels) * kPanelBytes) +
                               valid * 128;
               for (int o = lane * 16; o < nbytes; o += 32 * 16)
                 *reinterpret_cast<uint4*>(base + o) = make_uint4(0, 0, 0, 0);
@@ -256,15 +279,16 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
           __syncwarp();
           tc_fence_after_sync();
           if (lane == 0) {
-            const uint32_t a_addr = smem_u32(sA + s * kWgABytes);
-            const uint32_t b_addr = smem_u32(sB + s * kWgBBytes);
-            const uint64_t adesc = make_smem_desc(a_addr, kWgPanelBytes, 1024);
-            const uint64_t bdesc = make_smem_desc(b_addr, kWgPanelBytes, 1024);
+            const uint32_t a_addr = smem_u32(sA + s * kABytes);
+            const uint32_t b_addr = smem_u32(sB + s * kBBytes);
+            const uint64_t adesc = make_smem_desc(a_addr, kPanelBytes, 1024);
+            const uint64_t bdesc = make_smem_desc(b_addr, kPanelBytes, 1024);
             const uint32_t d_tmem = tmem_base + buf * kWgBlockN;
 #pragma unroll
-            for (int k = 0; k < kWgBlockK / 16; ++k) {
-              const uint64_t step = (uint64_t)((k * 16 * 128) >> 4);
-              umma_f16(d_tmem, adesc + step, bdesc + step, idesc, (done_kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kBlockK / Geo::kMmaK; ++k) {
+              const uint64_t step = (uint64_t)((k * Geo::kMmaK * 128) >> 4);
+              if constexpr (FP8) umma_f8(d_tmem, adesc + step, bdesc + step, idesc, (done_kb > 0 || k > 0) ? 1u : 0u);
+              else umma_f16(d_tmem, adesc + step, bdesc + step, idesc, (done_kb > 0 || k > 0) ? 1u : 0u);
             }
             umma_commit(&empty[s]);
             if (done_kb == total_kb - 1) umma_commit(&tfull[buf]);
@@ -299,6 +323,12 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
       const int m = m0 + q * 32 + lane;
       const int col0 = n0 + half * kCols;
       OutT* orow = out + ((long long)g * p.M + m) * p.N + col0;
+      float row_scale = 1.0f;
+      const float* col_scale = nullptr;
+      if constexpr (FP8) {
+        row_scale = m < p.M ? p.g_scale[(long long)g * p.M + m] : 0.f;
+        col_scale = p.x_scale + (long long)g * p.N + col0;
+      }
       int buf = 0;
       if (has_rows) {
         buf = tb & 1;
@@ -325,6 +355,13 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
               float v[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
+              if constexpr (FP8) {
+                const float4 s0 = *reinterpret_cast<const float4*>(col_scale + cc * 32 + j);
+                const float4 s1 = *reinterpret_cast<const float4*>(col_scale + cc * 32 + j + 4);
+                const float cs[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] *= row_scale * cs[i];
+              }
               finish8<OutT>(orow + cc * 32 + j, v, p.scale, p.accumulate);
             }
           }
@@ -738,6 +775,8 @@ static int grouped_wgrad_impl(const void* g, long long ldg, const void* x, long 
   p.status = status;
   p.scale = scale;
   p.accumulate = accumulate;
+  p.g_scale = nullptr;
+  p.x_scale = nullptr;
   // Wide outputs go to the CTA-pair kernel (256-row tiles); narrow ones (LoRA factors) and the
   // B200MOE_WGRAD_SINGLE=1 escape hatch use the single-CTA kernel.
   static const bool force_single = [] {
@@ -750,12 +789,82 @@ static int grouped_wgrad_impl(const void* g, long long ldg, const void* x, long 
   const long long tiles = (long long)groups * ((M + kWgBlockM - 1) / kWgBlockM) * ((N + kWgBlockN - 1) / kWgBlockN);
   long long grid = tiles < sm_count() ? tiles : sm_count();
   if (out_is_fp32) {
-    auto kern = grouped_wgrad_kernel<float>;
+    auto kern = grouped_wgrad_kernel<float, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmemBytes) != cudaSuccess)
       return B200MOE_ERR_LAUNCH;
     kern<<<(unsigned)grid, kWgThreads, kWgSmemBytes, s>>>(tg, tx, p);
   } else {
-    auto kern = grouped_wgrad_kernel<__nv_bfloat16>;
+    auto kern = grouped_wgrad_kernel<__nv_bfloat16, false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmemBytes) != cudaSuccess)
+      return B200MOE_ERR_LAUNCH;
+    kern<<<(unsigned)grid, kWgThreads, kWgSmemBytes, s>>>(tg, tx, p);
+  }
+  return launch_status();
+}
+
+// The same products from E4M3 operands: G and X quantised with one scale per (group, column)
+// (b200moe_quantize_columns), multiplied at the FP8 rate with fp32 sums over all of a group's
+// rows, and scaled by g_scale[g, m] * x_scale[g, n] at the store.  Behavioural model: the
+// reference's FP8 weight gradient (src/mlops/kernels/quack_moe/wgrad.py:30-69: both operands
+// quantised per feature over the expert's tokens, one GEMM with exact K, epilogue acc * xs * ws).
+extern "C" int b200moe_grouped_wgrad_fp8(const void* g, long long ldg, const float* g_scale, const void* x,
+                                         long long ldx, const float* x_scale, const int32_t* offsets, int groups,
+                                         int segments, long long rows_total, int M, int N, void* out,
+                                         int out_is_fp32, float scale, int accumulate, int32_t* status,
+                                         void* stream) {
+  if (!g || !x || !g_scale || !x_scale || !offsets || !out || !status) return B200MOE_ERR_ARG;
+  if (groups <= 0 || segments <= 0 || M <= 0 || N <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
+  if (groups > kWgMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  if ((long long)groups * segments + 1 > kWgMaxOffsets) return B200MOE_ERR_LIMIT;
+  if ((M % 16) || (N % 16) || (ldg % 16) || (ldx % 16)) return B200MOE_ERR_ALIGN;
+  if (((uintptr_t)g & 15) || ((uintptr_t)x & 15) || ((uintptr_t)out & 15) || ((uintptr_t)g_scale & 15) ||
+      ((uintptr_t)x_scale & 15))
+    return B200MOE_ERR_ALIGN;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const size_t esz = out_is_fp32 ? 4 : 2;
+  if (rows_total == 0) {
+    if (accumulate) return B200MOE_OK;
+    return cudaMemsetAsync(out, 0, (size_t)groups * M * N * esz, s) == cudaSuccess ? B200MOE_OK
+                                                                                   : B200MOE_ERR_LAUNCH;
+  }
+  using Geo = WgGeom<true>;
+  CUtensorMap tg, tx;
+  {
+    uint64_t dims[2] = {(uint64_t)M, (uint64_t)rows_total};
+    uint64_t strides[1] = {(uint64_t)ldg};
+    uint32_t box[2] = {(uint32_t)Geo::kPanelCols, (uint32_t)Geo::kBlockK};
+    int r = encode_tensor_map(&tg, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, g, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)rows_total};
+    uint64_t strides[1] = {(uint64_t)ldx};
+    uint32_t box[2] = {(uint32_t)Geo::kPanelCols, (uint32_t)Geo::kBlockK};
+    int r = encode_tensor_map(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != B200MOE_OK) return r;
+  }
+  WgradParams p;
+  p.out = out;
+  p.offsets = offsets;
+  p.groups = groups;
+  p.M = M;
+  p.N = N;
+  p.rows_total = (int)rows_total;
+  p.segments = segments;
+  p.status = status;
+  p.scale = scale;
+  p.accumulate = accumulate;
+  p.g_scale = g_scale;
+  p.x_scale = x_scale;
+  const long long tiles = (long long)groups * ((M + kWgBlockM - 1) / kWgBlockM) * ((N + kWgBlockN - 1) / kWgBlockN);
+  long long grid = tiles < sm_count() ? tiles : sm_count();
+  if (out_is_fp32) {
+    auto kern = grouped_wgrad_kernel<float, true>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmemBytes) != cudaSuccess)
+      return B200MOE_ERR_LAUNCH;
+    kern<<<(unsigned)grid, kWgThreads, kWgSmemBytes, s>>>(tg, tx, p);
+  } else {
+    auto kern = grouped_wgrad_kernel<__nv_bfloat16, true>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgSmemBytes) != cudaSuccess)
       return B200MOE_ERR_LAUNCH;
     kern<<<(unsigned)grid, kWgThreads, kWgSmemBytes, s>>>(tg, tx, p);

@@ -339,6 +339,123 @@ quantize_blocks_kernel(const SrcT* __restrict__ w, int out, int in, int blocks_o
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Column-scaled E4M3 for the FP8 weight gradient: the rows of a group (an expert's tokens)
+// share one scale per COLUMN, scale = max(amax over the group's rows * fp32(1/448), 1e-12),
+// the row quantiser's equations applied to a column (reference: the per-feature scales of
+// src/mlops/kernels/quack_moe/quantize_transpose.py:126-133).  The output stays token-major:
+// the weight-gradient GEMM reads both operands MN-major, so no transpose is ever stored.
+// `offsets` holds segments * groups + 1 row boundaries; range i belongs to group i % groups.
+// Pass 1: column maxima of every 256-row x 256-column piece, merged with atomicMax on the bit
+// pattern (non-negative floats order like their bits).  Pass 2: maxima -> scales in place.
+// Pass 3: the cast.
+// ---------------------------------------------------------------------------------------
+constexpr int kColRows = 256;  // rows per block: 8 warps x 32 rows
+
+// The range (index into offsets) that holds row r; ranges may be empty.
+__device__ __forceinline__ int range_of_row(const int* __restrict__ offsets, int ranges, int r) {
+  int lo = 0, hi = ranges;  // invariant: offsets[lo] <= r < offsets[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= r) lo = mid;
+    else hi = mid;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(256)
+column_amax_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int rows, int width,
+                   const int* __restrict__ offsets, int groups, int segments, unsigned int* __restrict__ amax_bits) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.y * 256 + lane * 8;
+  const int r0 = blockIdx.x * kColRows + warp * 32;
+  if (c >= width || r0 >= rows) return;
+  const int ranges = groups * segments;
+  const int r_begin = max(r0, offsets[0]);                       // rows outside the table belong to no group
+  const int r_end = min(min(r0 + 32, rows), offsets[ranges]);
+  if (r_begin >= r_end) return;
+  int range = range_of_row(offsets, ranges, r_begin);
+  int range_end = offsets[range + 1];
+  float m[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  auto flush = [&](int g) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (m[i] > 0.f) atomicMax(amax_bits + (long long)g * width + c + i, __float_as_uint(m[i]));
+      m[i] = 0.f;
+    }
+  };
+  for (int r = r_begin; r < r_end; ++r) {
+    if (r >= range_end) {  // the row belongs to a later range: hand in what this one gathered
+      flush(range % groups);
+      range = range_of_row(offsets, ranges, r);
+      range_end = offsets[range + 1];
+    }
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + (long long)r * ldx + c), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m[i] = fmaxf(m[i], fabsf(v[i]));  // a NaN never wins: the scale stays finite
+  }
+  flush(range % groups);
+}
+
+__global__ void __launch_bounds__(256)
+column_scale_kernel(float* __restrict__ scales, long long n) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i < n) scales[i] = fmaxf(scales[i] * kInv448, 1e-12f);  // the maxima arrive as fp32 bit patterns
+}
+
+__global__ void __launch_bounds__(256)
+column_cast_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int rows, int width,
+                   const int* __restrict__ offsets, int groups, int segments, const float* __restrict__ scales,
+                   uint8_t* __restrict__ q, long long ldq) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.y * 256 + lane * 8;
+  const int r0 = blockIdx.x * kColRows + warp * 32;
+  if (c >= width || r0 >= rows) return;
+  const int ranges = groups * segments;
+  const int r_begin = max(r0, offsets[0]);
+  const int r_end = min(min(r0 + 32, rows), offsets[ranges]);
+  int range = -1, range_end = -1;
+  float sc[8], inv[8];
+  for (int r = r_begin; r < r_end; ++r) {
+    if (r >= range_end) {
+      range = range_of_row(offsets, ranges, r);
+      range_end = offsets[range + 1];
+      const float* sg = scales + (long long)(range % groups) * width + c;
+      const float4 a = *reinterpret_cast<const float4*>(sg), b = *reinterpret_cast<const float4*>(sg + 4);
+      sc[0] = a.x; sc[1] = a.y; sc[2] = a.z; sc[3] = a.w;
+      sc[4] = b.x; sc[5] = b.y; sc[6] = b.z; sc[7] = b.w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) inv[i] = __frcp_rn(sc[i]);
+    }
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + (long long)r * ldx + c), v);
+    // the same exact-division shortcut as quantize8, with one scale per value
+    uint32_t w[2] = {0, 0};
+    bool exact = true;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const float q0 = v[i] * inv[i], q1 = v[i + 1] * inv[i + 1];
+      const float e0 = q0 * 4.76837158203125e-7f, e1 = q1 * 4.76837158203125e-7f;  // 2^-21
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q0 + e0, q1 + e1), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0 - e0, q1 - e1), __NV_SATFINITE, __NV_E4M3);
+      exact = exact && (hi == lo);
+      w[i >> 2] |= (hi & 0xffffu) << (8 * (i & 3));
+    }
+    if (!exact) {
+      w[0] = w[1] = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float qv = __fdiv_rn(v[i], sc[i]);
+        qv = fminf(fmaxf(qv, -448.0f), 448.0f);
+        w[i >> 2] |= (uint32_t)to_e4m3(qv) << (8 * (i & 3));
+      }
+    }
+    *reinterpret_cast<uint2*>(q + (long long)r * ldq + c) = make_uint2(w[0], w[1]);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -420,6 +537,34 @@ extern "C" int b200moe_dswiglu_routed(const void* h13, long long ldh, const void
       reinterpret_cast<__nv_bfloat16*>(act_scaled), lda, limit, limited, status);
   return launch_status();
 }
+
+// E4M3 rows of x [rows, width] with one scale per (group, column): scales [groups, width].
+// Rows outside every range (none, when offsets[0] == 0 and the last entry == rows) are not written.
+extern "C" int b200moe_quantize_columns(const void* x, long long ldx, long long rows, int width,
+                                        const int32_t* offsets, int groups, int segments, void* q, long long ldq,
+                                        float* scales, void* stream) {
+  if (!x || !offsets || !q || !scales || rows < 0 || width <= 0 || groups <= 0 || segments <= 0)
+    return B200MOE_ERR_ARG;
+  if (rows > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
+  if ((width % 8) || (ldx % 8) || (ldq % 8) || ((uintptr_t)x & 15) || ((uintptr_t)q & 7) || ((uintptr_t)scales & 15))
+    return B200MOE_ERR_ALIGN;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long n = (long long)groups * width;
+  if (cudaMemsetAsync(scales, 0, (size_t)n * sizeof(float), s) != cudaSuccess) return B200MOE_ERR_LAUNCH;
+  if (rows > 0) {
+    dim3 grid((unsigned)((rows + kColRows - 1) / kColRows), (unsigned)((width + 255) / 256));
+    column_amax_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx, (int)rows, width,
+                                            offsets, groups, segments, reinterpret_cast<unsigned int*>(scales));
+  }
+  column_scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(scales, n);
+  if (rows > 0) {
+    dim3 grid((unsigned)((rows + kColRows - 1) / kColRows), (unsigned)((width + 255) / 256));
+    column_cast_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx, (int)rows, width,
+                                            offsets, groups, segments, scales, reinterpret_cast<uint8_t*>(q), ldq);
+  }
+  return launch_status();
+}
+
 
 extern "C" int b200moe_quantize_blocks(const void* w, int src_is_fp32, int experts, int out, int in,
                                        void* q, float* scale, void* stream) {

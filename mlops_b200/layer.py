@@ -191,6 +191,16 @@ def forward_routed(
 
 
 # ----------------------------------------------------------------------------- backward
+def _weight_gradient(g_rows, x_rows, offsets, experts, dtype, operands):
+    """`out[e] = g_rows[rows_e].T @ x_rows[rows_e]` from bf16 operands, or from their column-scaled
+    E4M3 forms."""
+    if operands == "bf16":
+        return ops.grouped_wgrad(g_rows, x_rows, offsets, experts, dtype)
+    g_q, g_s = ops.quantize_columns(g_rows, offsets, experts)
+    x_q, x_s = ops.quantize_columns(x_rows, offsets, experts)
+    return ops.grouped_wgrad_fp8(g_q, g_s, x_q, x_s, offsets, experts, dtype)
+
+
 def backward_routed(
     grad_output: torch.Tensor,
     grad_aux: torch.Tensor | None,
@@ -217,12 +227,18 @@ def backward_routed(
     need_w2: bool = True,
     router_grad_dtype: torch.dtype | None = None,
     block_n: int = BLOCK_N_DEFAULT,
+    weight_grad_operands: str = "bf16",
 ) -> tuple[torch.Tensor, ...]:
     """VJPs for `h2, residual, router_weight, w13, w2` in order. A gradient nobody asked
     for (`need_* = False`) is an empty placeholder and its GEMM is not launched
     (reference: src/mlops/providers/moe_common.py:127-139, 269-378). Input gradients are
     E4M3 products against the stored weights read along their rows; weight gradients are
-    bf16-operand products with fp32 sums, written at `weight_grad_dtype` (bf16 when None)."""
+    bf16-operand products with fp32 sums, written at `weight_grad_dtype` (bf16 when None).
+    `weight_grad_operands="fp8"` selects the reference's optional FP8 weight-gradient recipe
+    instead (src/mlops/kernels/quack_moe/wgrad.py:30-69): both operands of each product are
+    quantised to E4M3 with one scale per expert and column and multiplied at the FP8 rate."""
+    if weight_grad_operands not in ("bf16", "fp8"):
+        raise ValueError("weight_grad_operands is 'bf16' or 'fp8'")
     w13_data, w13_scale = w13
     w2_data, w2_scale = w2
     experts = w13_data.shape[0]
@@ -247,13 +263,13 @@ def backward_routed(
         )
         grad_route_weights = ops.gather_scalar(dscore, slots)
         if need_w2:
-            grad_w2 = ops.grouped_wgrad(dy_rows, act_scaled, offsets, experts, wdtype)
+            grad_w2 = _weight_gradient(dy_rows, act_scaled, offsets, experts, wdtype, weight_grad_operands)
             del dy_rows, act_scaled
         else:
             grad_w2 = torch.empty(0, dtype=wdtype, device=h2.device)
         if need_w13:
             x_rows = ops.dispatch(h2_flat, order, int(top_k))
-            grad_w13 = ops.grouped_wgrad(gh_b, x_rows, offsets, experts, wdtype)
+            grad_w13 = _weight_gradient(gh_b, x_rows, offsets, experts, wdtype, weight_grad_operands)
             del x_rows, gh_b
         else:
             grad_w13 = torch.empty(0, dtype=wdtype, device=h2.device)

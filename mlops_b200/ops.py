@@ -636,6 +636,59 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16, *, accumulate
 
 
 @_on_tensor_device
+def quantize_columns(x, offsets, groups):
+    """Column-scaled E4M3 of bf16 rows `x [rows, width]`: one scale per (group, column) over the
+    group's rows, `scale = max(amax * fp32(1/448), 1e-12)`. Returns `(q [rows, width] E4M3,
+    scales [groups, width] fp32)`; `offsets` as for `grouped_wgrad` (segments * groups + 1)."""
+    device = _need_cuda(x, offsets)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise NativeError("x must be bf16 [rows, width] with unit inner stride")
+    rows, width = x.shape
+    segments = (offsets.numel() - 1) // groups
+    q = torch.empty((rows, width), dtype=FP8, device=device)
+    scales = torch.empty((groups, width), dtype=torch.float32, device=device)
+    check(
+        lib.b200moe_quantize_columns(x.data_ptr(), x.stride(0), rows, width, offsets.data_ptr(), groups, segments,
+                                     q.data_ptr(), q.stride(0), scales.data_ptr(), _stream()),
+        "quantize_columns",
+    )
+    _count(3)
+    return q, scales
+
+
+@_on_tensor_device
+def grouped_wgrad_fp8(g_q, g_scale, x_q, x_scale, offsets, groups, out_dtype=torch.bfloat16, *,
+                      accumulate_into=None, scale=1.0):
+    """`[G, M, N]` with `out[e] = (g_scale[e][:, None] * x_scale[e][None, :]) * (g_q[rows_e].T @ x_q[rows_e])`
+    from column-scaled E4M3 operands (`quantize_columns`), fp32 sums over all of an expert's rows."""
+    device = _need_cuda(g_q, g_scale, x_q, x_scale, offsets, accumulate_into)
+    rows, m = g_q.shape
+    n = x_q.shape[1]
+    segments = (offsets.numel() - 1) // groups
+    if accumulate_into is not None:
+        out = accumulate_into
+        if tuple(out.shape) != (groups, m, n) or not out.is_contiguous() or \
+                out.dtype not in (torch.bfloat16, torch.float32):
+            raise NativeError(f"accumulate_into must be a contiguous bf16 or fp32 [{groups}, {m}, {n}] tensor")
+    else:
+        if out_dtype not in (torch.bfloat16, torch.float32):
+            raise NativeError("weight gradients are written as bf16 or fp32")
+        out = torch.empty((groups, m, n), dtype=out_dtype, device=device)
+    with _Timed("wgrad_fp8", 2.0 * rows * m * n):
+        check(
+            lib.b200moe_grouped_wgrad_fp8(
+                g_q.data_ptr(), g_q.stride(0), g_scale.data_ptr(), x_q.data_ptr(), x_q.stride(0), x_scale.data_ptr(),
+                offsets.data_ptr(), groups, segments, rows, m, n, out.data_ptr(),
+                1 if out.dtype == torch.float32 else 0, float(scale), 1 if accumulate_into is not None else 0,
+                status_block(device).data_ptr(), _stream(),
+            ),
+            "grouped_wgrad_fp8",
+        )
+    _count()
+    return out
+
+
+@_on_tensor_device
 def lora_project(x, factor, offsets, *, rank_major):
     """`t [rows, r] = x[row] . factor[expert(row)]`; factor `[E, r, K]` (`rank_major`) or `[E, K, r]`."""
     device = _need_cuda(x, factor, offsets)

@@ -22,6 +22,8 @@ the reference asserts that `torch.ops.mlops` holds exactly its own manifest
 
 from __future__ import annotations
 
+import os
+
 import torch
 from torch.utils.flop_counter import register_flop_formula
 
@@ -35,6 +37,22 @@ MAX_EXPERTS = 1024
 MAX_TOP_K = 32
 ROUTING_MODES = ("softmax_then_topk", "topk_then_softmax", "sigmoid_noaux_tc")
 ROUTE_WEIGHT_PRECISIONS = ("float32", "input")
+
+
+# The optional FP8 weight-gradient recipe (both operands of dW13 and dW2 quantised to E4M3 with
+# one scale per expert and column; the reference's `fp8_current` weight gradient,
+# src/mlops/kernels/quack_moe/wgrad.py:30-69). A process-wide recipe choice like the reference's
+# container type, read when a backward runs; bf16 operands are the default.
+WEIGHT_GRADIENT_OPERANDS = os.environ.get("B200MOE_WGRAD_OPERANDS", "bf16")
+
+
+def set_weight_gradient_operands(kind: str) -> str:
+    """`"bf16"` (default) or `"fp8"`; returns the previous setting."""
+    global WEIGHT_GRADIENT_OPERANDS
+    if kind not in ("bf16", "fp8"):
+        raise ValueError("weight-gradient operands are 'bf16' or 'fp8'")
+    previous, WEIGHT_GRADIENT_OPERANDS = WEIGHT_GRADIENT_OPERANDS, kind
+    return previous
 
 
 # ----------------------------------------------------------------- the reference's contexts
@@ -182,7 +200,8 @@ def moe_bwd(grad_output: torch.Tensor, grad_aux: torch.Tensor, grad_probability_
             grad_output, grad_aux, grad_probability_sum, h2, router_weight, w13, w2, logits, route_weights,
             route_ids, order, offsets, slots, h13, top_k=top_k, routing_mode=routing_mode, lengths=lengths,
             weight_grad_dtype=wdtype, router_grad_dtype=weight_grad_dtype, swiglu_limit=swiglu_limit,
-            need_router=need_router, need_w13=need_w13, need_w2=need_w2)
+            need_router=need_router, need_w13=need_w13, need_w2=need_w2,
+            weight_grad_operands=WEIGHT_GRADIENT_OPERANDS)
 
 
 @moe_bwd.register_fake
@@ -473,6 +492,7 @@ def backward(grad_output, grad_aux, grad_probability_sum, h2, router_weight, w13
     wdtype = kwargs.pop("weight_grad_dtype", None)
     if wdtype is None:
         wdtype = _context_weight_gradient_dtype() or w13_experts.dtype
+    kwargs.setdefault("weight_grad_operands", WEIGHT_GRADIENT_OPERANDS)
     return layer.backward_routed(
         grad_output, grad_aux, grad_probability_sum, h2, router_weight, split(w13_experts),
         split(w2_experts), logits, route_weights, route_ids, order, offsets, slots, h13, top_k=int(top_k),

@@ -270,6 +270,48 @@ def grouped_wgrad(g, x, offsets, groups, dtype=torch.float64):
 
 
 # ------------------------------------------------------------------ SwiGLU and combine
+def quantize_columns(value, offsets, groups):
+    """(data E4M3 [rows, N] token-major, scales fp32 [groups, N]): one scale per column over the
+    rows of each group, `scale = max(amax * (1/448), 1e-12)`, `q = clamp(x / scale)` -- the row
+    quantiser's equations applied to the columns of an expert's token block, as the reference's
+    FP8 weight gradient quantises both of its operands
+    (src/mlops/kernels/quack_moe/quantize_transpose.py:126-133; the reference's implementation is a
+    CUDA-only Triton kernel, so this restatement follows its stated equations: parity unpinned).
+    `offsets` holds segments * groups + 1 boundaries; range i belongs to group i % groups."""
+    rows = value.float()
+    n = rows.shape[1]
+    bounds = [int(v) for v in offsets.tolist()]
+    ranges = len(bounds) - 1
+    amax = rows.new_zeros(groups, n)
+    for i in range(ranges):
+        lo, hi = bounds[i], bounds[i + 1]
+        if hi > lo:
+            block = rows[lo:hi].abs()
+            block = torch.where(torch.isnan(block), torch.zeros_like(block), block)  # a NaN never sets a scale
+            amax[i % groups] = torch.maximum(amax[i % groups], block.amax(dim=0))
+    scales = torch.clamp_min(amax * (1.0 / 448.0), 1e-12)
+    data = torch.zeros(rows.shape, dtype=FP8)
+    for i in range(ranges):
+        lo, hi = bounds[i], bounds[i + 1]
+        if hi > lo:
+            data[lo:hi] = torch.clamp(rows[lo:hi] / scales[i % groups][None, :], -448.0, 448.0).to(FP8)
+    return data, scales
+
+
+def grouped_wgrad_fp8(g_q, g_scale, x_q, x_scale, offsets, groups, dtype=torch.float64):
+    """`out[e] = (g_scale[e][:, None] * x_scale[e][None, :]) * (g_q[rows_e].T @ x_q[rows_e])`: the
+    reference's FP8 weight gradient on given operands (src/mlops/kernels/quack_moe/wgrad.py:30-69:
+    one product over all of the expert's tokens, `acc * xs * ws` at the end)."""
+    bounds = [int(v) for v in offsets.tolist()]
+    ranges = len(bounds) - 1
+    out = torch.zeros(groups, g_q.shape[1], x_q.shape[1], dtype=dtype)
+    for i in range(ranges):
+        lo, hi = bounds[i], bounds[i + 1]
+        if hi > lo:
+            out[i % groups] += g_q[lo:hi].to(dtype).t() @ x_q[lo:hi].to(dtype)
+    return out * g_scale.to(dtype)[:, :, None] * x_scale.to(dtype)[:, None, :]
+
+
 def swiglu(h13, limit=None):
     """fp32 `silu(gate) * up` of h13 = [gate | up], GLM clamp when `limit` is given.
     Follows src/mlops/kernels/quack_moe/swiglu_rows.py:49-80 (fp32, rounded by the

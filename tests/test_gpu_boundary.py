@@ -332,3 +332,32 @@ def test_reference_dispatch_can_select_the_composition():
     assert torch.equal(out, default_out)
     grads = torch.autograd.grad(out, [x, w13, w2], c1["dy"].to(DEV))
     assert grads[1].shape == w13.shape and grads[2].shape == w2.shape
+
+
+def test_fp8_weight_gradient_recipe_through_the_operator():
+    """`provider.set_weight_gradient_operands("fp8")`: the backward operator quantises both
+    operands of each expert weight gradient (one scale per expert and column) and multiplies at
+    the FP8 rate; activations' and the router's gradients are untouched, the expert gradients
+    stay within the reference's bound for that recipe (tests/test_sonicmoe_fp8.py:114-124)."""
+    from mlops_b200 import ops, provider
+
+    c1, x, router, w13, w2 = _containers()
+    dy, residual = c1["dy"].to(DEV), torch.zeros_like(c1["x"]).to(DEV)
+    kwargs = dict(top_k=2, routing_mode="softmax_then_topk")
+    grads = {}
+    previous = provider.set_weight_gradient_operands("bf16")
+    try:
+        for kind in ("bf16", "fp8"):
+            provider.set_weight_gradient_operands(kind)
+            out = provider.apply(x, residual, router, w13, w2, **kwargs)
+            grads[kind] = torch.autograd.grad(out[0], [x, router, w13, w2], dy)
+    finally:
+        provider.set_weight_gradient_operands(previous)
+    ops.check_status(DEV)
+    assert torch.equal(grads["fp8"][0], grads["bf16"][0]) and torch.equal(grads["fp8"][1], grads["bf16"][1])
+    for i in (2, 3):
+        exact, fp8 = grads["bf16"][i].double(), grads["fp8"][i].double()
+        assert not torch.equal(exact, fp8)
+        assert ((fp8 - exact).norm() / exact.norm()).item() < 6e-2
+    with pytest.raises(ValueError):
+        provider.set_weight_gradient_operands("fp4")

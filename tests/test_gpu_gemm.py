@@ -232,6 +232,84 @@ def test_wgrad_groups_are_isolated_from_a_neighbours_inf_and_nan(m, n):
     assert torch.equal(dirty[2][:, keep.to(DEV)], clean[2][:, keep.to(DEV)])
 
 
+@pytest.mark.parametrize("counts,width", [([64], 128), ([0, 70, 131, 15, 260], 384), ([300, 1, 0, 555], 1024)])
+def test_quantize_columns_is_bit_exact(counts, width):
+    """Column-scaled E4M3 (one scale per expert and column over the expert's rows): bytes and
+    scales bit-for-bit against the CPU restatement, including an empty group (scale 1e-12), a
+    one-row group, groups that end inside a 32-row warp piece, and a scale spread of 2^+-14."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(width + len(counts))
+    rows, groups = sum(counts), len(counts)
+    x = torch.randn(rows, width, generator=g)
+    x *= torch.exp2(torch.randint(-14, 15, (1, width), generator=g).float())     # per-column spread
+    x[:, 5] = 0.0                                                               # an all-zero column
+    x = x.bfloat16()
+    offs = _offsets(counts)
+    q, scales = ops.quantize_columns(x.to(DEV), offs.to(DEV), groups)
+    ops.check_status(DEV)
+    q_ref, s_ref = O.quantize_columns(x, offs, groups)
+    assert torch.equal(scales.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize(
+    "counts,m,n",
+    [([128], 128, 256), ([64], 128, 256), ([0, 70, 131, 15, 260], 256, 512),
+     ([0, 70, 131, 15, 260], 384, 320), ([1000, 3, 0, 500], 1024, 768)],
+)
+def test_wgrad_fp8(counts, m, n, out_dtype):
+    """The FP8 weight gradient on given column-scaled operands against float64 of the same
+    dequantised operands; then the whole recipe against the bf16 product at the reference's own
+    bound for FP8 weight gradients (6e-2 relative Frobenius, tests/test_sonicmoe_fp8.py:114-124)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + n + 1)
+    rows, groups = sum(counts), len(counts)
+    grad = torch.randn(rows, m, generator=g).bfloat16()
+    x = torch.randn(rows, n, generator=g).bfloat16()
+    offs = _offsets(counts)
+    g_q, g_s = ops.quantize_columns(grad.to(DEV), offs.to(DEV), groups)
+    x_q, x_s = ops.quantize_columns(x.to(DEV), offs.to(DEV), groups)
+    out = ops.grouped_wgrad_fp8(g_q, g_s, x_q, x_s, offs.to(DEV), groups, out_dtype)
+    ops.check_status(DEV)
+    ref = O.grouped_wgrad_fp8(g_q.cpu(), g_s.cpu(), x_q.cpu(), x_s.cpu(), offs, groups)
+    exact = O.grouped_wgrad(grad, x, offs, groups)
+    for e, count in enumerate(counts):
+        if count == 0:
+            assert int(torch.count_nonzero(out[e])) == 0
+            continue
+        mx, mean = O.rel_errors(out[e].float().cpu(), ref[e])
+        assert mx <= (1e-5 if out_dtype == torch.float32 else MAX_REL), mx
+        assert mean <= (1e-6 if out_dtype == torch.float32 else MEAN_REL), mean
+        frob = ((out[e].double().cpu() - exact[e]).norm() / exact[e].norm()).item()
+        assert frob <= 6e-2, frob
+    # accumulate into a caller's buffer, scaled
+    base = torch.randn(groups, m, n, generator=g).to(out_dtype)
+    acc = ops.grouped_wgrad_fp8(g_q, g_s, x_q, x_s, offs.to(DEV), groups, accumulate_into=base.to(DEV).clone(), scale=0.5)
+    expect = base.double() + 0.5 * ref
+    mx, mean = O.rel_errors(acc.float().cpu(), expect)
+    assert mx <= (1e-5 if out_dtype == torch.float32 else MAX_REL), mx
+
+
+def test_wgrad_fp8_groups_are_isolated_from_a_neighbours_nan():
+    ops = _ops()
+    g = torch.Generator().manual_seed(78)
+    counts, m, n = [70, 131, 40], 128, 256
+    rows = sum(counts)
+    grad = torch.randn(rows, m, generator=g).bfloat16()
+    x = torch.randn(rows, n, generator=g).bfloat16()
+    offs = _offsets(counts).to(DEV)
+    g_q, g_s = ops.quantize_columns(grad.to(DEV), offs, 3)
+    x_q, x_s = ops.quantize_columns(x.to(DEV), offs, 3)
+    clean = ops.grouped_wgrad_fp8(g_q, g_s, x_q, x_s, offs, 3, torch.float32)
+    x_bad = x_q.clone()
+    x_bad.view(torch.uint8)[70] = 0x7F   # E4M3 NaN in the first row of group 1
+    dirty = ops.grouped_wgrad_fp8(g_q, g_s, x_bad, x_s, offs, 3, torch.float32)
+    ops.check_status(DEV)
+    assert torch.equal(dirty[0], clean[0]) and torch.equal(dirty[2], clean[2])
+    assert bool(torch.isnan(dirty[1]).any())
+
+
 def test_segmented_layout_matches_expert_sorted_layout():
     """Rows laid out [source][expert] (what an expert-parallel exchange delivers): the GEMM
     with `weights < groups` and the weight gradient with `segments > 1` must equal the plain

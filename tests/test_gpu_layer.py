@@ -82,6 +82,35 @@ def _run_case(x, residual, router, w13, w2, dy, *, top_k, mode, bias=None, n_gro
     return result, grads
 
 
+def test_fp8_weight_gradients_stay_within_the_reference_bound_of_that_recipe():
+    """`weight_grad_operands="fp8"`: the other gradients do not change at all, and the expert
+    weight gradients stay within the relative-Frobenius bound the reference sets for its FP8
+    weight-gradient recipe (6e-2, tests/test_sonicmoe_fp8.py:114-124) of the bf16-operand ones."""
+    layer, ops = _layer()
+    c1 = inputs.config1()
+    w13_q, w13_s = O.quantize_blocks(c1["w13"])
+    w2_q, w2_s = O.quantize_blocks(c1["w2"])
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    w13, w2 = (dev(w13_q), dev(w13_s)), (dev(w2_q), dev(w2_s))
+    result = layer.forward_routed(dev(c1["x"]), dev(c1["residual"]), dev(c1["router"]), w13, w2,
+                                  top_k=c1["top_k"], routing_mode=c1["routing_mode"])
+    saved = result[4:]
+    grads = {}
+    for operands in ("bf16", "fp8"):
+        grads[operands] = layer.backward_routed(
+            dev(c1["dy"]), None, None, dev(c1["x"]), dev(c1["router"]), w13, w2, *saved, top_k=c1["top_k"],
+            routing_mode=c1["routing_mode"], weight_grad_dtype=torch.float32, weight_grad_operands=operands)
+    ops.check_status(DEV)
+    for i in (0, 1, 2):
+        assert torch.equal(grads["fp8"][i], grads["bf16"][i])
+    for i in (3, 4):
+        exact, fp8 = grads["bf16"][i].double(), grads["fp8"][i].double()
+        assert ((fp8 - exact).norm() / exact.norm()).item() < 6e-2
+    with pytest.raises(ValueError):
+        layer.backward_routed(dev(c1["dy"]), None, None, dev(c1["x"]), dev(c1["router"]), w13, w2, *saved,
+                              top_k=c1["top_k"], routing_mode=c1["routing_mode"], weight_grad_operands="fp4")
+
+
 def test_config1_against_oracle_and_reference_fixture(golden):
     c1 = inputs.config1()
     result, grads = _run_case(c1["x"], c1["residual"], c1["router"], c1["w13"], c1["w2"], c1["dy"],

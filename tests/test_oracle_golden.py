@@ -212,3 +212,28 @@ def test_expert_major_layer_equals_the_forward_backward_pair():
         assert torch.equal(both["grad_w13"][e], bwd["grad_w13"][e]) and torch.equal(both["grad_w2"][e], bwd["grad_w2"][e])
     plain, share = O.plain_max_rel(fwd["output"].float() * (1 + 1e-3), fwd["output"].float())
     assert abs(plain - 1e-3) < 1e-4 and share > 0.9
+
+
+def test_column_quantiser_is_the_pinned_row_quantiser_on_the_transpose():
+    """The reference defines its per-feature quantiser as "per-row quantization of `value.T`
+    exactly" (src/mlops/kernels/quack_moe/quantize_transpose.py:1-6); the row quantiser is pinned
+    against the reference's own function above, so the column form is pinned through it."""
+    g = torch.Generator().manual_seed(41)
+    x = (torch.randn(300, 96, generator=g) * torch.exp2(torch.randint(-6, 7, (1, 96), generator=g).float())).bfloat16()
+    offsets = torch.tensor([0, 120, 120, 300], dtype=torch.int32)
+    data, scales = O.quantize_columns(x, offsets, 3)
+    for e, (lo, hi) in enumerate(((0, 120), (120, 120), (120, 300))):
+        if hi == lo:
+            assert torch.equal(scales[e], torch.full((96,), 1e-12))
+            continue
+        rows_q, rows_s = O.quantize_rows(x[lo:hi].t().contiguous(), mode="row")
+        assert torch.equal(scales[e], rows_s[:, 0])
+        assert torch.equal(data[lo:hi].view(torch.uint8), rows_q.t().contiguous().view(torch.uint8))
+    # the product on given operands is the plain one times the two scale vectors
+    y = torch.randn(300, 32, generator=g).bfloat16()
+    y_q, y_s = O.quantize_columns(y, offsets, 3)
+    out = O.grouped_wgrad_fp8(data, scales, y_q, y_s, offsets, 3)
+    exact = O.grouped_wgrad(x, y, offsets, 3)
+    assert int(torch.count_nonzero(out[1])) == 0
+    for e in (0, 2):
+        assert ((out[e] - exact[e]).norm() / exact[e].norm()).item() < 6e-2
