@@ -348,6 +348,19 @@ int b200moe_grouped_wgrad_bf16_accumulate(const void* g, long long ldg, const vo
                                           float scale, int32_t* status, void* stream);
 
 /*
+ * bf16 grouped GEMM of the bf16 compute path (fp32 sums in TMEM over the whole K loop):
+ *   d[rows of g, 0:N] = a[rows of g, 0:K] @ op(b[g % weights])  (+ addend), rounded once to bf16
+ * b_mn_major = 0: b is [weights, N, K] (y = x W^T on the stored nn.Linear weight);
+ * b_mn_major = 1: b is [weights, K, N] read along its rows (dx = dy W on the SAME stored weight
+ * [out = K, in = N]; no transposed copy).  N, K and the pitches are multiples of 8.
+ * Reference: src/mlops/kernels/moe_grouped_gemm.py:201-299 (`grouped_mm_forward`,
+ * `grouped_mm_dgrad`; CPU form `_native_torch` :185-198).
+ */
+int b200moe_grouped_gemm_bf16(const void* a, long long lda, const void* b, void* d, long long ldd,
+                              const void* addend, long long ldc, const int32_t* offsets, int groups, int weights,
+                              long long rows_total, int N, int K, int b_mn_major, int32_t* status, void* stream);
+
+/*
  * E4M3 rows of x [rows, width] (bf16, token-major) with ONE SCALE PER (GROUP, COLUMN):
  *   scales[g, c] = max(max over the rows of group g of |x[r, c]| * fp32(1/448), 1e-12)
  *   q[r, c]      = e4m3_rn(clamp(x[r, c] / scales[g(r), c], -448, 448))     (RN division)

@@ -137,7 +137,9 @@ def forward_routed(
     order, offsets, slots, h13)`.
 
     `w13 = (data E4M3 [E, 2F, D], scale fp32 [E, 2F/128, D/128])` with gate rows then up
-    rows, `w2 = (data [E, D, F], scale)`: the components of a block-FP8 weight container.
+    rows, `w2 = (data [E, D, F], scale)`: the components of a block-FP8 weight container. Plain
+    bf16 tensors `w13 [E, 2F, D]`, `w2 [E, D, F]` select the bf16 compute path instead (bf16
+    grouped GEMMs with fp32 sums, no quantisation anywhere).
     `route = (route_weights, route_ids)` bypasses the selection (the logits and the
     statistics are still computed). `fuse_swiglu` runs SwiGLU and the activation quantiser in
     the up GEMM's epilogue (bit-identical results; measured 7% slower than the two-kernel form
@@ -146,8 +148,14 @@ def forward_routed(
     atomics instead of writing expert-order rows for `combine`: not bitwise repeatable, and
     slower for top-8 routing (a token row is read-modify-written eight times in HBM), so it is
     off by default as well."""
-    w13_data, w13_scale = w13
-    w2_data, w2_scale = w2
+    bf16_weights = isinstance(w13, torch.Tensor)
+    if bf16_weights:
+        _check_bf16_weights(w13, w2)
+        w13_data, w2_data = w13, w2
+        w13_scale = w2_scale = None
+    else:
+        w13_data, w13_scale = w13
+        w2_data, w2_scale = w2
     experts = w13_data.shape[0]
     with torch.no_grad():
         original_shape = h2.shape
@@ -170,6 +178,20 @@ def forward_routed(
             # the sort reported ids outside [0, experts) and placed them on the nearest expert;
             # the residual handed to the statistics and to the backward pass says the same
             route_ids = route_ids.clamp(0, experts - 1)
+        if bf16_weights:
+            # the bf16 compute path (reference: src/mlops/kernels/moe_grouped_gemm.py:201-299 around
+            # the builtin's dispatch / SwiGLU / combine): nothing is quantised
+            x_rows = ops.dispatch(h2_flat, order, int(top_k))
+            h13 = ops.grouped_gemm_bf16(x_rows, w13_data, offsets)
+            del x_rows
+            _q, _s, act = ops.swiglu_quantize(h13, limit=swiglu_limit, quantized=False, rounded=True)
+            expert_output = ops.grouped_gemm_bf16(act, w2_data, offsets)
+            output = ops.combine(expert_output, slots, route_weights, residual_flat).reshape(original_shape)
+            aux, counts, probability_sum = routing_statistics(
+                logits, route_ids, counts, routing_mode=str(routing_mode), lengths=normalized, experts=experts
+            )
+            return (output, aux, counts, probability_sum, logits, route_weights, route_ids, order, offsets, slots,
+                    h13)
         # every token quantised once, its E4M3 row written to each of its K expert-ordered rows
         x_q, x_s = ops.quantize_rows_scatter(h2_flat, slots)
         if fuse_swiglu and w2_data.shape[2] % 128 == 0:
@@ -188,6 +210,16 @@ def forward_routed(
             logits, route_ids, counts, routing_mode=str(routing_mode), lengths=normalized, experts=experts
         )
     return (output, aux, counts, probability_sum, logits, route_weights, route_ids, order, offsets, slots, h13)
+
+
+def _check_bf16_weights(w13, w2):
+    if not isinstance(w2, torch.Tensor) or w13.dtype != torch.bfloat16 or w2.dtype != torch.bfloat16:
+        raise ValueError("the bf16 compute path takes both expert weights as plain bf16 tensors")
+    if w13.dim() != 3 or w2.dim() != 3 or w13.shape[0] != w2.shape[0] or w13.shape[1] != 2 * w2.shape[2] \
+            or w13.shape[2] != w2.shape[1]:
+        raise ValueError("expected w13 [E, 2F, D] and w2 [E, D, F]")
+    if w13.shape[2] % 8 or w2.shape[2] % 8:
+        raise ValueError("the bf16 grouped GEMM needs D and F to be multiples of 8")
 
 
 # ----------------------------------------------------------------------------- backward
@@ -239,8 +271,14 @@ def backward_routed(
     quantised to E4M3 with one scale per expert and column and multiplied at the FP8 rate."""
     if weight_grad_operands not in ("bf16", "fp8"):
         raise ValueError("weight_grad_operands is 'bf16' or 'fp8'")
-    w13_data, w13_scale = w13
-    w2_data, w2_scale = w2
+    bf16_weights = isinstance(w13, torch.Tensor)
+    if bf16_weights:
+        _check_bf16_weights(w13, w2)
+        w13_data, w2_data = w13.contiguous(), w2.contiguous()
+        w13_scale = w2_scale = None
+    else:
+        w13_data, w13_scale = w13
+        w2_data, w2_scale = w2
     experts = w13_data.shape[0]
     wdtype = torch.bfloat16 if weight_grad_dtype is None else weight_grad_dtype
     with torch.no_grad():
@@ -250,6 +288,34 @@ def backward_routed(
         normalized = _normalized_lengths(lengths, h2_flat.shape[0])
         counts = (offsets[1:] - offsets[:-1]).long()
 
+        if bf16_weights:
+            dy_rows = ops.dispatch(grad_flat, order, int(top_k))
+            r = ops.grouped_gemm_bf16(dy_rows, w2_data, offsets, b_mn_major=True)
+            dscore, _gq, _gs, gh_b, act_scaled = ops.dswiglu_routed(
+                h13, r, route_weights, order, limit=swiglu_limit, quantized=False, rounded=True,
+                scaled_activation=need_w2,
+            )
+            del r
+            grad_route_weights = ops.gather_scalar(dscore, slots)
+            if need_w2:
+                grad_w2 = _weight_gradient(dy_rows, act_scaled, offsets, experts, wdtype, weight_grad_operands)
+                del act_scaled
+            else:
+                grad_w2 = torch.empty(0, dtype=wdtype, device=h2.device)
+            del dy_rows
+            if need_w13:
+                x_rows = ops.dispatch(h2_flat, order, int(top_k))
+                grad_w13 = _weight_gradient(gh_b, x_rows, offsets, experts, wdtype, weight_grad_operands)
+                del x_rows
+            else:
+                grad_w13 = torch.empty(0, dtype=wdtype, device=h2.device)
+            grad_rows = ops.grouped_gemm_bf16(gh_b, w13_data, offsets, b_mn_major=True)
+            del gh_b
+            grad_h2 = ops.dispatch_backward(grad_rows, slots)
+            return _finish_backward(grad_h2, grad_output, grad_aux, grad_probability_sum, grad_route_weights,
+                                    route_weights, route_ids, logits, counts, routing_mode, normalized,
+                                    router_weight, h2_flat, need_router, router_grad_dtype, original_shape,
+                                    grad_w13, grad_w2)
         # one pass over dy: E4M3 rows for the input gradient and, when the down weight's gradient
         # is wanted, the same rows in bf16 as its operand
         if need_w2:
@@ -276,7 +342,17 @@ def backward_routed(
         grad_rows = ops.grouped_gemm_fp8(gh_q, gh_s, w13_data, w13_scale, offsets, b_mn_major=True,
                                          block_n=block_n)
         grad_h2 = ops.dispatch_backward(grad_rows, slots)
+        return _finish_backward(grad_h2, grad_output, grad_aux, grad_probability_sum, grad_route_weights,
+                                route_weights, route_ids, logits, counts, routing_mode, normalized, router_weight,
+                                h2_flat, need_router, router_grad_dtype, original_shape, grad_w13, grad_w2)
 
+
+def _finish_backward(grad_h2, grad_output, grad_aux, grad_probability_sum, grad_route_weights, route_weights,
+                     route_ids, logits, counts, routing_mode, normalized, router_weight, h2_flat, need_router,
+                     router_grad_dtype, original_shape, grad_w13, grad_w2):
+    """The router's share of the backward pass: the routing VJP, the router weight's gradient and
+    the router's contribution to the input gradient."""
+    with torch.no_grad():
         grad_logits = routing_gradient(
             grad_aux, grad_probability_sum, grad_route_weights, route_weights, route_ids, logits, counts,
             routing_mode=str(routing_mode), lengths=normalized,
@@ -286,7 +362,7 @@ def backward_routed(
             rdtype = router_weight.dtype if router_grad_dtype is None else router_grad_dtype
             grad_router = _router_weight_gradient(grad_logits, h2_flat, rdtype)
         else:
-            grad_router = torch.empty(0, dtype=router_weight.dtype, device=h2.device)
+            grad_router = torch.empty(0, dtype=router_weight.dtype, device=h2_flat.device)
         grad_h2.addmm_(grad_logits.to(h2_flat.dtype), router_operand.to(h2_flat.dtype))
     return (grad_h2.reshape(original_shape), grad_output.clone(), grad_router, grad_w13, grad_w2)
 

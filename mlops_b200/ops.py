@@ -636,6 +636,35 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16, *, accumulate
 
 
 @_on_tensor_device
+def grouped_gemm_bf16(a, b, offsets, *, b_mn_major=False, addend=None):
+    """`out[rows_e] = a[rows_e] @ op(b[e])` in bf16 with fp32 sums. `b` is `[E, N, K]` (K-major: the
+    stored `nn.Linear` weight, `y = x W^T`) or, with `b_mn_major`, `[E, K, N]` read along its rows
+    (`dx = dy W` on the same stored weight). More groups than weights: group g uses `b[g % E]`."""
+    device = _need_cuda(a, b, offsets, addend)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.stride(1) != 1 or not b.is_contiguous():
+        raise NativeError("a must be bf16 rows with unit inner stride and b a contiguous bf16 [experts, ., .] tensor")
+    rows, k = a.shape
+    weights = b.shape[0]
+    n = b.shape[2] if b_mn_major else b.shape[1]
+    if (b.shape[1] if b_mn_major else b.shape[2]) != k:
+        raise NativeError("inner dimensions of a and b differ")
+    groups = offsets.numel() - 1
+    out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
+    if rows:
+        with _Timed("gemm_bf16", 2.0 * rows * n * k):
+            check(
+                lib.b200moe_grouped_gemm_bf16(
+                    a.data_ptr(), a.stride(0), b.data_ptr(), out.data_ptr(), out.stride(0), _ptr(addend),
+                    0 if addend is None else addend.stride(0), offsets.data_ptr(), groups, weights, rows, n, k,
+                    1 if b_mn_major else 0, status_block(device).data_ptr(), _stream(),
+                ),
+                "grouped_gemm_bf16",
+            )
+        _count()
+    return out
+
+
+@_on_tensor_device
 def quantize_columns(x, offsets, groups):
     """Column-scaled E4M3 of bf16 rows `x [rows, width]`: one scale per (group, column) over the
     group's rows, `scale = max(amax * fp32(1/448), 1e-12)`. Returns `(q [rows, width] E4M3,

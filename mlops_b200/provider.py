@@ -91,10 +91,15 @@ def refusal(h2, residual, router_weight, w13_experts, w2_experts, *, surface="se
         return "b200.moe needs every argument on one device"
     if torch.cuda.get_device_capability(h2.device) != (10, 0):
         return "b200.moe is built for compute capability 10.0 (sm_100a) only"
-    if compute_precision not in (None, "fp8_block"):
-        return f"b200.moe computes in block FP8; compute_precision={compute_precision!r} is not served"
-    if not (holds_blocks(w13_experts) and holds_blocks(w2_experts)):
-        return "expert weights must be BlockFP8Weight containers (E4M3, 128x128 block scales)"
+    if compute_precision not in (None, "fp8_block", "bf16"):
+        return f"b200.moe computes in block FP8 or bf16; compute_precision={compute_precision!r} is not served"
+    containers = holds_blocks(w13_experts) and holds_blocks(w2_experts)
+    plain = _plain_bf16(w13_experts) and _plain_bf16(w2_experts)
+    if not (containers or plain):
+        return ("expert weights must be BlockFP8Weight containers (E4M3, 128x128 block scales) or plain bf16 "
+                "tensors")
+    if plain and compute_precision == "fp8_block":
+        return "plain bf16 expert weights are multiplied in bf16; quantise them (BlockFP8Weight.quantize) for fp8_block"
     if h2.dtype != torch.bfloat16 or residual.dtype != torch.bfloat16:
         return "h2 and residual must be bf16"
     if h2.shape != residual.shape:
@@ -108,8 +113,10 @@ def refusal(h2, residual, router_weight, w13_experts, w2_experts, *, surface="se
     inner = w2_experts.shape[2]
     if tuple(w13_experts.shape[1:]) != (2 * inner, width) or w2_experts.shape[1] != width:
         return "expert weights must be w13 [experts, 2F, D] and w2 [experts, D, F]"
-    if width % 128 or inner % 128:
+    if containers and (width % 128 or inner % 128):
         return "hidden and expert widths must be multiples of 128"
+    if plain and (width % 8 or inner % 8):
+        return "hidden and expert widths must be multiples of 8"
     if experts > MAX_EXPERTS or not 0 < int(top_k) <= min(experts, MAX_TOP_K):
         return f"supported sizes: experts <= {MAX_EXPERTS}, 0 < top_k <= min(experts, {MAX_TOP_K})"
     if routing_mode not in ROUTING_MODES:
@@ -128,6 +135,32 @@ def refusal(h2, residual, router_weight, w13_experts, w2_experts, *, surface="se
     return None
 
 
+def _plain_bf16(weight) -> bool:
+    return type(weight) in (torch.Tensor, torch.nn.Parameter) and weight.dtype == torch.bfloat16 and weight.dim() == 3
+
+
+def _operands(weight):
+    """What the layer takes for one expert weight: the bf16 tensor, or (E4M3 data, block scales)."""
+    return weight if _plain_bf16(weight) else split(weight)
+
+
+class _DequantizedCopy(torch.autograd.Function):
+    """bf16 values of a block-FP8 container for the bf16 compute path; the gradient of the copy is
+    the container's gradient (the reference multiplies the dequantised weights the same way,
+    src/mlops/providers/expert_weights.py:46-52)."""
+
+    @staticmethod
+    def forward(ctx, container):
+        data, scale = split(container)
+        rows, cols = data.shape[1], data.shape[2]
+        wide = scale.repeat_interleave(128, 1)[:, :rows].repeat_interleave(128, 2)[:, :, :cols]
+        return (data.float() * wide).to(torch.bfloat16)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad
+
+
 # ------------------------------------------------------------------ the operator pair
 _ELEVEN = tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
                 torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]
@@ -135,6 +168,8 @@ _FIVE = tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tens
 
 
 def _with_scales(w13_data, w2_data, weight_components):
+    if w13_data.dtype == torch.bfloat16 and w2_data.dtype == torch.bfloat16 and len(weight_components) == 0:
+        return w13_data, w2_data  # plain bf16 weights: the bf16 compute path
     if len(weight_components) != 2:
         raise ValueError("b200moe operators take the two block-scale tensors (w13's, then w2's) as "
                          "weight_components; pass the weight containers and leave the list empty")
@@ -451,10 +486,11 @@ def apply(h2, residual, router_weight, w13_experts, w2_experts, *, top_k, routin
                      shared_w2=shared_w2, compute_precision=compute_precision)
     if reason is not None:
         raise ValueError(reason)
-    if type(w13_experts) not in _DISPATCH_REGISTERED:
-        register_container(type(w13_experts))
-    if type(w2_experts) not in _DISPATCH_REGISTERED:
-        register_container(type(w2_experts))
+    if compute_precision == "bf16" and holds_blocks(w13_experts):
+        w13_experts, w2_experts = _DequantizedCopy.apply(w13_experts), _DequantizedCopy.apply(w2_experts)
+    for weight in (w13_experts, w2_experts):
+        if not _plain_bf16(weight) and type(weight) not in _DISPATCH_REGISTERED:
+            register_container(type(weight))
     limit = None if swiglu_limit is None else float(swiglu_limit)
     base = residual
     if shared_w13 is not None:
@@ -478,7 +514,7 @@ def forward(h2, residual, router_weight, w13_experts, w2_experts, *, top_k, rout
     if weight_precision not in ROUTE_WEIGHT_PRECISIONS:
         raise ValueError(f"unsupported route-weight precision {weight_precision!r}")
     return layer.forward_routed(
-        h2, residual, router_weight, split(w13_experts), split(w2_experts), top_k=int(top_k),
+        h2, residual, router_weight, _operands(w13_experts), _operands(w2_experts), top_k=int(top_k),
         routing_mode=str(routing_mode), router_bias=router_bias, n_group=int(n_group), topk_group=int(topk_group),
         routed_scaling=float(routed_scaling), lengths=lengths, swiglu_limit=swiglu_limit,
     )
@@ -494,8 +530,8 @@ def backward(grad_output, grad_aux, grad_probability_sum, h2, router_weight, w13
         wdtype = _context_weight_gradient_dtype() or w13_experts.dtype
     kwargs.setdefault("weight_grad_operands", WEIGHT_GRADIENT_OPERANDS)
     return layer.backward_routed(
-        grad_output, grad_aux, grad_probability_sum, h2, router_weight, split(w13_experts),
-        split(w2_experts), logits, route_weights, route_ids, order, offsets, slots, h13, top_k=int(top_k),
+        grad_output, grad_aux, grad_probability_sum, h2, router_weight, _operands(w13_experts),
+        _operands(w2_experts), logits, route_weights, route_ids, order, offsets, slots, h13, top_k=int(top_k),
         routing_mode=str(routing_mode), lengths=lengths, weight_grad_dtype=wdtype, **kwargs,
     )
 

@@ -257,6 +257,21 @@ def grouped_block_gemm(a_q, a_scale, b_q, b_scale, offsets, *, b_mn_major=False,
     return out
 
 
+def grouped_mm(a, b, offsets, *, b_mn_major=False, dtype=torch.float64):
+    """`out[rows_e] = a[rows_e] @ b[e].T` (`b [E, N, K]`) or `a[rows_e] @ b[e]` (`b [E, K, N]`,
+    `b_mn_major`): the dense per-expert products of the bf16 path
+    (src/mlops/kernels/moe_grouped_gemm.py:185-198), at `dtype`."""
+    n = b.shape[2] if b_mn_major else b.shape[1]
+    out = torch.zeros((a.shape[0], n), dtype=dtype)
+    offs = offsets.tolist()
+    for e in range(len(offs) - 1):
+        lo, hi = offs[e], offs[e + 1]
+        if hi > lo:
+            w = b[e % b.shape[0]].to(dtype)
+            out[lo:hi] = a[lo:hi].to(dtype) @ (w if b_mn_major else w.t())
+    return out
+
+
 def grouped_wgrad(g, x, offsets, groups, dtype=torch.float64):
     """`out[e] = g[rows_e].T @ x[rows_e]`; zeros for an expert without rows.
     Follows src/mlops/kernels/moe_grouped_gemm.py:185-198,300-342."""
@@ -414,6 +429,47 @@ def backward_block_fp8(grad_output, h2, fwd, w13_q, w13_s, w2_q, w2_s, *, top_k,
     x_rows = h2[token_of_row].to(torch.bfloat16)
     grad_w2 = grouped_wgrad(dy_rows, act_scaled.to(torch.bfloat16), offsets, experts, gemm_dtype)
     grad_w13 = grouped_wgrad(grad_h13.to(torch.bfloat16), x_rows, offsets, experts, gemm_dtype)
+    return dict(r=r, dscore=dscore, grad_route_weights=grad_route_weights, grad_h13=grad_h13,
+                grad_rows=grad_rows, grad_h2=grad_h2, grad_w2=grad_w2, grad_w13=grad_w13)
+
+
+def forward_bf16(h2, residual, logits, w13, w2, *, top_k, routing_mode, router_bias=None, n_group=1,
+                 topk_group=1, routed_scaling=1.0, swiglu_limit=None, gemm_dtype=torch.float64):
+    """The routed layer on plain bf16 expert weights: route -> sort -> gather -> up product (bf16
+    h13, gate rows then up rows) -> SwiGLU (fp32, one rounding) -> down product (bf16 rows) ->
+    combine. Orchestration: src/mlops/providers/moe_common.py:174-266 around the bf16 grouped
+    products of src/mlops/kernels/moe_grouped_gemm.py:185-198."""
+    experts = w13.shape[0]
+    weights, ids = route(logits, top_k, routing_mode, bias=router_bias, n_group=n_group,
+                         topk_group=topk_group, routed_scaling=routed_scaling)
+    order, offsets, slots = sort_assignments(ids, experts)
+    token_of_row = torch.div(order.long(), int(top_k), rounding_mode="floor")
+    x_rows = h2[token_of_row].to(torch.bfloat16)
+    h13 = grouped_mm(x_rows, w13, offsets, dtype=gemm_dtype).to(torch.bfloat16)
+    act = swiglu(h13, swiglu_limit).to(torch.bfloat16)
+    y = grouped_mm(act, w2, offsets, dtype=gemm_dtype).to(torch.bfloat16)
+    output = combine(y, slots, weights, residual)
+    return dict(weights=weights, ids=ids, order=order, offsets=offsets, slots=slots, h13=h13, act=act, y=y,
+                output=output)
+
+
+def backward_bf16(grad_output, h2, fwd, w13, w2, *, top_k, swiglu_limit=None, gemm_dtype=torch.float64):
+    """VJP of `forward_bf16` (src/mlops/providers/moe_common.py:269-378): every product on bf16
+    operands with wide sums, each intermediate rounded to bf16 where the device stores it."""
+    experts = w13.shape[0]
+    order, offsets, slots, weights = fwd["order"], fwd["offsets"], fwd["slots"], fwd["weights"]
+    token_of_row = torch.div(order.long(), int(top_k), rounding_mode="floor")
+    dy_rows = grad_output[token_of_row].to(torch.bfloat16)
+    r = grouped_mm(dy_rows, w2, offsets, b_mn_major=True, dtype=gemm_dtype).to(torch.bfloat16)
+    score = weights.reshape(-1)[order.long()].float()
+    dscore, grad_h13, act_scaled = dswiglu_routed(fwd["h13"], r, score, swiglu_limit)
+    grad_route_weights = dscore[slots.reshape(-1).long()].view_as(weights)
+    gh = grad_h13.to(torch.bfloat16)
+    grad_rows = grouped_mm(gh, w13, offsets, b_mn_major=True, dtype=gemm_dtype).to(torch.bfloat16)
+    grad_h2 = combine(grad_rows, slots, None, None)
+    x_rows = h2[token_of_row].to(torch.bfloat16)
+    grad_w2 = grouped_wgrad(dy_rows, act_scaled.to(torch.bfloat16), offsets, experts, gemm_dtype)
+    grad_w13 = grouped_wgrad(gh, x_rows, offsets, experts, gemm_dtype)
     return dict(r=r, dscore=dscore, grad_route_weights=grad_route_weights, grad_h13=grad_h13,
                 grad_rows=grad_rows, grad_h2=grad_h2, grad_w2=grad_w2, grad_w13=grad_w13)
 

@@ -361,3 +361,37 @@ def test_fp8_weight_gradient_recipe_through_the_operator():
         assert ((fp8 - exact).norm() / exact.norm()).item() < 6e-2
     with pytest.raises(ValueError):
         provider.set_weight_gradient_operands("fp4")
+
+
+def test_bf16_experts_run_the_bf16_path_through_the_operator(golden):
+    """Plain bf16 expert tensors (the builtin's default weights) and `compute_precision="bf16"` on
+    block-FP8 containers both reach the bf16 grouped GEMMs; on the same weight values the two agree
+    bit for bit, and with the stored outputs of the reference's bf16 provider to rounding."""
+    from mlops_b200 import ops, provider
+    from mlops_b200.weights import BlockFP8Weight
+
+    c1 = inputs.config1()
+    x = c1["x"].to(DEV).requires_grad_(True)
+    router = c1["router"].to(DEV).requires_grad_(True)
+    dy, residual = c1["dy"].to(DEV), torch.zeros_like(c1["x"]).to(DEV)
+    q13, q2 = BlockFP8Weight.quantize(c1["w13"].to(DEV)), BlockFP8Weight.quantize(c1["w2"].to(DEV))
+    w13 = q13.dequantize().to(torch.bfloat16).detach().requires_grad_(True)
+    w2 = q2.dequantize().to(torch.bfloat16).detach().requires_grad_(True)
+    kwargs = dict(top_k=2, routing_mode="softmax_then_topk")
+    assert provider.refusal(x, residual, router, w13, w2, surface="opaque", **kwargs) is None
+    assert provider.refusal(x, residual, router, w13, w2, surface="opaque", compute_precision="fp8_block",
+                            **kwargs) is not None
+    out = provider.apply(x, residual, router, w13, w2, **kwargs)
+    grads = torch.autograd.grad(out[0], [x, router, w13, w2], dy)
+    q13.requires_grad_(True), q2.requires_grad_(True)
+    out_c = provider.apply(x, residual, router, q13, q2, compute_precision="bf16", **kwargs)
+    grads_c = torch.autograd.grad(out_c[0], [x, router, q13, q2], dy)
+    ops.check_status(DEV)
+    assert torch.equal(out[0], out_c[0])
+    for a, b in zip(grads, grads_c):
+        assert torch.equal(a, b)
+    fixture = golden("config1_native_torch.pt")
+    frob = lambda a, e: ((a.double().cpu() - e.double()).norm() / e.double().norm()).item()  # noqa: E731
+    assert frob(out[0], fixture["output"]) < 1e-2
+    assert frob(grads[0], fixture["grad_x"]) < 1e-2
+    assert frob(grads[2][:, ::16, ::8], fixture["grad_w13_sample"]) < 1e-2

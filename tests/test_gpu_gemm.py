@@ -232,6 +232,34 @@ def test_wgrad_groups_are_isolated_from_a_neighbours_inf_and_nan(m, n):
     assert torch.equal(dirty[2][:, keep.to(DEV)], clean[2][:, keep.to(DEV)])
 
 
+@pytest.mark.parametrize("b_mn_major", [False, True])
+@pytest.mark.parametrize(
+    "counts,n,k",
+    [([128], 256, 64), ([128], 256, 512), ([0, 70, 131, 15, 260], 512, 192), ([0, 70, 131, 15, 260], 320, 456),
+     ([1000, 3, 0, 500], 768, 1024)],
+)
+def test_grouped_gemm_bf16(counts, n, k, b_mn_major):
+    """The bf16 forward / input-gradient product against float64 of the same operands: one rounding
+    to bf16 is the only difference, so the bound is bf16's half ulp. Empty experts, partial row
+    tiles, N and K that are no multiples of the tile, both operand orders of the stored weight."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(n + k + int(b_mn_major))
+    rows, groups = sum(counts), len(counts)
+    a = torch.randn(rows, k, generator=g).bfloat16()
+    b = (torch.randn(groups, k, n, generator=g) if b_mn_major else torch.randn(groups, n, k, generator=g)).bfloat16()
+    addend = torch.randn(rows, n, generator=g).bfloat16()
+    offs = _offsets(counts)
+    out = ops.grouped_gemm_bf16(a.to(DEV), b.to(DEV), offs.to(DEV), b_mn_major=b_mn_major)
+    out_add = ops.grouped_gemm_bf16(a.to(DEV), b.to(DEV), offs.to(DEV), b_mn_major=b_mn_major, addend=addend.to(DEV))
+    ops.check_status(DEV)
+    ref = O.grouped_mm(a, b, offs, b_mn_major=b_mn_major)
+    assert torch.equal(out.cpu(), ref.bfloat16()) or O.rel_errors(out.float().cpu(), ref)[0] <= 4e-3
+    mx, mean = O.rel_errors(out.float().cpu(), ref)
+    assert mx <= 4e-3 and mean <= 1.5e-3, (mx, mean)
+    mx, mean = O.rel_errors(out_add.float().cpu(), ref + addend.double())
+    assert mx <= 4e-3 and mean <= 1.5e-3, (mx, mean)
+
+
 @pytest.mark.parametrize("counts,width", [([64], 128), ([0, 70, 131, 15, 260], 384), ([300, 1, 0, 555], 1024)])
 def test_quantize_columns_is_bit_exact(counts, width):
     """Column-scaled E4M3 (one scale per expert and column over the expert's rows): bytes and

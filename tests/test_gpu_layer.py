@@ -82,6 +82,73 @@ def _run_case(x, residual, router, w13, w2, dy, *, top_k, mode, bias=None, n_gro
     return result, grads
 
 
+@pytest.mark.parametrize("case", ["config1", "groups"])
+def test_bf16_compute_path_against_the_oracle_and_the_reference(case, golden):
+    """Plain bf16 expert weights select the bf16 path (bf16 grouped GEMMs, nothing quantised):
+    every output and gradient against the CPU restatement on the same bf16 weights, and on
+    configuration 1 against the stored outputs of the reference's own bf16 provider
+    (`native_torch.moe` on the dequantised block-FP8 weights: the same weight values)."""
+    layer, ops = _layer()
+    if case == "config1":
+        c = inputs.config1()
+        x, residual, router, dy = c["x"], c["residual"], c["router"], c["dy"]
+        w13_q, w13_s = O.quantize_blocks(c["w13"])
+        w2_q, w2_s = O.quantize_blocks(c["w2"])
+        w13 = O.dequantize_blocks(w13_q, w13_s, torch.bfloat16)   # what the reference multiplies
+        w2 = O.dequantize_blocks(w2_q, w2_s, torch.bfloat16)
+        kwargs = dict(top_k=c["top_k"], routing_mode=c["routing_mode"])
+        bias = None
+    else:
+        g = torch.Generator().manual_seed(31)
+        tokens, width, inner, experts = 192, 192, 80, 16   # partial tiles everywhere
+        x = torch.randn(tokens, width, generator=g).bfloat16()
+        residual = torch.randn(tokens, width, generator=g).bfloat16()
+        dy = torch.randn(tokens, width, generator=g).bfloat16()
+        router = torch.randn(experts, width, generator=g) * 0.05
+        w13 = (torch.randn(experts, 2 * inner, width, generator=g) * 0.05).bfloat16()
+        w2 = (torch.randn(experts, width, inner, generator=g) * 0.05).bfloat16()
+        bias = torch.randn(experts, generator=g) * 0.1
+        kwargs = dict(top_k=4, routing_mode="sigmoid_noaux_tc", n_group=4, topk_group=2, routed_scaling=2.5)
+    dev = lambda t: None if t is None else t.to(DEV)  # noqa: E731
+    result = layer.forward_routed(dev(x), dev(residual), dev(router), dev(w13), dev(w2), router_bias=dev(bias),
+                                  swiglu_limit=7.0 if case == "groups" else None, **kwargs)
+    output, aux, counts, psum, logits, route_weights, route_ids, order, offsets, slots, h13 = result
+    ops.check_status(DEV)
+    fwd = O.forward_bf16(x, residual, logits.cpu(), w13, w2, router_bias=bias,
+                         swiglu_limit=7.0 if case == "groups" else None, **kwargs)
+    assert torch.equal(route_ids.cpu(), fwd["ids"]) and torch.equal(order.cpu(), fwd["order"])
+    _check(h13, fwd["h13"].float(), "h13")
+    _check(output, fwd["output"].float(), "output")
+    back_kwargs = {k: v for k, v in kwargs.items() if k in ("top_k", "routing_mode")}
+    grads = layer.backward_routed(dev(dy), None, None, dev(x), dev(router), dev(w13), dev(w2), logits,
+                                  route_weights, route_ids, order, offsets, slots, h13,
+                                  swiglu_limit=7.0 if case == "groups" else None,
+                                  weight_grad_dtype=torch.float32, **back_kwargs)
+    ops.check_status(DEV)
+    bwd = O.backward_bf16(dy, x, dict(fwd, h13=h13.cpu()), w13, w2, top_k=kwargs["top_k"],
+                          swiglu_limit=7.0 if case == "groups" else None)
+    grad_logits = O.routing_gradient(None, None, bwd["grad_route_weights"], fwd["weights"], fwd["ids"],
+                                     logits.cpu(), counts.cpu(), routing_mode=kwargs["routing_mode"],
+                                     lengths=(x.shape[0],))
+    _check(grads[0], bwd["grad_h2"].float() + grad_logits.bfloat16().float() @ router.bfloat16().float(), "grad_h2")
+    assert torch.equal(grads[1].cpu(), dy)
+    _check(grads[2], grad_logits.t() @ x.float(), "grad_router")
+    _check(grads[3], bwd["grad_w13"], "grad_w13")
+    _check(grads[4], bwd["grad_w2"], "grad_w2")
+    if case == "config1":
+        fixture = golden("config1_native_torch.pt")
+
+        def frob(a, e):
+            return ((a.double().cpu() - e.double()).norm() / e.double().norm()).item()
+
+        # bf16 against bf16 on the same weight values: rounding-order differences only
+        assert frob(output, fixture["output"]) < 1e-2
+        assert frob(grads[0], fixture["grad_x"]) < 1e-2
+        assert frob(grads[2], fixture["grad_router"]) < 2e-2
+        assert frob(grads[3][:, ::16, ::8], fixture["grad_w13_sample"]) < 1e-2
+        assert frob(grads[4][:, ::8, ::16], fixture["grad_w2_sample"]) < 1e-2
+
+
 def test_fp8_weight_gradients_stay_within_the_reference_bound_of_that_recipe():
     """`weight_grad_operands="fp8"`: the other gradients do not change at all, and the expert
     weight gradients stay within the relative-Frobenius bound the reference sets for its FP8

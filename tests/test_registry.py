@@ -79,7 +79,11 @@ def test_refusal_reasons_are_specific():
         assert provider.refusal(x, x, router, w13, w2, **ok) is None
         assert "BlockFP8Weight" in provider.refusal(x, x, router, dense, w2, **ok)
         assert "bf16" in provider.refusal(x.float(), x.float(), router, w13, w2, **ok)
-        assert "compute_precision" in provider.refusal(x, x, router, w13, w2, compute_precision="bf16", **ok)
+        assert "compute_precision" in provider.refusal(x, x, router, w13, w2, compute_precision="fp4", **ok)
+        assert provider.refusal(x, x, router, w13, w2, compute_precision="bf16", **ok) is None
+        assert provider.refusal(x, x, router, dense, w2.dequantize(), **ok) is None          # plain bf16 experts
+        assert "fp8_block" in provider.refusal(x, x, router, dense, w2.dequantize(), compute_precision="fp8_block",
+                                               **ok)
         assert "top_k" in provider.refusal(x, x, router, w13, w2, top_k=9, routing_mode="softmax_then_topk")
         assert "routing mode" in provider.refusal(x, x, router, w13, w2, top_k=2, routing_mode="other")
         assert "lengths" in provider.refusal(x, x, router, w13, w2, lengths=(3,), **ok)
