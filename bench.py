@@ -377,7 +377,7 @@ class Layer:
     """One workload on one device (or one rank): parameters, inputs and `step(x, dy)`, which runs
     forward + backward through the public call and returns `(output, grad_x, aux, counts)`."""
 
-    def __init__(self, cfg, device, *, world=1, rank=0, group=None, bias_std=BALANCED_BIAS_STD):
+    def __init__(self, cfg, device, *, world=1, rank=0, group=None, bias_std=BALANCED_BIAS_STD, bf16_weights=False):
         from mlops_b200 import provider
         from mlops_b200.weights import BlockFP8Weight
 
@@ -426,8 +426,14 @@ class Layer:
         else:
             # what a trainer holds: parameters that ask for gradients (a frozen base under LoRA)
             frozen = self.factors is not None
-            self.w13_param = BlockFP8Weight(*self.w13).requires_grad_(not frozen)
-            self.w2_param = BlockFP8Weight(*self.w2).requires_grad_(not frozen)
+            if bf16_weights:
+                # plain bf16 experts with the same values: the bf16 compute path
+                self.w13_param = BlockFP8Weight(*self.w13).dequantize().to(torch.bfloat16).requires_grad_(not frozen)
+                self.w2_param = BlockFP8Weight(*self.w2).dequantize().to(torch.bfloat16).requires_grad_(not frozen)
+                self.w13 = self.w2 = None
+            else:
+                self.w13_param = BlockFP8Weight(*self.w13).requires_grad_(not frozen)
+                self.w2_param = BlockFP8Weight(*self.w2).requires_grad_(not frozen)
             self.router_param = self.router.requires_grad_(not frozen)
             if self.shared is not None:
                 self.shared = tuple(w.requires_grad_(True) for w in self.shared)
@@ -490,7 +496,7 @@ class Layer:
 
 
 def gemm_summary(timings, steps):
-    fp8 = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind == "fp8"]
+    fp8 = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind in ("fp8", "gemm_bf16")]
     wg = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind in ("wgrad_bf16", "wgrad_fp8")]
     fp8_ms, fp8_flops = sum(t for t, _ in fp8), sum(f for _, f in fp8)
     return {
@@ -677,11 +683,11 @@ def extras(device, peaks, fp8_peak):
     from mlops_b200 import provider
 
     for key, bias_std in (("c3", BALANCED_BIAS_STD), ("c5", BALANCED_BIAS_STD), ("c4_skewed", SKEWED_BIAS_STD),
-                          ("c4_fp8_weight_gradients", BALANCED_BIAS_STD)):
-        cfg = dict(WORKLOADS["c4" if key.startswith("c4_") else key])
+                          ("c4_fp8_weight_gradients", BALANCED_BIAS_STD), ("c3_bf16_experts", BALANCED_BIAS_STD)):
+        cfg = dict(WORKLOADS["c4" if key.startswith("c4_") else "c3" if key.startswith("c3") else key])
         gc.collect()
         torch.cuda.empty_cache()
-        layer = Layer(cfg, device, bias_std=bias_std)
+        layer = Layer(cfg, device, bias_std=bias_std, bf16_weights=key == "c3_bf16_experts")
         # the optional recipe with E4M3 operands for the expert weight gradients (not the headline's)
         previous = provider.set_weight_gradient_operands("fp8" if key == "c4_fp8_weight_gradients" else "bf16")
         try:
@@ -699,6 +705,12 @@ def extras(device, peaks, fp8_peak):
             entry["fp8_frac_of_measured_fp8_sustained"] = (gemms["fp8_tflops"] or 0.0) / fp8_peak["sustained"]
         if key == "c4_skewed":
             entry["router_bias"] = f"N(0, {SKEWED_BIAS_STD}): skewed load"
+        if key == "c3_bf16_experts":
+            entry["compute"] = ("plain bf16 expert weights: bf16 grouped GEMMs, nothing quantised; fp8_gemm_tflops "
+                                "holds the bf16 forward / input-gradient GEMMs here (compare with bf16 peaks)")
+            del entry["fp8_frac_of_2x_bf16_sustained"]
+            entry.pop("fp8_frac_of_measured_fp8_sustained", None)
+            entry["bf16_gemm_frac_of_bf16_sustained"] = (gemms["fp8_tflops"] or 0.0) / peaks["bf16_tflops_sustained"]
         if key == "c4_fp8_weight_gradients":
             entry["weight_grads"] = ("E4M3 operands, one scale per expert and column (quantised per step), fp32 sums; "
                                      "wgrad_tflops counts the GEMMs only, ms_per_step includes the quantisation")
