@@ -739,6 +739,8 @@ def gpu_arm(args, cfg):
         # their tiles dynamically and take whatever SMs are left
         comm_sms = int(os.environ.get("B200MOE_EP_COMM_SMS", "32"))
         os.environ.setdefault("NCCL_MAX_CTAS", str(comm_sms))
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # keeps NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
         from mlops_b200 import ep as ep_module
