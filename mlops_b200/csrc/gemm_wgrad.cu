@@ -44,6 +44,7 @@ struct WgradParams {
   // X ([groups, N]); the product of a group is multiplied by g_scale[m] * x_scale[n] at the store.
   const float* g_scale;
   const float* x_scale;
+  int wide_store;  // the output's base and row pitch are multiples of 32 bytes: 32-byte stores
 };
 
 // Geometry of a K block in shared memory.  A panel is 128 bytes of an operand's columns for every
@@ -100,8 +101,14 @@ __device__ __forceinline__ void load8<float>(const float* src, float (&v)[8]) {
 
 // The store of eight sums: scaled, and added to what the destination holds when the caller
 // accumulates gradients over several calls (micro-batches) in one buffer.
+// -DB200_WGRAD_ABLATE_STORE=1 (timing experiments only) drops the store: what the epilogue's
+// writes cost the main loop shows as the difference.  The shipped library stores.
+#ifndef B200_WGRAD_ABLATE_STORE
+#define B200_WGRAD_ABLATE_STORE 0
+#endif
 template <typename OutT>
 __device__ __forceinline__ void finish8(OutT* dst, float (&v)[8], float scale, int accumulate) {
+  if (B200_WGRAD_ABLATE_STORE && v[0] != 12345.678f) return;
   if (accumulate) {
     float old[8];
     load8<OutT>(dst, old);
@@ -112,6 +119,90 @@ __device__ __forceinline__ void finish8(OutT* dst, float (&v)[8], float scale, i
     for (int i = 0; i < 8; ++i) v[i] *= scale;
   }
   store8<OutT>(dst, v);
+}
+
+// 32 bytes per lane and instruction: a lane's store fills whole 32-byte sectors of its output row
+// (16-byte pieces of 32 different rows per instruction cost the weight gradient a fifth of its
+// time in sector-merging traffic).  The address must be 32-byte aligned.
+__device__ __forceinline__ void store_v8(void* dst, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+__device__ __forceinline__ void load_v8(const void* src, uint32_t (&w)[8]) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(src)
+               : "memory");
+}
+
+// The store of one lane's 32 consecutive sums of a row (`cols` of them inside the matrix, a
+// multiple of 8): scaled, added to the destination when the caller accumulates, rounded once.
+// `wide`: the row pitch and base allow 32-byte accesses.
+template <typename OutT>
+__device__ __forceinline__ void finish32(OutT* dst, float (&v)[32], int cols, float scale, int accumulate, bool wide);
+
+template <>
+__device__ __forceinline__ void finish32<float>(float* dst, float (&v)[32], int cols, float scale, int accumulate,
+                                                bool wide) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if (g * 8 + 8 > cols) break;
+    float part[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part[i] = v[g * 8 + i];
+    if (!wide) {
+      finish8<float>(dst + g * 8, part, scale, accumulate);
+      continue;
+    }
+    uint32_t w[8];
+    if (accumulate) {
+      load_v8(dst + g * 8, w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) part[i] = fmaf(scale, part[i], __uint_as_float(w[i]));
+    } else if (scale != 1.0f) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) part[i] *= scale;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __float_as_uint(part[i]);
+    store_v8(dst + g * 8, w);
+  }
+}
+
+template <>
+__device__ __forceinline__ void finish32<__nv_bfloat16>(__nv_bfloat16* dst, float (&v)[32], int cols, float scale,
+                                                        int accumulate, bool wide) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (wide && h * 16 + 16 <= cols) {
+      uint32_t w[8];
+      if (accumulate) {
+        load_v8(dst + h * 16, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 old = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+          v[h * 16 + 2 * i] = fmaf(scale, v[h * 16 + 2 * i], old.x);
+          v[h * 16 + 2 * i + 1] = fmaf(scale, v[h * 16 + 2 * i + 1], old.y);
+        }
+      } else if (scale != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[h * 16 + i] *= scale;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(v[h * 16 + 2 * i], v[h * 16 + 2 * i + 1]);
+      store_v8(dst + h * 16, w);
+    } else {
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        if (h * 16 + g * 8 + 8 > cols) break;
+        float part[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) part[i] = v[h * 16 + g * 8 + i];
+        finish8<__nv_bfloat16>(dst + h * 16 + g * 8, part, scale, accumulate);
+      }
+    }
+  }
 }
 
 template <typename OutT, bool FP8>
@@ -348,23 +439,24 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_co
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (m < p.M) {
+        const int cols = min(32, p.N - (col0 + cc * 32));  // of this chunk inside the matrix (a multiple of 8)
+        if (m < p.M && cols > 0) {
+          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col0 + cc * 32 + j + 8 <= p.N) {
-              float v[8];
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if constexpr (FP8) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
-              if constexpr (FP8) {
-                const float4 s0 = *reinterpret_cast<const float4*>(col_scale + cc * 32 + j);
-                const float4 s1 = *reinterpret_cast<const float4*>(col_scale + cc * 32 + j + 4);
-                const float cs[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] *= row_scale * cs[i];
+            for (int j = 0; j < 32; j += 4) {
+              if (j < cols) {
+                const float4 cs = *reinterpret_cast<const float4*>(col_scale + cc * 32 + j);
+                v[j] *= row_scale * cs.x;
+                v[j + 1] *= row_scale * cs.y;
+                v[j + 2] *= row_scale * cs.z;
+                v[j + 3] *= row_scale * cs.w;
               }
-              finish8<OutT>(orow + cc * 32 + j, v, p.scale, p.accumulate);
             }
           }
+          finish32<OutT>(orow + cc * 32, v, cols, p.scale, p.accumulate, p.wide_store != 0);
         }
       }
       if (has_rows) {
@@ -650,16 +742,12 @@ grouped_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tmap_g, const __gr
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (m < p.M) {
+        const int cols = min(32, p.N - (col0 + cc * 32));  // of this chunk inside the matrix (a multiple of 8)
+        if (m < p.M && cols > 0) {
+          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col0 + cc * 32 + j + 8 <= p.N) {
-              float v[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]);
-              finish8<OutT>(orow + cc * 32 + j, v, p.scale, p.accumulate);
-            }
-          }
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          finish32<OutT>(orow + cc * 32, v, cols, p.scale, p.accumulate, p.wide_store != 0);
         }
       }
       if (has_rows) {
@@ -777,6 +865,7 @@ static int grouped_wgrad_impl(const void* g, long long ldg, const void* x, long 
   p.accumulate = accumulate;
   p.g_scale = nullptr;
   p.x_scale = nullptr;
+  p.wide_store = (((uintptr_t)out & 31) == 0 && ((size_t)N * esz) % 32 == 0 && ((size_t)M * N * esz) % 32 == 0) ? 1 : 0;
   // Wide outputs go to the CTA-pair kernel (256-row tiles); narrow ones (LoRA factors) and the
   // B200MOE_WGRAD_SINGLE=1 escape hatch use the single-CTA kernel.
   static const bool force_single = [] {
@@ -856,6 +945,7 @@ extern "C" int b200moe_grouped_wgrad_fp8(const void* g, long long ldg, const flo
   p.accumulate = accumulate;
   p.g_scale = g_scale;
   p.x_scale = x_scale;
+  p.wide_store = (((uintptr_t)out & 31) == 0 && ((size_t)N * esz) % 32 == 0 && ((size_t)M * N * esz) % 32 == 0) ? 1 : 0;
   const long long tiles = (long long)groups * ((M + kWgBlockM - 1) / kWgBlockM) * ((N + kWgBlockN - 1) / kWgBlockN);
   long long grid = tiles < sm_count() ? tiles : sm_count();
   if (out_is_fp32) {

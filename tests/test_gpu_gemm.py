@@ -260,6 +260,62 @@ def test_grouped_gemm_bf16(counts, n, k, b_mn_major):
     assert mx <= 4e-3 and mean <= 1.5e-3, (mx, mean)
 
 
+def test_bf16_gemm_and_fp8_weight_gradient_at_layer_size():
+    """The two newer tensor-core kernels at the size of a DeepSeek-V3-shaped layer slice (32
+    experts with a Zipf split of 32768 rows, D=7168, 2F=4096): size-independent properties and
+    sampled pieces against float64. bf16 GEMM: exact linearity in a power-of-two factor of the
+    weights, sampled rows. FP8 weight gradient: exact linearity in the column scales, sampled
+    output blocks, and the all-experts sum against one dense product of the quantised operands."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    p = torch.arange(1, 33).float().pow(-1.1)
+    counts = torch.bincount(torch.multinomial(p / p.sum(), 32768, replacement=True, generator=g), minlength=32)
+    offs = _offsets(counts.tolist()).to(DEV)
+    gd = torch.Generator(device=DEV).manual_seed(4)
+    x = torch.randn(32768, 7168, device=DEV, generator=gd).bfloat16()
+    w13 = (torch.randn(32, 4096, 7168, device=DEV, generator=gd) * 0.05).bfloat16()
+    h = ops.grouped_gemm_bf16(x, w13, offs)
+    assert torch.equal(ops.grouped_gemm_bf16(x, w13 * 4, offs).float(), h.float() * 4)
+    back = ops.grouped_gemm_bf16(h, w13, offs, b_mn_major=True)   # dx-shaped product on the same weight
+    ops.check_status(DEV)
+    offs_cpu = offs.cpu().tolist()
+    for group in (0, 7, 31):
+        lo, hi = offs_cpu[group], offs_cpu[group + 1]
+        if hi == lo:
+            continue
+        rows = slice(lo, min(hi, lo + 48))
+        local = torch.tensor([0, rows.stop - rows.start], dtype=torch.int32)
+        ref = O.grouped_mm(x[rows].cpu(), w13[group:group + 1].cpu(), local)
+        mx, mean = O.rel_errors(h[rows].float().cpu(), ref)
+        assert mx <= 4e-3 and mean <= 1.5e-3, (mx, mean)
+        ref = O.grouped_mm(h[rows].cpu(), w13[group:group + 1].cpu(), local, b_mn_major=True)
+        mx, mean = O.rel_errors(back[rows].float().cpu(), ref)
+        assert mx <= 4e-3 and mean <= 1.5e-3, (mx, mean)
+    # FP8 weight gradient dW13 = dh^T x per expert
+    dh = torch.randn(32768, 4096, device=DEV, generator=gd).bfloat16()
+    dh_q, dh_s = ops.quantize_columns(dh, offs, 32)
+    x_q, x_s = ops.quantize_columns(x, offs, 32)
+    dw = ops.grouped_wgrad_fp8(dh_q, dh_s, x_q, x_s, offs, 32, torch.float32)
+    assert torch.equal(ops.grouped_wgrad_fp8(dh_q, dh_s * 2, x_q, x_s * 0.5, offs, 32, torch.float32), dw)
+    ops.check_status(DEV)
+    for group in (0, 7, 31):
+        lo, hi = offs_cpu[group], offs_cpu[group + 1]
+        if hi == lo:
+            assert int(torch.count_nonzero(dw[group])) == 0
+            continue
+        local = torch.tensor([0, hi - lo], dtype=torch.int32)
+        ref = O.grouped_wgrad_fp8(dh_q[lo:hi, 128:192].cpu(), dh_s[group:group + 1, 128:192].cpu(),
+                                  x_q[lo:hi, 7040:7168].cpu(), x_s[group:group + 1, 7040:7168].cpu(), local, 1)
+        mx, mean = O.rel_errors(dw[group, 128:192, 7040:7168].cpu(), ref[0])
+        assert mx <= 1e-4 and mean <= 1e-5, (mx, mean)
+    # checksum over experts: with unit scales, the sum of all experts' products is one dense product
+    ones_m, ones_n = torch.ones_like(dh_s), torch.ones_like(x_s)
+    total = ops.grouped_wgrad_fp8(dh_q, ones_m, x_q, ones_n, offs, 32, torch.float32).sum(0)
+    dense = dh_q[:, :256].float().t() @ x_q[:, :512].float()
+    mx, mean = O.rel_errors(total[:256, :512].cpu(), dense.double().cpu())
+    assert mx <= 1e-3 and mean <= 1e-4, (mx, mean)
+
+
 @pytest.mark.parametrize("counts,width", [([64], 128), ([0, 70, 131, 15, 260], 384), ([300, 1, 0, 555], 1024)])
 def test_quantize_columns_is_bit_exact(counts, width):
     """Column-scaled E4M3 (one scale per expert and column over the expert's rows): bytes and
