@@ -126,6 +126,7 @@ struct GemmFp8Params {
   const int* row_map;  // optional: output row r is stored at d[row_map[r]] (NULL: in place)
   long long out_rows;  // rows of d (row_map) or of out_f32 (row_token): targets outside are skipped
   int sched_slot;      // slot of g_tile_counter, or -1: tiles by CTA index
+  int wide_store;      // d's base and row pitch are multiples of 32 bytes: 32-byte stores per lane
   int* status;
 #ifdef B200_GEMM_TRACE
   long long* trace;
@@ -800,6 +801,30 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             continue;
           }
+          const int chunk_col0 = EPI == 1 ? ((cc >> 1) ? c.col1 : c.col0) + (cc & 1) * 32 : col0 + cc * 32;
+          if (p.wide_store && chunk_col0 + 32 <= p.N) {
+            // 32 bytes per lane and instruction straight from the registers: whole sectors of the
+            // lane's own row, no trip through shared memory (the store phase of a tile holds up the
+            // next tile's accumulators, so its length counts: 16 K blocks per tile in the down
+            // projection)
+            if (lane < rows_here && out_row >= 0) {
+              __nv_bfloat16* drow = p.d + (long long)out_row * p.ldd + chunk_col0;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(drow + h * 16),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 0], acc[cc * 32 + h * 16 + 1])),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 2], acc[cc * 32 + h * 16 + 3])),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 4], acc[cc * 32 + h * 16 + 5])),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 6], acc[cc * 32 + h * 16 + 7])),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 8], acc[cc * 32 + h * 16 + 9])),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 10], acc[cc * 32 + h * 16 + 11])),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 12], acc[cc * 32 + h * 16 + 13])),
+                             "r"(pack_bf16x2(acc[cc * 32 + h * 16 + 14], acc[cc * 32 + h * 16 + 15]))
+                             : "memory");
+              }
+            }
+            continue;
+          }
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -1077,6 +1102,11 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
   p.b_scale = b_scale;
   p.d = reinterpret_cast<__nv_bfloat16*>(d);
   p.ldd = ldd;
+  static const bool narrow_store = [] {  // B200MOE_GEMM_WIDE_STORE=0: the store through shared memory
+    const char* v = getenv("B200MOE_GEMM_WIDE_STORE");
+    return v != nullptr && v[0] == '0';
+  }();
+  p.wide_store = (!narrow_store && d != nullptr && ((uintptr_t)d & 31) == 0 && (ldd % 16) == 0) ? 1 : 0;
   p.addend = reinterpret_cast<const __nv_bfloat16*>(addend);
   p.ldc = ldc;
   p.offsets = offsets;
@@ -1251,6 +1281,7 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.bs_k_stride = 1;
   p.d = reinterpret_cast<__nv_bfloat16*>(h13);
   p.ldd = ldh;
+  p.wide_store = (((uintptr_t)h13 & 31) == 0 && (ldh % 16) == 0) ? 1 : 0;
   p.addend = nullptr;
   p.ldc = 0;
   p.offsets = offsets;
