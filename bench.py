@@ -453,6 +453,10 @@ class Layer:
         # one pre-weighted row per token copy on the way back (the reference's layers return
         # pre-weighted rows too); B200MOE_EP_PRESUM=0 returns one row per assignment
         presum = dedup and os.environ.get("B200MOE_EP_PRESUM", "1") == "1"
+        # the token rows of a de-duplicated dispatch travel by this library's own kernel over NVLink
+        # peer memory (B200MOE_EP_TRANSPORT=nccl: through a send buffer and the library all-to-all)
+        transport = os.environ.get("B200MOE_EP_TRANSPORT", "peer") if dedup and self.world <= 16 else "nccl"
+        self.transport = transport
         lora = None
         if self.factors is not None:
             lora = dict(zip(("a13", "b13", "a2", "b2"), self.factors), scale=1.0)
@@ -460,7 +464,7 @@ class Layer:
             ep_module.ExpertParallelConfig(hidden=cfg["D"], experts=cfg["E"], intermediate=cfg["F"], top_k=cfg["K"],
                                            routing_mode=cfg["mode"], n_group=cfg["n_group"],
                                            topk_group=cfg["topk_group"], routed_scaling=cfg["scaling"],
-                                           expert_map=expert_map, dedup=dedup, presum=presum),
+                                           expert_map=expert_map, dedup=dedup, presum=presum, transport=transport),
             group, router_weight=self.router, router_bias=self.bias, w13=self.w13, w2=self.w2, shared=self.shared,
             device=self.device,
             chunks=int(os.environ["B200MOE_EP_CHUNKS"]) if "B200MOE_EP_CHUNKS" in os.environ else None,
@@ -750,7 +754,8 @@ def gpu_arm(args, cfg):
         ep_check = ep_module.parity_check(group, device, routing_mode=cfg["mode"], n_group=cfg["n_group"],
                                           topk_group=cfg["topk_group"], routed_scaling=cfg["scaling"],
                                           shared=cfg["shared"],
-                                          presum=os.environ.get("B200MOE_EP_PRESUM", "1") == "1")
+                                          presum=os.environ.get("B200MOE_EP_PRESUM", "1") == "1",
+                                          transport=os.environ.get("B200MOE_EP_TRANSPORT", "peer"))
     if args.workload == "c2":
         peaks, peak_kind = measured_peaks()
         fp8_peak = measure_fp8_peak(device)
@@ -876,6 +881,7 @@ def gpu_arm(args, cfg):
                    "expert_parallel": world, "expert_map": layer.ep.config.expert_map if distributed else "local",
                    "dedup_dispatch": bool(distributed and layer.ep.config.dedup),
                    "presum_return": bool(distributed and layer.ep.config.presum),
+                   "dispatch_transport": (layer.ep.config.transport if distributed else None),
                    "rows_per_rank": per_rank_rows, "weights": "block-FP8 e4m3 128x128, random N(0,0.02)",
                    "activations": "e4m3 1x128 blocks", "weight_grads": "bf16 operands, fp32 sums, bf16 out",
                    "l2": "inputs exceed L2 (no flush needed)" if T * D * 2 > (126 << 20) else "inputs fit L2"},

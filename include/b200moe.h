@@ -361,6 +361,22 @@ int b200moe_grouped_gemm_bf16(const void* a, long long lda, const void* b, void*
                               long long rows_total, int N, int K, int b_mn_major, int32_t* status, void* stream);
 
 /*
+ * Expert-parallel dispatch as one kernel: gather + transfer over NVLink peer memory.  Send row i
+ * is the bf16 row src[gather[i]]; send rows [send_start[r], send_start[r+1]) belong to rank r and
+ * are written, in order, from row dest_row0[r] of dest[r] on: dest[r] is rank r's receive arena as
+ * mapped into THIS process (symmetric / peer memory; r == own rank: a local pointer).  Plain
+ * 16-byte stores; the kernel waits for nobody.  The caller orders the ranks afterwards (any
+ * collective on the same stream) before an arena is read, and before one is written again.
+ * world <= 16.  (No reference counterpart: the reference's transport is MoonEP, a third-party
+ * library, src/mlops/expert_parallel/quack/communication.py; its plan -- send once per
+ * destination rank, receive grouped by source -- is the same.)
+ */
+int b200moe_peer_dispatch_rows(const void* src, long long lds, long long src_rows, const int32_t* gather,
+                               long long rows, int width, void* const* dest, long long ldd, long long dest_rows,
+                               const int32_t* send_start, const long long* dest_row0, int world, int32_t* status,
+                               void* stream);
+
+/*
  * E4M3 rows of x [rows, width] (bf16, token-major) with ONE SCALE PER (GROUP, COLUMN):
  *   scales[g, c] = max(max over the rows of group g of |x[r, c]| * fp32(1/448), 1e-12)
  *   q[r, c]      = e4m3_rn(clamp(x[r, c] / scales[g(r), c], -448, 448))     (RN division)

@@ -72,6 +72,41 @@ gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, long lo
     *reinterpret_cast<uint4*>(dst + r * ldd + c) = *reinterpret_cast<const uint4*>(src + s * lds + c);
 }
 
+// The dispatch of an expert-parallel layer as ONE kernel: gather + transfer.  Send row i is the
+// bf16 row src[gather[i]]; the send rows are grouped by destination rank (send_start), and row i
+// of the group for rank r is written straight into r's receive arena over NVLink (plain 16-byte
+// stores through a peer mapping of that GPU's memory: no send buffer, no copy engine, no
+// library collective).  Nothing in here waits for another GPU: the ranks meet afterwards, on the
+// host side's collective, before anyone reads its arena.
+constexpr int kPeerMaxRanks = 16;
+struct PeerDispatchParams {
+  __nv_bfloat16* dest[kPeerMaxRanks];  // base of every rank's arena slot, as mapped on THIS GPU
+  int send_start[kPeerMaxRanks + 1];   // send rows [send_start[r], send_start[r+1]) go to rank r
+  long long dest_row0[kPeerMaxRanks];  // first arena row at rank r that belongs to this sender
+  long long dest_rows;                 // rows of an arena slot (bound of every destination row)
+  int world;
+};
+
+__global__ void __launch_bounds__(256)
+peer_dispatch_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, long long src_rows,
+                          const int* __restrict__ gather, long long rows, int D, long long ldd,
+                          const PeerDispatchParams pp, int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long i = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= rows) return;
+  int r = 0;
+  while (r + 1 < pp.world && i >= pp.send_start[r + 1]) ++r;
+  long long s = gather[i];
+  const long long d = pp.dest_row0[r] + (i - pp.send_start[r]);
+  if (s < 0 || s >= src_rows || d < 0 || d >= pp.dest_rows) {  // reported; nothing is read or written out of bounds
+    if (lane == 0) report_error(status, ERR_BAD_OFFSETS, 26, (int)i);
+    return;
+  }
+  __nv_bfloat16* dst = pp.dest[r] + d * ldd;
+  for (int c = lane * 8; c < D; c += 256)
+    *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + s * lds + c);
+}
+
 // out[t, k] = values[slots[t, k]]: a per-sorted-row scalar brought back to assignment order.
 __global__ void gather_scalar_kernel(const float* __restrict__ values, long long n_values,
                                      const int* __restrict__ slots, long long n, float* __restrict__ out,
@@ -150,6 +185,38 @@ extern "C" int b200moe_gather_rows(const void* src, long long lds, long long src
   gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(src), lds, src_rows, gather, gather_div, rows, width,
       reinterpret_cast<__nv_bfloat16*>(dst), ldd, status);
+  return launch_status();
+}
+
+// Fused gather + transfer of an expert-parallel dispatch (see peer_dispatch_rows_kernel).
+// `dest[r]`: the arena slot of rank r as mapped into this process (r == own rank: the local
+// arena); `send_start` has world + 1 entries; `dest_row0[r]`: where this sender's rows start in
+// r's slot; every destination row is bounded by `dest_rows`.  All pointers are bf16 rows of
+// `width` elements with pitch `ldd` (destination) / `lds` (source).
+extern "C" int b200moe_peer_dispatch_rows(const void* src, long long lds, long long src_rows,
+                                          const int32_t* gather, long long rows, int width,
+                                          void* const* dest, long long ldd, long long dest_rows,
+                                          const int32_t* send_start, const long long* dest_row0, int world,
+                                          int32_t* status, void* stream) {
+  if (!src || !gather || !dest || !send_start || !dest_row0 || !status || rows < 0 || width <= 0 || world <= 0)
+    return B200MOE_ERR_ARG;
+  if (world > kPeerMaxRanks) return B200MOE_ERR_LIMIT;
+  if ((width % 8) || (lds % 8) || (ldd % 8) || ((uintptr_t)src & 15)) return B200MOE_ERR_ALIGN;
+  PeerDispatchParams pp;
+  for (int r = 0; r < kPeerMaxRanks; ++r) {
+    pp.dest[r] = r < world ? reinterpret_cast<__nv_bfloat16*>(dest[r]) : nullptr;
+    pp.dest_row0[r] = r < world ? dest_row0[r] : 0;
+    if (r < world && (!dest[r] || ((uintptr_t)dest[r] & 15))) return B200MOE_ERR_ALIGN;
+  }
+  for (int r = 0; r <= kPeerMaxRanks; ++r) pp.send_start[r] = send_start[r < world ? r : world];
+  if (pp.send_start[0] != 0 || pp.send_start[world] != rows) return B200MOE_ERR_ARG;
+  for (int r = 0; r < world; ++r)
+    if (pp.send_start[r + 1] < pp.send_start[r]) return B200MOE_ERR_ARG;
+  pp.dest_rows = dest_rows;
+  pp.world = world;
+  if (rows == 0) return B200MOE_OK;
+  peer_dispatch_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(src), lds, src_rows, gather, rows, width, ldd, pp, status);
   return launch_status();
 }
 

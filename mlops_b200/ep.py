@@ -54,8 +54,19 @@ class ExpertParallelConfig:
     # token's experts sit on half as many ranks as it has experts; the output then carries one
     # more bf16 rounding than the single-GPU layer (which sums all K rows before rounding).
     presum: bool = False
+    # with `dedup`: how the token rows travel. "nccl": gathered into a send buffer, then an
+    # all-to-all. "peer": ONE kernel per rank gathers the rows and writes them straight into the
+    # destinations' receive arenas in NVLink peer memory (mlops_b200/peer.py); the small per-copy
+    # metadata and the returns stay on the library all-to-all.
+    transport: str = "nccl"
 
     def validate(self, world: int) -> None:
+        if self.transport not in ("nccl", "peer"):
+            raise ValueError(f"unknown transport {self.transport!r}")
+        if self.transport == "peer" and not self.dedup:
+            raise ValueError("the peer transport carries the de-duplicated dispatch: it needs dedup")
+        if self.transport == "peer" and world > 16:
+            raise ValueError("the peer transport serves at most 16 ranks")
         if self.experts % world:
             raise ValueError(f"experts ({self.experts}) must divide evenly over {world} ranks")
         if world > 128 or self.top_k > 32:
@@ -101,6 +112,7 @@ class ExchangePlan:
     # de-duplicated dispatch: token copies instead of rows (None when not used)
     send_copies: list[int] | None = None
     recv_copies: list[int] | None = None
+    recv_copies_device: torch.Tensor | None = None  # the same counts as an int64 device tensor
 
 
 def copy_mask(keys: torch.Tensor, world: int, local: int) -> torch.Tensor:
@@ -181,6 +193,7 @@ def make_plans(send_counts: torch.Tensor, group, copy_counts: torch.Tensor | Non
         plan = ExchangePlan(send_splits, recv_splits, offsets, int(sum(recv_splits)), int(sum(send_splits)))
         if copy_counts is not None:
             plan.send_copies, plan.recv_copies = sizes[2, :, c].tolist(), sizes[3, :, c].tolist()
+            plan.recv_copies_device = theirs[:, c, local].contiguous()
         plans.append(plan)
     return plans
 
@@ -291,6 +304,7 @@ class ExpertParallelMoE:
                              b2t=b2.transpose(1, 2).contiguous(), scale=float(lora["scale"]), rank=rank)
         self.keys = placement(config, self.world, self.device)
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        self.arena = None  # receive arenas in peer memory, created at the first step that needs them
         self.bytes_moved = 0
         self.last_recv_rows = 0
         self.profile = False  # when set, phase boundaries are marked with CUDA events
@@ -338,6 +352,20 @@ class ExpertParallelMoE:
         return [(b[0], a[1].elapsed_time(b[1])) for a, b in zip(marks, marks[1:])]
 
     # ----------------------------------------------------------------------- forward
+    def _peer_arena(self, rows_per_peer: int, width: int):
+        """The arena of the peer transport (collective when it has to be created or grown: every
+        rank calls this at the same step with its own chunk size, and the largest one decides)."""
+        from .peer import PeerArena
+
+        if self.arena is not None and self.arena.fits(rows_per_peer, width):
+            return self.arena
+        need = torch.tensor([rows_per_peer], dtype=torch.int64, device=self.device)
+        dist.all_reduce(need, op=dist.ReduceOp.MAX, group=self.group)
+        if self.arena is not None:
+            self.arena.close()
+        self.arena = PeerArena(self.group, self.device, int(need.item()), width)
+        return self.arena
+
     def forward(self, x, residual=None, expert_ids=None, routing_weights=None):
         """Tokens are processed in `self.chunks` contiguous chunks: the dispatch of chunk c+1
         and the return of chunk c are in flight while chunk c's expert GEMMs run."""
@@ -400,6 +428,10 @@ class ExpertParallelMoE:
             regroup = [regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
                                      plans[c].recv_rows) for c in range(chunks)]
 
+            arena = None
+            if dedup and cfg.transport == "peer":
+                arena = self._peer_arena(max(b - a for a, b in zip(bounds[:-1], bounds[1:])), width)
+
             def send(c):
                 part = parts[c]
                 lo, hi = part["lo"], part["hi"]
@@ -410,12 +442,20 @@ class ExpertParallelMoE:
                         part["mask"], keys[lo:hi], weights[lo:hi], self.local_experts,
                         int(sum(plans[c].send_copies)))
                     part["copy_token"], part["token_copies"] = token, token_copies
-                    rows = ops.dispatch(flat[lo:hi], token, 1)
                     meta = torch.cat([copy_ids, copy_w.view(torch.int32)], dim=1)
-                    got_rows, wx = exchange(rows, plans[c], self.group, async_op=True, copies=True)
+                    if arena is not None:
+                        # gather + transfer in one kernel, straight into the peers' arenas
+                        wx = arena.dispatch(flat[lo:hi], token, plans[c].send_copies)
+                        rows, got_rows = None, wx.rows
+                        part["arena_rows"] = arena.received_index(plans[c].recv_copies_device,
+                                                                  int(sum(plans[c].recv_copies)))
+                        self.bytes_moved += token.numel() * width * 2
+                    else:
+                        rows = ops.dispatch(flat[lo:hi], token, 1)
+                        got_rows, wx = exchange(rows, plans[c], self.group, async_op=True, copies=True)
+                        self.bytes_moved += rows.numel() * 2
                     got_meta, ww = exchange(meta, plans[c], self.group, async_op=True, copies=True)
                     part["recv_copies"], part["recv_meta"] = got_rows, got_meta
-                    self.bytes_moved += rows.numel() * 2
                     return rows, meta, wx, ww
                 rows = ops.dispatch(flat[lo:hi], part["order"], cfg.top_k)
                 row_weights = weights[lo:hi].reshape(-1)[part["order"].long()].contiguous()
@@ -463,7 +503,13 @@ class ExpertParallelMoE:
                         copy_rows[pick.long()] = torch.arange(pick.numel(), dtype=torch.int32, device=flat.device)
                         part["copy_rows"] = copy_rows.view(copies_here, cfg.top_k)
                         part["copy_weights"] = meta[:, cfg.top_k:].contiguous().view(torch.float32)
-                    x_q, x_s, _ = ops.quantize_rows(part.pop("recv_copies"), gather=pick, gather_div=cfg.top_k,
+                    gather = pick
+                    if arena is not None:
+                        # the copies sit in one fixed segment per source rank: name them by arena row
+                        copy, slot = torch.div(pick, cfg.top_k, rounding_mode="floor"), pick % cfg.top_k
+                        gather = (part.pop("arena_rows")[copy.long()] * cfg.top_k + slot).to(torch.int32)
+                        part["arena_pick"] = gather
+                    x_q, x_s, _ = ops.quantize_rows(part.pop("recv_copies"), gather=gather, gather_div=cfg.top_k,
                                                     copy_out=x_rows[rows])
                     row_w[rows] = meta[:, cfg.top_k:].contiguous().view(torch.float32).reshape(-1)[pick.long()]
                 else:
@@ -543,6 +589,11 @@ class ExpertParallelMoE:
 
             def send(c):
                 part = parts[c]
+                if dedup and "arena_pick" in part:  # the same copies, the same way as in the forward pass
+                    work = self.arena.dispatch(dy[part["lo"]:part["hi"]], part["copy_token"], plans[c].send_copies)
+                    part["recv_dy_copies"] = work.rows
+                    self.bytes_moved += part["copy_token"].numel() * width * 2
+                    return None, work
                 if dedup:  # the same copies as in the forward pass
                     rows = ops.dispatch(dy[part["lo"]:part["hi"]], part["copy_token"], 1)
                     part["recv_dy_copies"], work = exchange(rows, plans[c], self.group, async_op=True, copies=True)
@@ -580,7 +631,8 @@ class ExpertParallelMoE:
                 identity = torch.arange(count, dtype=torch.int32, device=flat.device)
                 offsets, source = regroup[c]
                 if dedup:
-                    arrived, gather, div = parts[c].pop("recv_dy_copies"), parts[c]["pick"], cfg.top_k
+                    arrived, div = parts[c].pop("recv_dy_copies"), cfg.top_k
+                    gather = parts[c].get("arena_pick", parts[c]["pick"])
                 else:
                     arrived, gather, div = recv_dy[rows], source, 1
                 if keep_rows:
@@ -678,12 +730,15 @@ class ExpertParallelMoE:
             from . import ops
 
             ops.set_cta_limit(0)
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
         self.side_stream = None
 
 
 def parity_check(group, device, *, routing_mode="softmax_then_topk", n_group=1, topk_group=1,
-                 routed_scaling=1.0, shared=False, presum=False, tokens=384, width=512, inner=256,
-                 experts_per_rank=4, seed=5) -> dict:
+                 routed_scaling=1.0, shared=False, presum=False, transport="nccl", tokens=384, width=512,
+                 inner=256, experts_per_rank=4, seed=5) -> dict:
     """The expert-parallel layer against the single-GPU layer on the gathered weights, on a
     small case with this group's world size: every rank builds the same global experts, keeps
     its shard, runs `ExpertParallelMoE` on its own tokens and `layer.forward_routed /
@@ -722,7 +777,8 @@ def parity_check(group, device, *, routing_mode="softmax_then_topk", n_group=1, 
     config = ExpertParallelConfig(hidden=width, experts=experts, intermediate=inner, top_k=top_k,
                                   routing_mode=routing_mode, n_group=n_group, topk_group=topk_group,
                                   routed_scaling=routed_scaling, expert_map="contiguous" if dedup else "strided",
-                                  dedup=dedup, presum=bool(presum and dedup))
+                                  dedup=dedup, presum=bool(presum and dedup),
+                                  transport=transport if dedup else "nccl")
     keys = placement(config, world)
     mine = sorted((e for e in range(experts) if int(keys[e]) // experts_per_rank == rank), key=lambda e: int(keys[e]))
     pick = torch.tensor(mine, device=device)
@@ -758,6 +814,7 @@ def parity_check(group, device, *, routing_mode="softmax_then_topk", n_group=1, 
 
     result = {"world": world, "experts": experts, "top_k": top_k, "tokens_per_rank": tokens,
               "routing": routing_mode, "dedup_dispatch": dedup, "presum_return": config.presum,
+              "transport": config.transport,
               "counts_equal": bool(torch.equal(counts, ref[2])),
               "output_bit_equal": bool(torch.equal(output, ref[0])),
               "output_max_rel": max_rel(output, ref[0]),

@@ -664,6 +664,35 @@ def grouped_gemm_bf16(a, b, offsets, *, b_mn_major=False, addend=None):
     return out
 
 
+def peer_dispatch_rows(src, gather, dest_ptrs, dest_pitch, dest_rows, send_start, dest_row0, *, stream=None):
+    """Gather + transfer of an expert-parallel dispatch in one kernel: send row i is
+    `src[gather[i]]` (bf16); rows `[send_start[r], send_start[r+1])` go, in order, to rows
+    `dest_row0[r]...` of the arena at `dest_ptrs[r]` (device addresses valid in this process: the
+    peers' symmetric-memory buffers). Plain stores over NVLink; the caller orders the ranks
+    afterwards. `stream`: the torch stream to launch on (default: the current one)."""
+    import ctypes
+
+    device = _need_cuda(src, gather)
+    if src.dtype != torch.bfloat16 or src.stride(1) != 1 or gather.dtype != torch.int32:
+        raise NativeError("src must be bf16 rows with unit inner stride, gather int32")
+    world = len(dest_ptrs)
+    rows = gather.numel()
+    if len(send_start) != world + 1 or len(dest_row0) != world:
+        raise NativeError("send_start needs world + 1 entries and dest_row0 world entries")
+    ptrs = (ctypes.c_void_p * world)(*[int(p) for p in dest_ptrs])
+    starts = (ctypes.c_int32 * (world + 1))(*[int(v) for v in send_start])
+    row0 = (ctypes.c_longlong * world)(*[int(v) for v in dest_row0])
+    with torch.cuda.device(device):
+        launch_stream = (torch.cuda.current_stream() if stream is None else stream).cuda_stream
+        check(
+            lib.b200moe_peer_dispatch_rows(src.data_ptr(), src.stride(0), src.shape[0], gather.data_ptr(), rows,
+                                           src.shape[1], ptrs, int(dest_pitch), int(dest_rows), starts, row0, world,
+                                           status_block(device).data_ptr(), launch_stream),
+            "peer_dispatch_rows",
+        )
+    _count()
+
+
 @_on_tensor_device
 def quantize_columns(x, offsets, groups):
     """Column-scaled E4M3 of bf16 rows `x [rows, width]`: one scale per (group, column) over the

@@ -23,12 +23,19 @@ def main():
         dict(routing_mode="sigmoid_noaux_tc", n_group=2, topk_group=1, routed_scaling=2.5, shared=True, presum=True),
         dict(routing_mode="sigmoid_noaux_tc", n_group=2, topk_group=1, routed_scaling=2.5, shared=True, presum=False),
         dict(routing_mode="softmax_then_topk", shared=False),
+        # the token rows written straight into the peers' arenas by this library's kernel (NVLink
+        # peer memory) instead of the library all-to-all: the same results, bit for bit without presum
+        dict(routing_mode="sigmoid_noaux_tc", n_group=2, topk_group=1, routed_scaling=2.5, shared=True, presum=False,
+             transport="peer"),
+        dict(routing_mode="sigmoid_noaux_tc", n_group=2, topk_group=1, routed_scaling=2.5, shared=True, presum=True,
+             transport="peer"),
     )
     for case in cases:
         result = ep.parity_check(dist.group.WORLD, device, **case)
         if dist.get_rank() == 0:
             print("ep check ok:", result)
         assert result["presum_return"] == bool(case.get("presum")) and (result["output_bit_equal"] or case.get("presum"))
+        assert result["transport"] == case.get("transport", "nccl")
     dist.barrier()
     if dist.get_rank() == 0:
         print("ep check worker ok")
