@@ -377,6 +377,18 @@ int b200moe_peer_dispatch_rows(const void* src, long long lds, long long src_row
                                void* stream);
 
 /*
+ * The sender's plan of a de-duplicated expert-parallel dispatch, in one launch: one copy of a token
+ * per rank holding at least one of its experts (rank = keys[t, k] / local), ordered by rank, then
+ * token.  copy_start (HOST array, world + 1 entries): where each rank's copies begin.  Outputs:
+ * token_of [copies], meta [copies, 2 * top_k] = [local expert id or -1 | route weight bits or 0],
+ * token_copies [tokens, world] = position of the token's copy for each rank or -1.
+ * Reference: src/mlops/expert_parallel/quack/runtime.py:93-108 (the dispatch plan, "dedup").
+ */
+int b200moe_build_copies(const int32_t* keys, const float* weights, int tokens, int top_k, int world, int local,
+                         const int32_t* copy_start, int32_t* token_of, int32_t* meta, int32_t* token_copies,
+                         int32_t* status, void* stream);
+
+/*
  * E4M3 rows of x [rows, width] (bf16, token-major) with ONE SCALE PER (GROUP, COLUMN):
  *   scales[g, c] = max(max over the rows of group g of |x[r, c]| * fp32(1/448), 1e-12)
  *   q[r, c]      = e4m3_rn(clamp(x[r, c] / scales[g(r), c], -448, 448))     (RN division)

@@ -75,6 +75,7 @@ SIGNATURES = {
     "b200moe_combine": (I, [P, LL, LL, P, P, P, LL, P, LL, LL, I, I, P]),
     "b200moe_gather_rows": (I, [P, LL, LL, P, I, LL, I, P, LL, P, P]),
     "b200moe_peer_dispatch_rows": (I, [P, LL, LL, P, LL, I, P, LL, LL, P, P, I, P, P]),
+    "b200moe_build_copies": (I, [P, P, I, I, I, I, P, P, P, P, P, P]),
     "b200moe_gather_scalar": (I, [P, LL, P, LL, P, P, P]),
 }
 

@@ -5,6 +5,8 @@
 #include "common.cuh"
 #include "host_util.h"
 
+#include <stdlib.h>
+
 namespace b200 {
 
 constexpr int kCombineThreads = 128;
@@ -87,24 +89,106 @@ struct PeerDispatchParams {
   int world;
 };
 
-__global__ void __launch_bounds__(256)
+constexpr int kPeerWarps = 16;  // rows in flight per CTA
+__global__ void __launch_bounds__(kPeerWarps * 32)
 peer_dispatch_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, long long src_rows,
                           const int* __restrict__ gather, long long rows, int D, long long ldd,
                           const PeerDispatchParams pp, int* status) {
   const int lane = threadIdx.x & 31;
-  const long long i = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (i >= rows) return;
-  int r = 0;
-  while (r + 1 < pp.world && i >= pp.send_start[r + 1]) ++r;
-  long long s = gather[i];
-  const long long d = pp.dest_row0[r] + (i - pp.send_start[r]);
-  if (s < 0 || s >= src_rows || d < 0 || d >= pp.dest_rows) {  // reported; nothing is read or written out of bounds
-    if (lane == 0) report_error(status, ERR_BAD_OFFSETS, 26, (int)i);
-    return;
+  // a few resident CTAs walk all rows (like a collective's kernel, this one runs beside the GEMMs
+  // of the previous chunk and must leave them their SMs)
+  for (long long i = (long long)blockIdx.x * kPeerWarps + (threadIdx.x >> 5); i < rows;
+       i += (long long)gridDim.x * kPeerWarps) {
+    int r = 0;
+    while (r + 1 < pp.world && i >= pp.send_start[r + 1]) ++r;
+    const long long s = gather[i];
+    const long long d = pp.dest_row0[r] + (i - pp.send_start[r]);
+    if (s < 0 || s >= src_rows || d < 0 || d >= pp.dest_rows) {  // reported; nothing is read or written out of bounds
+      if (lane == 0) report_error(status, ERR_BAD_OFFSETS, 26, (int)i);
+      continue;
+    }
+    __nv_bfloat16* dst = pp.dest[r] + d * ldd;
+    const __nv_bfloat16* from = src + s * lds;
+    int c = lane * 8;
+    for (; c + 768 < D; c += 1024) {  // four 16-byte loads in flight per lane
+      const uint4 v0 = *reinterpret_cast<const uint4*>(from + c), v1 = *reinterpret_cast<const uint4*>(from + c + 256);
+      const uint4 v2 = *reinterpret_cast<const uint4*>(from + c + 512), v3 = *reinterpret_cast<const uint4*>(from + c + 768);
+      *reinterpret_cast<uint4*>(dst + c) = v0;
+      *reinterpret_cast<uint4*>(dst + c + 256) = v1;
+      *reinterpret_cast<uint4*>(dst + c + 512) = v2;
+      *reinterpret_cast<uint4*>(dst + c + 768) = v3;
+    }
+    for (; c < D; c += 256) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(from + c);
   }
-  __nv_bfloat16* dst = pp.dest[r] + d * ldd;
-  for (int c = lane * 8; c < D; c += 256)
-    *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + s * lds + c);
+}
+
+// The sender's plan of a de-duplicated expert-parallel dispatch in one launch.  One copy of a token
+// per rank that holds at least one of its K experts (rank = key / local), ordered by rank, then
+// token.  Block r scans the tokens for rank r (copy_start[r] is where its copies begin) and writes
+// for each copy: its token, and the metadata row [K local expert ids (-1: that assignment lives on
+// another rank) | K route weights (fp32 bits; 0 for those)]; and for every (token, rank) the copy's
+// position or -1.
+struct CopyPlanParams {
+  int copy_start[kPeerMaxRanks * 8 + 1];  // up to 128 ranks
+};
+__global__ void __launch_bounds__(1024)
+build_copies_kernel(const int* __restrict__ keys, const float* __restrict__ weights, int tokens, int K, int world,
+                    int local, const CopyPlanParams cp, int* __restrict__ token_of, int* __restrict__ meta,
+                    int* __restrict__ token_copies, int* status) {
+  __shared__ int warp_sums[32];
+  __shared__ int running_s;
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) running_s = cp.copy_start[r];
+  __syncthreads();
+  for (int base = 0; base < tokens; base += 1024) {
+    const int t = base + tid;
+    int has = 0;
+    if (t < tokens) {
+      for (int k = 0; k < K; ++k) {
+        const int key = keys[(long long)t * K + k];
+        has |= (key >= 0 && key / local == r) ? 1 : 0;
+      }
+    }
+    // exclusive scan of `has` over the block
+    int incl = has;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += v;
+      }
+      warp_sums[lane] = w;  // inclusive over warps
+    }
+    __syncthreads();
+    const int before = running_s + (warp ? warp_sums[warp - 1] : 0) + incl - has;
+    const int block_total = warp_sums[31];
+    if (t < tokens) {
+      if (has && before < cp.copy_start[r + 1]) {
+        token_of[before] = t;
+        for (int k = 0; k < K; ++k) {
+          const int key = keys[(long long)t * K + k];
+          const bool here = key >= 0 && key / local == r;
+          meta[(long long)before * 2 * K + k] = here ? key - r * local : -1;
+          meta[(long long)before * 2 * K + K + k] = here ? __float_as_int(weights[(long long)t * K + k]) : 0;
+        }
+        token_copies[(long long)t * world + r] = before;
+      } else {
+        token_copies[(long long)t * world + r] = -1;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) running_s += block_total;
+    __syncthreads();
+  }
+  if (tid == 0 && running_s != cp.copy_start[r + 1]) report_error(status, ERR_BAD_OFFSETS, 27, r);  // plan and keys disagree
 }
 
 // out[t, k] = values[slots[t, k]]: a per-sorted-row scalar brought back to assignment order.
@@ -215,8 +299,32 @@ extern "C" int b200moe_peer_dispatch_rows(const void* src, long long lds, long l
   pp.dest_rows = dest_rows;
   pp.world = world;
   if (rows == 0) return B200MOE_OK;
-  peer_dispatch_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  // at most `B200MOE_PEER_CTAS` CTAs (default 64) so the kernel can run beside the expert GEMMs
+  static const int cta_cap = [] {
+    const char* v = getenv("B200MOE_PEER_CTAS");
+    const int n = v ? atoi(v) : 64;
+    return n > 0 ? n : 64;
+  }();
+  long long blocks = (rows + kPeerWarps - 1) / kPeerWarps;
+  if (blocks > cta_cap) blocks = cta_cap;
+  peer_dispatch_rows_kernel<<<(unsigned)blocks, kPeerWarps * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(src), lds, src_rows, gather, rows, width, ldd, pp, status);
+  return launch_status();
+}
+
+// The sender's plan of a de-duplicated dispatch (see build_copies_kernel).  `copy_start` (host,
+// world + 1 entries): where each rank's copies begin; copy_start[world] copies in all.
+extern "C" int b200moe_build_copies(const int32_t* keys, const float* weights, int tokens, int top_k, int world,
+                                    int local, const int32_t* copy_start, int32_t* token_of, int32_t* meta,
+                                    int32_t* token_copies, int32_t* status, void* stream) {
+  if (!keys || !weights || !copy_start || !token_of || !meta || !token_copies || !status) return B200MOE_ERR_ARG;
+  if (tokens < 0 || top_k <= 0 || world <= 0 || local <= 0) return B200MOE_ERR_ARG;
+  if (world > kPeerMaxRanks * 8) return B200MOE_ERR_LIMIT;
+  CopyPlanParams cp;
+  for (int r = 0; r <= kPeerMaxRanks * 8; ++r) cp.copy_start[r] = copy_start[r < world ? r : world];
+  if (tokens == 0) return B200MOE_OK;
+  build_copies_kernel<<<(unsigned)world, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      keys, weights, tokens, top_k, world, local, cp, token_of, meta, token_copies, status);
   return launch_status();
 }
 

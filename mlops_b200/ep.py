@@ -147,7 +147,7 @@ def build_copies(mask: torch.Tensor, keys: torch.Tensor, weights: torch.Tensor, 
     return token_of.to(torch.int32), ids.contiguous(), route_weight.contiguous(), token_copies
 
 
-def expand_copies(ids: torch.Tensor, recv_copies, local: int, rows: int, sort=None):
+def expand_copies(ids: torch.Tensor, recv_copies, local: int, rows: int, sort=None, counts_device=None):
     """The receiver's side: `ids [copies, K]` (local expert or -1) of the copies received from
     each rank (`recv_copies[s]` of them from rank s, in token order). Returns `(assignment
     [rows] int32, segment_offsets int32 [world * local + 1])`: the received assignments as
@@ -159,8 +159,10 @@ def expand_copies(ids: torch.Tensor, recv_copies, local: int, rows: int, sort=No
         sort = ops.sort_assignments
     world = len(recv_copies)
     device = ids.device
-    source = torch.repeat_interleave(torch.arange(world, device=device),
-                                     torch.tensor(recv_copies, device=device), output_size=ids.shape[0])
+    # (the counts as a device tensor, when the plan kept them: a host list would have to be copied
+    # to the device, and a pageable copy waits for the stream)
+    counts = counts_device if counts_device is not None else torch.tensor(recv_copies, device=device)
+    source = torch.repeat_interleave(torch.arange(world, device=device), counts, output_size=ids.shape[0])
     # assignments that live on another rank sort behind every real (source, expert) group
     key = torch.where(ids >= 0, source[:, None] * local + ids.long(), world * local).to(torch.int32)
     order, offsets, _slots, _counts = sort(key.contiguous(), world * local + 1)
@@ -425,8 +427,7 @@ class ExpertParallelMoE:
             if lora is not None:  # x A13^T and act A2^T of every row: the factor gradients need them
                 t1 = torch.empty((total, lora["a13"].shape[1]), dtype=torch.bfloat16, device=flat.device)
                 t2 = torch.empty_like(t1)
-            regroup = [regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
-                                     plans[c].recv_rows) for c in range(chunks)]
+            regroup = [None] * chunks  # filled per chunk while its rows are in flight
 
             arena = None
             if dedup and cfg.transport == "peer":
@@ -438,11 +439,18 @@ class ExpertParallelMoE:
                 if dedup:
                     # one copy of a token per destination rank, and what to do with it there:
                     # K (local expert or -1, route weight) pairs, the weights as raw bits
-                    token, copy_ids, copy_w, token_copies = build_copies(
-                        part["mask"], keys[lo:hi], weights[lo:hi], self.local_experts,
-                        int(sum(plans[c].send_copies)))
+                    if flat.is_cuda:  # one launch
+                        token, meta, token_copies = ops.build_copies(
+                            keys[lo:hi].to(torch.int32).contiguous(), weights[lo:hi].contiguous(), self.world,
+                            self.local_experts, plans[c].send_copies)
+                    else:
+                        token, copy_ids, copy_w, token_copies = build_copies(
+                            part["mask"], keys[lo:hi], weights[lo:hi], self.local_experts,
+                            int(sum(plans[c].send_copies)))
+                        meta = torch.cat([copy_ids, copy_w.view(torch.int32)], dim=1)
                     part["copy_token"], part["token_copies"] = token, token_copies
-                    meta = torch.cat([copy_ids, copy_w.view(torch.int32)], dim=1)
+                    if c == 0:
+                        self._mark("first copies built")
                     if arena is not None:
                         # gather + transfer in one kernel, straight into the peers' arenas
                         wx = arena.dispatch(flat[lo:hi], token, plans[c].send_copies)
@@ -466,6 +474,7 @@ class ExpertParallelMoE:
                 return rows, row_weights, wx, ww
 
             in_flight = send(0)
+            self._mark("first dispatch issued")
             shared_h13 = None
             if self.shared is not None:  # overlaps the first dispatch
                 side = self.side_stream
@@ -479,6 +488,8 @@ class ExpertParallelMoE:
             returns = []
             for c in range(chunks):
                 nxt = send(c + 1) if c + 1 < chunks else None
+                regroup[c] = regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
+                                           plans[c].recv_rows)
                 in_flight[2].wait()
                 in_flight[3].wait()
                 in_flight = nxt
@@ -493,7 +504,8 @@ class ExpertParallelMoE:
                     part = parts[c]
                     meta = part.pop("recv_meta")
                     assignment, _segments = expand_copies(meta[:, :cfg.top_k].contiguous(), plans[c].recv_copies,
-                                                          self.local_experts, plans[c].recv_rows)
+                                                          self.local_experts, plans[c].recv_rows,
+                                                          counts_device=plans[c].recv_copies_device)
                     pick = assignment[source.long()].contiguous()  # expert-order row -> copy * K + slot
                     part["pick"] = pick
                     if cfg.presum:

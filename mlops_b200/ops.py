@@ -664,6 +664,36 @@ def grouped_gemm_bf16(a, b, offsets, *, b_mn_major=False, addend=None):
     return out
 
 
+@_on_tensor_device
+def build_copies(keys, weights, world, local, send_copies):
+    """The sender's plan of a de-duplicated dispatch in one launch: `(token [copies] int32, meta
+    [copies, 2K] int32 = [local expert ids or -1 | route-weight bits], token_copies [tokens, world]
+    int32)`. `keys [tokens, K]` int32 placement keys (rank = key // local), `weights [tokens, K]`
+    fp32, `send_copies`: copies per destination rank (host integers, from the plan)."""
+    import ctypes
+
+    device = _need_cuda(keys, weights)
+    if keys.dtype != torch.int32 or weights.dtype != torch.float32 or not keys.is_contiguous() \
+            or not weights.is_contiguous():
+        raise NativeError("keys must be contiguous int32 [tokens, K] and weights contiguous fp32 [tokens, K]")
+    tokens, top_k = keys.shape
+    starts = [0]
+    for v in send_copies:
+        starts.append(starts[-1] + int(v))
+    copies = starts[-1]
+    token = torch.empty(copies, dtype=torch.int32, device=device)
+    meta = torch.empty((copies, 2 * top_k), dtype=torch.int32, device=device)
+    token_copies = torch.empty((tokens, world), dtype=torch.int32, device=device)
+    check(
+        lib.b200moe_build_copies(keys.data_ptr(), weights.data_ptr(), tokens, top_k, world, local,
+                                 (ctypes.c_int32 * (world + 1))(*starts), token.data_ptr(), meta.data_ptr(),
+                                 token_copies.data_ptr(), status_block(device).data_ptr(), _stream()),
+        "build_copies",
+    )
+    _count()
+    return token, meta, token_copies
+
+
 def peer_dispatch_rows(src, gather, dest_ptrs, dest_pitch, dest_rows, send_start, dest_row0, *, stream=None):
     """Gather + transfer of an expert-parallel dispatch in one kernel: send row i is
     `src[gather[i]]` (bf16); rows `[send_start[r], send_start[r+1])` go, in order, to rows

@@ -196,3 +196,24 @@ def test_routing_gradient_kernel_against_the_oracle_at_size(mode, experts, top_k
                                                 experts=experts)
         torch.testing.assert_close(aux.cpu(), aux_ref, rtol=1e-5, atol=1e-6)
         torch.testing.assert_close(psum.cpu(), psum_ref, rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("world,local,top_k,tokens", [(2, 4, 4, 700), (8, 32, 8, 3000), (4, 1, 2, 33)])
+def test_build_copies_kernel_matches_the_host_logic(world, local, top_k, tokens):
+    """The sender's plan of a de-duplicated dispatch as one kernel against the tensor-op form that
+    the CPU (gloo) tests of the expert-parallel layer pin: identical copies, metadata and positions."""
+    from mlops_b200 import ep, ops
+
+    g = torch.Generator().manual_seed(world * 100 + tokens)
+    experts = world * local
+    keys = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(tokens)]).to(torch.int32)
+    weights = torch.rand(tokens, top_k, generator=g)
+    mask = ep.copy_mask(keys, world, local)
+    send_copies = mask.sum(0).tolist()
+    token_ref, ids_ref, w_ref, tc_ref = ep.build_copies(mask, keys, weights, local, int(sum(send_copies)))
+    token, meta, token_copies = ops.build_copies(keys.to(DEV), weights.to(DEV), world, local, send_copies)
+    ops.check_status(DEV)
+    assert torch.equal(token.cpu(), token_ref)
+    assert torch.equal(meta[:, :top_k].cpu(), ids_ref)
+    assert torch.equal(meta[:, top_k:].contiguous().view(torch.float32).cpu(), w_ref)
+    assert torch.equal(token_copies.cpu(), tc_ref)
