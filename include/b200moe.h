@@ -349,16 +349,19 @@ int b200moe_grouped_wgrad_bf16_accumulate(const void* g, long long ldg, const vo
 
 /*
  * bf16 grouped GEMM of the bf16 compute path (fp32 sums in TMEM over the whole K loop):
- *   d[rows of g, 0:N] = a[rows of g, 0:K] @ op(b[g % weights])  (+ addend), rounded once to bf16
+ *   d[rows of g, 0:N] = alpha * a[rows of g, 0:K] @ op(b[g % weights])  (+ addend), rounded once to bf16
  * b_mn_major = 0: b is [weights, N, K] (y = x W^T on the stored nn.Linear weight);
  * b_mn_major = 1: b is [weights, K, N] read along its rows (dx = dy W on the SAME stored weight
- * [out = K, in = N]; no transposed copy).  N, K and the pitches are multiples of 8.
+ * [out = K, in = N]; no transposed copy).  N, K and the pitches are multiples of 8; either may be as
+ * small as 8 (the rank-r products of expert LoRA run on this kernel: the unused part of a tile is
+ * zero-filled by the TMA unit and costs no memory traffic).
  * Reference: src/mlops/kernels/moe_grouped_gemm.py:201-299 (`grouped_mm_forward`,
  * `grouped_mm_dgrad`; CPU form `_native_torch` :185-198).
  */
 int b200moe_grouped_gemm_bf16(const void* a, long long lda, const void* b, void* d, long long ldd,
                               const void* addend, long long ldc, const int32_t* offsets, int groups, int weights,
-                              long long rows_total, int N, int K, int b_mn_major, int32_t* status, void* stream);
+                              long long rows_total, int N, int K, int b_mn_major, float alpha, int32_t* status,
+                              void* stream);
 
 /*
  * Expert-parallel dispatch as one kernel: gather + transfer over NVLink peer memory.  Send row i

@@ -65,7 +65,7 @@ SIGNATURES = {
     "b200moe_finish_combine": (I, [P, LL, P, LL, P, LL, LL, I, P]),
     "b200moe_grouped_wgrad_bf16": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, P, P]),
     "b200moe_grouped_wgrad_bf16_accumulate": (I, [P, LL, P, LL, P, I, I, LL, I, I, P, I, F, P, P]),
-    "b200moe_grouped_gemm_bf16": (I, [P, LL, P, P, LL, P, LL, P, I, I, LL, I, I, I, P, P]),
+    "b200moe_grouped_gemm_bf16": (I, [P, LL, P, P, LL, P, LL, P, I, I, LL, I, I, I, F, P, P]),
     "b200moe_quantize_columns": (I, [P, LL, LL, I, P, I, I, P, LL, P, P]),
     "b200moe_grouped_wgrad_fp8": (I, [P, LL, P, P, LL, P, P, I, I, LL, I, I, P, I, F, I, P, P]),
     "b200moe_set_cta_limit": (I, [I]),

@@ -2,7 +2,7 @@
 // path (weights kept or dequantised in bf16; reference: src/mlops/kernels/moe_grouped_gemm.py:
 // 201-299, `grouped_mm_forward` / `grouped_mm_dgrad`):
 //
-//   D[rows of g, 0:N] = A[rows of g, 0:K] @ op(B[g])        (+ addend), bf16 out, fp32 sums
+//   D[rows of g, 0:N] = alpha * A[rows of g, 0:K] @ op(B[g])  (+ addend), bf16 out, fp32 sums
 //
 // A [rows, K] bf16 is K-major.  B is either [groups, N, K] (K-major: y = x W^T, the stored
 // nn.Linear weight) or [groups, K, N] read MN-major (the SAME stored weight [out=K, in=N] for
@@ -43,6 +43,7 @@ struct GemmBf16Params {
   const int* offsets;
   int groups, N, K, rows_total;
   int weights;  // group g multiplies weight matrix g % weights
+  float alpha;  // d = alpha * (a @ op(b)) + addend
   int* status;
 };
 
@@ -259,7 +260,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         float acc[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) acc[j] = p.alpha * __uint_as_float(r[j]);
         if (p.addend != nullptr && lane < rows_here) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -317,7 +318,7 @@ using namespace b200;
 extern "C" int b200moe_grouped_gemm_bf16(const void* a, long long lda, const void* b, void* d, long long ldd,
                                          const void* addend, long long ldc, const int32_t* offsets, int groups,
                                          int weights, long long rows_total, int N, int K, int b_mn_major,
-                                         int32_t* status, void* stream) {
+                                         float alpha, int32_t* status, void* stream) {
   if (!a || !b || !d || !offsets || !status) return B200MOE_ERR_ARG;
   if (groups <= 0 || weights <= 0 || groups % weights != 0 || N <= 0 || K <= 0 || rows_total < 0) return B200MOE_ERR_ARG;
   if (groups > kBfMaxGroups || rows_total > 0x7fffffffLL) return B200MOE_ERR_LIMIT;
@@ -358,6 +359,7 @@ extern "C" int b200moe_grouped_gemm_bf16(const void* a, long long lda, const voi
   p.K = K;
   p.rows_total = (int)rows_total;
   p.weights = weights;
+  p.alpha = alpha;
   p.status = status;
   // upper bound of the tile count: every group may end in a partial tile
   const long long m_tiles = rows_total / kBfBlockM + groups;

@@ -636,7 +636,7 @@ def grouped_wgrad(g, x, offsets, groups, out_dtype=torch.bfloat16, *, accumulate
 
 
 @_on_tensor_device
-def grouped_gemm_bf16(a, b, offsets, *, b_mn_major=False, addend=None):
+def grouped_gemm_bf16(a, b, offsets, *, b_mn_major=False, addend=None, alpha=1.0):
     """`out[rows_e] = a[rows_e] @ op(b[e])` in bf16 with fp32 sums. `b` is `[E, N, K]` (K-major: the
     stored `nn.Linear` weight, `y = x W^T`) or, with `b_mn_major`, `[E, K, N]` read along its rows
     (`dx = dy W` on the same stored weight). More groups than weights: group g uses `b[g % E]`."""
@@ -656,7 +656,7 @@ def grouped_gemm_bf16(a, b, offsets, *, b_mn_major=False, addend=None):
                 lib.b200moe_grouped_gemm_bf16(
                     a.data_ptr(), a.stride(0), b.data_ptr(), out.data_ptr(), out.stride(0), _ptr(addend),
                     0 if addend is None else addend.stride(0), offsets.data_ptr(), groups, weights, rows, n, k,
-                    1 if b_mn_major else 0, status_block(device).data_ptr(), _stream(),
+                    1 if b_mn_major else 0, float(alpha), status_block(device).data_ptr(), _stream(),
                 ),
                 "grouped_gemm_bf16",
             )
@@ -776,6 +776,11 @@ def grouped_wgrad_fp8(g_q, g_scale, x_q, x_scale, offsets, groups, out_dtype=tor
     return out
 
 
+# B200MOE_LORA_SIMT=1: the rank-r products of expert LoRA on the SIMT kernels (csrc/lora.cu) instead
+# of the tensor-core grouped GEMM
+_LORA_TENSOR_CORES = os.environ.get("B200MOE_LORA_SIMT", "0") != "1"
+
+
 @_on_tensor_device
 def lora_project(x, factor, offsets, *, rank_major):
     """`t [rows, r] = x[row] . factor[expert(row)]`; factor `[E, r, K]` (`rank_major`) or `[E, K, r]`."""
@@ -784,6 +789,11 @@ def lora_project(x, factor, offsets, *, rank_major):
     experts = factor.shape[0]
     rank = factor.shape[1] if rank_major else factor.shape[2]
     factor = factor.contiguous()
+    if _LORA_TENSOR_CORES and rank % 8 == 0 and k % 8 == 0 and x.dtype == torch.bfloat16 and \
+            factor.dtype == torch.bfloat16 and x.stride(1) == 1:
+        # a GEMM with one narrow side: the bf16 grouped GEMM on the tensor cores (the TMA unit
+        # zero-fills the unused part of the tile), memory-bound as it should be
+        return grouped_gemm_bf16(x, factor, offsets, b_mn_major=not rank_major)
     out = torch.empty((rows, rank), dtype=torch.bfloat16, device=device)
     if rows == 0:
         return out
@@ -806,6 +816,9 @@ def lora_expand(t, factor, offsets, *, wide_major, scale=1.0):
     experts = factor.shape[0]
     n = factor.shape[1] if wide_major else factor.shape[2]
     factor = factor.contiguous()
+    if _LORA_TENSOR_CORES and rank % 8 == 0 and n % 8 == 0 and t.dtype == torch.bfloat16 and \
+            factor.dtype == torch.bfloat16 and t.stride(1) == 1:
+        return grouped_gemm_bf16(t, factor, offsets, b_mn_major=not wide_major, alpha=scale)
     out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
     if rows == 0:
         return out

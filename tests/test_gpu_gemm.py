@@ -236,7 +236,10 @@ def test_wgrad_groups_are_isolated_from_a_neighbours_inf_and_nan(m, n):
 @pytest.mark.parametrize(
     "counts,n,k",
     [([128], 256, 64), ([128], 256, 512), ([0, 70, 131, 15, 260], 512, 192), ([0, 70, 131, 15, 260], 320, 456),
-     ([1000, 3, 0, 500], 768, 1024)],
+     ([1000, 3, 0, 500], 768, 1024),
+     # one narrow side: the rank-r products of expert LoRA (project: N = r, expand: K = r)
+     ([0, 70, 131, 15, 260], 16, 456), ([1000, 3, 0, 500], 8, 2048), ([0, 70, 131, 15, 260], 320, 16),
+     ([1000, 3, 0, 500], 1536, 24)],
 )
 def test_grouped_gemm_bf16(counts, n, k, b_mn_major):
     """The bf16 forward / input-gradient product against float64 of the same operands: one rounding
