@@ -84,8 +84,8 @@ def moe_lora_fwd(hidden: torch.Tensor, residual: torch.Tensor, router_weight: to
             logits, top_k, routing_mode, bias=None if router_bias.numel() == 0 else router_bias, n_group=n_group,
             topk_group=topk_group, routed_scaling=routed_scaling)
         order, offsets, slots, counts = ops.sort_assignments(ids, experts)
-        x_rows = ops.dispatch(flat, order, top_k)
-        x_q, x_s = ops.quantize_rows(x_rows)
+        # one pass over the tokens: E4M3 rows for the base product, bf16 rows for the rank-r one
+        x_q, x_s, x_rows = ops.quantize_rows_scatter(flat, slots, with_copy=True)
         t1 = ops.lora_project(x_rows, a13p, offsets, rank_major=True)
         c1 = ops.lora_expand(t1, b13t, offsets, wide_major=False, scale=scale)
         h13 = ops.grouped_gemm_fp8(x_q, x_s, *w13, offsets, addend=c1)
@@ -136,8 +136,7 @@ def _lora_backward(grad_output, grad_aux, grad_probability_sum, hidden, router_w
         counts = (offsets[1:] - offsets[:-1]).long()
         empty = lambda dtype: torch.empty(0, dtype=dtype, device=flat.device)  # noqa: E731
 
-        dy_rows = ops.dispatch(dy, order, top_k)
-        dy_q, dy_s = ops.quantize_rows(dy_rows)
+        dy_q, dy_s, dy_rows = ops.quantize_rows_scatter(dy, slots, with_copy=True)
         t2g = ops.lora_project(dy_rows, b2t, offsets, rank_major=True)              # dy B2      [R, r]
         r_add = ops.lora_expand(t2g, a2p, offsets, wide_major=False, scale=scale)   # s dy B2 A2 [R, F]
         r = ops.grouped_gemm_fp8(dy_q, dy_s, w2_d, w2_s, offsets, b_mn_major=True, addend=r_add)
