@@ -500,7 +500,8 @@ class Layer:
 
 
 def gemm_summary(timings, steps):
-    fp8 = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind in ("fp8", "gemm_bf16")]
+    fp8 = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind == "fp8"]
+    bf16 = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind == "gemm_bf16"]
     wg = [(s.elapsed_time(e), fl) for s, e, kind, fl in timings if kind in ("wgrad_bf16", "wgrad_fp8")]
     fp8_ms, fp8_flops = sum(t for t, _ in fp8), sum(f for _, f in fp8)
     return {
@@ -508,6 +509,9 @@ def gemm_summary(timings, steps):
         "fp8_ms_per_step": fp8_ms / max(steps, 1), "fp8_launches": len(fp8),
         "wgrad_tflops": (sum(f for _, f in wg) / (sum(t for t, _ in wg) * 1e-3) / 1e12) if wg else None,
         "wgrad_ms_per_step": sum(t for t, _ in wg) / max(steps, 1),
+        # the bf16 forward / input-gradient GEMMs (plain bf16 experts) and the rank-r LoRA products
+        "bf16_tflops": (sum(f for _, f in bf16) / (sum(t for t, _ in bf16) * 1e-3) / 1e12) if bf16 else None,
+        "bf16_ms_per_step": sum(t for t, _ in bf16) / max(steps, 1),
     }
 
 
@@ -707,14 +711,16 @@ def extras(device, peaks, fp8_peak):
                  "rows_per_expert_min_max": [int(counts.min()), int(counts.max())], "steps": 3, "warmup": 2}
         if fp8_peak.get("sustained"):
             entry["fp8_frac_of_measured_fp8_sustained"] = (gemms["fp8_tflops"] or 0.0) / fp8_peak["sustained"]
+        if key == "c5":
+            entry["lora_rank_products_ms_per_step"] = gemms["bf16_ms_per_step"]
         if key == "c4_skewed":
             entry["router_bias"] = f"N(0, {SKEWED_BIAS_STD}): skewed load"
         if key == "c3_bf16_experts":
-            entry["compute"] = ("plain bf16 expert weights: bf16 grouped GEMMs, nothing quantised; fp8_gemm_tflops "
-                                "holds the bf16 forward / input-gradient GEMMs here (compare with bf16 peaks)")
-            del entry["fp8_frac_of_2x_bf16_sustained"]
-            entry.pop("fp8_frac_of_measured_fp8_sustained", None)
-            entry["bf16_gemm_frac_of_bf16_sustained"] = (gemms["fp8_tflops"] or 0.0) / peaks["bf16_tflops_sustained"]
+            entry["compute"] = "plain bf16 expert weights: bf16 grouped GEMMs, nothing quantised"
+            for key_ in ("fp8_gemm_tflops", "fp8_frac_of_2x_bf16_sustained", "fp8_frac_of_measured_fp8_sustained"):
+                entry.pop(key_, None)
+            entry["bf16_gemm_tflops"] = gemms["bf16_tflops"]
+            entry["bf16_gemm_frac_of_bf16_sustained"] = (gemms["bf16_tflops"] or 0.0) / peaks["bf16_tflops_sustained"]
         if key == "c4_fp8_weight_gradients":
             entry["weight_grads"] = ("E4M3 operands, one scale per expert and column (quantised per step), fp32 sums; "
                                      "wgrad_tflops counts the GEMMs only, ms_per_step includes the quantisation")
