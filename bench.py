@@ -455,7 +455,9 @@ class Layer:
         presum = dedup and os.environ.get("B200MOE_EP_PRESUM", "1") == "1"
         # the token rows of a de-duplicated dispatch travel by this library's own kernel over NVLink
         # peer memory (B200MOE_EP_TRANSPORT=nccl: through a send buffer and the library all-to-all)
-        transport = os.environ.get("B200MOE_EP_TRANSPORT", "peer") if dedup and self.world <= 16 else "nccl"
+        # (default: on the world sizes it was verified on; B200MOE_EP_TRANSPORT=peer selects it up to 16 ranks)
+        default_transport = "peer" if self.world <= 4 else "nccl"
+        transport = os.environ.get("B200MOE_EP_TRANSPORT", default_transport) if dedup and self.world <= 16 else "nccl"
         self.transport = transport
         lora = None
         if self.factors is not None:
@@ -761,7 +763,8 @@ def gpu_arm(args, cfg):
                                           topk_group=cfg["topk_group"], routed_scaling=cfg["scaling"],
                                           shared=cfg["shared"],
                                           presum=os.environ.get("B200MOE_EP_PRESUM", "1") == "1",
-                                          transport=os.environ.get("B200MOE_EP_TRANSPORT", "peer"))
+                                          transport=os.environ.get("B200MOE_EP_TRANSPORT",
+                                                                   "peer" if world <= 4 else "nccl"))
     if args.workload == "c2":
         peaks, peak_kind = measured_peaks()
         fp8_peak = measure_fp8_peak(device)
