@@ -307,6 +307,8 @@ class ExpertParallelMoE:
         self.keys = placement(config, self.world, self.device)
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.arena = None  # receive arenas in peer memory, created at the first step that needs them
+        # the receiver's per-chunk planning (small tensor ops) runs here, beside the GEMMs
+        self.plan_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.bytes_moved = 0
         self.last_recv_rows = 0
         self.profile = False  # when set, phase boundaries are marked with CUDA events
@@ -485,46 +487,86 @@ class ExpertParallelMoE:
                     base = base + y_shared
                 for tensor in (base, shared_h13):  # produced on the side stream, consumed on this one
                     tensor.record_stream(torch.cuda.current_stream())
-            returns = []
-            for c in range(chunks):
-                nxt = send(c + 1) if c + 1 < chunks else None
-                regroup[c] = regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
-                                           plans[c].recv_rows)
-                in_flight[2].wait()
-                in_flight[3].wait()
-                in_flight = nxt
-                self._mark("dispatch wait")
-                rows = slice(starts[c], starts[c + 1])
-                offsets, source = regroup[c]
-                # expert order from here on: gathered by the quantiser, given back in arrival
-                # order by the down projection's store
-                if dedup:
+
+            def prepare(c, meta_work):
+                """The receiver's plan of chunk c (which received copy feeds which expert-order row, the
+                regroup index, the per-row route weights), computed on the planning stream as soon as
+                the chunk's metadata has arrived: beside the previous chunk's GEMMs, not between them."""
+                part = parts[c]
+                current = torch.cuda.current_stream()
+                side = self.plan_stream
+                side.wait_stream(current)
+                with torch.cuda.stream(side):
+                    meta_work.wait()
+                    meta = part["recv_meta"]
+                    meta.record_stream(side)
+                    offsets, source = regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
+                                                    plans[c].recv_rows)
                     # the copies become this rank's assignments: [source][expert][token] rows as a
                     # row-per-assignment dispatch delivers them, then expert order
-                    part = parts[c]
-                    meta = part.pop("recv_meta")
                     assignment, _segments = expand_copies(meta[:, :cfg.top_k].contiguous(), plans[c].recv_copies,
                                                           self.local_experts, plans[c].recv_rows,
                                                           counts_device=plans[c].recv_copies_device)
                     pick = assignment[source.long()].contiguous()  # expert-order row -> copy * K + slot
-                    part["pick"] = pick
+                    out = dict(offsets=offsets, source=source, pick=pick)
+                    copy_weights = meta[:, cfg.top_k:].contiguous().view(torch.float32)
                     if cfg.presum:
                         # copy_rows[c, k]: the expert-order row of assignment k of copy c (-1: not here)
                         copies_here = meta.shape[0]
                         copy_rows = torch.full((copies_here * cfg.top_k,), -1, dtype=torch.int32, device=flat.device)
                         copy_rows[pick.long()] = torch.arange(pick.numel(), dtype=torch.int32, device=flat.device)
-                        part["copy_rows"] = copy_rows.view(copies_here, cfg.top_k)
-                        part["copy_weights"] = meta[:, cfg.top_k:].contiguous().view(torch.float32)
-                    gather = pick
+                        out["copy_rows"] = copy_rows.view(copies_here, cfg.top_k)
+                        out["copy_weights"] = copy_weights
+                    out["gather"] = pick
                     if arena is not None:
                         # the copies sit in one fixed segment per source rank: name them by arena row
                         copy, slot = torch.div(pick, cfg.top_k, rounding_mode="floor"), pick % cfg.top_k
-                        gather = (part.pop("arena_rows")[copy.long()] * cfg.top_k + slot).to(torch.int32)
-                        part["arena_pick"] = gather
-                    x_q, x_s, _ = ops.quantize_rows(part.pop("recv_copies"), gather=gather, gather_div=cfg.top_k,
-                                                    copy_out=x_rows[rows])
-                    row_w[rows] = meta[:, cfg.top_k:].contiguous().view(torch.float32).reshape(-1)[pick.long()]
+                        arena_rows = part.pop("arena_rows")
+                        arena_rows.record_stream(side)
+                        out["gather"] = (arena_rows[copy.long()] * cfg.top_k + slot).to(torch.int32)
+                    out["row_weights"] = copy_weights.reshape(-1)[pick.long()]
+                    done = torch.cuda.Event()
+                    done.record()
+                for tensor in out.values():
+                    tensor.record_stream(current)
+                return out, done
+
+            prepared = [None] * chunks
+            if dedup:
+                prepared[0] = prepare(0, in_flight[3])
+            returns = []
+            for c in range(chunks):
+                nxt = send(c + 1) if c + 1 < chunks else None
+                if dedup and nxt is not None:
+                    prepared[c + 1] = prepare(c + 1, nxt[3])
+                if not dedup:
+                    regroup[c] = regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
+                                               plans[c].recv_rows)
+                in_flight[2].wait()
+                in_flight[3].wait()
+                in_flight = nxt
+                rows = slice(starts[c], starts[c + 1])
+                # expert order from here on: gathered by the quantiser, given back in arrival
+                # order by the down projection's store
+                if dedup:
+                    part = parts[c]
+                    plan_c, plan_done = prepared[c]
+                    torch.cuda.current_stream().wait_event(plan_done)
+                    self._mark("dispatch wait")
+                    part.pop("recv_meta")
+                    regroup[c] = (plan_c["offsets"], plan_c["source"])
+                    offsets, source = regroup[c]
+                    part["pick"] = plan_c["pick"]
+                    if cfg.presum:
+                        part["copy_rows"], part["copy_weights"] = plan_c["copy_rows"], plan_c["copy_weights"]
+                    if arena is not None:
+                        part["arena_pick"] = plan_c["gather"]
+                    x_q, x_s, _ = ops.quantize_rows(part.pop("recv_copies"), gather=plan_c["gather"],
+                                                    gather_div=cfg.top_k, copy_out=x_rows[rows])
+                    row_w[rows] = plan_c["row_weights"]
                 else:
+                    self._mark("dispatch wait")
+                    offsets, source = regroup[c]
                     x_q, x_s, _ = ops.quantize_rows(recv_x[rows], gather=source, copy_out=x_rows[rows])
                     row_w[rows] = recv_w[rows][source.long()]
                 presum = dedup and cfg.presum  # rows stay in expert order; one weighted row per copy goes back
@@ -745,7 +787,7 @@ class ExpertParallelMoE:
         if self.arena is not None:
             self.arena.close()
             self.arena = None
-        self.side_stream = None
+        self.side_stream = self.plan_stream = None
 
 
 def parity_check(group, device, *, routing_mode="softmax_then_topk", n_group=1, topk_group=1,
