@@ -753,7 +753,10 @@ def gpu_arm(args, cfg):
         os.environ.setdefault("NCCL_MAX_CTAS", str(comm_sms))
         if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
             os.environ["NCCL_DEBUG"] = "WARN"  # keeps NCCL's version banner off stdout: one JSON line only
-        dist.init_process_group("nccl", device_id=device)
+        # the collectives of a step are short and on its critical path: their kernels go ahead of the
+        # GEMMs' CTAs when SMs free up
+        options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=device, pg_options=options)
         group = dist.group.WORLD
         from mlops_b200 import ep as ep_module
 

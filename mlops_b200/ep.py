@@ -308,7 +308,9 @@ class ExpertParallelMoE:
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.arena = None  # receive arenas in peer memory, created at the first step that needs them
         # the receiver's per-chunk planning (small tensor ops) runs here, beside the GEMMs
-        self.plan_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        # (high priority: its kernels are tiny and on the critical path of the next chunk, while the
+        # GEMMs they run beside fill every SM)
+        self.plan_stream = torch.cuda.Stream(device=self.device, priority=-1) if self.device.type == "cuda" else None
         self.bytes_moved = 0
         self.last_recv_rows = 0
         self.profile = False  # when set, phase boundaries are marked with CUDA events
@@ -488,14 +490,16 @@ class ExpertParallelMoE:
                 for tensor in (base, shared_h13):  # produced on the side stream, consumed on this one
                     tensor.record_stream(torch.cuda.current_stream())
 
-            def prepare(c, meta_work):
+            def prepare(c, meta_work, after):
                 """The receiver's plan of chunk c (which received copy feeds which expert-order row, the
                 regroup index, the per-row route weights), computed on the planning stream as soon as
-                the chunk's metadata has arrived: beside the previous chunk's GEMMs, not between them."""
+                the chunk's metadata has arrived: beside the previous chunk's GEMMs, not between them.
+                `after`: an event on the calling stream behind everything the plan reads (the host may
+                queue this plan later than that point, after the launches that are more urgent)."""
                 part = parts[c]
                 current = torch.cuda.current_stream()
                 side = self.plan_stream
-                side.wait_stream(current)
+                side.wait_event(after)
                 with torch.cuda.stream(side):
                     meta_work.wait()
                     meta = part["recv_meta"]
@@ -531,14 +535,18 @@ class ExpertParallelMoE:
                     tensor.record_stream(current)
                 return out, done
 
+            def issued():
+                event = torch.cuda.Event()
+                event.record()
+                return event
+
             prepared = [None] * chunks
             if dedup:
-                prepared[0] = prepare(0, in_flight[3])
+                prepared[0] = prepare(0, in_flight[3], issued())
             returns = []
             for c in range(chunks):
                 nxt = send(c + 1) if c + 1 < chunks else None
-                if dedup and nxt is not None:
-                    prepared[c + 1] = prepare(c + 1, nxt[3])
+                sent = issued() if nxt is not None else None
                 if not dedup:
                     regroup[c] = regroup_index(plans[c].segment_offsets, self.world, self.local_experts,
                                                plans[c].recv_rows)
@@ -590,6 +598,10 @@ class ExpertParallelMoE:
                     y = ops.combine(y, parts[c]["copy_rows"], parts[c]["copy_weights"], None)
                 self._mark("expert fwd")
                 y_back, work = exchange(y, plans[c], self.group, back=True, async_op=True, copies=presum)
+                if dedup and nxt is not None:
+                    # queued only now, behind this chunk's launches: the host reaches the GEMMs sooner; on
+                    # the device the plan still starts as soon as chunk c + 1's metadata is there
+                    prepared[c + 1] = prepare(c + 1, nxt[3], sent)
                 self.bytes_moved += y.numel() * 2
                 returns.append((y, y_back, work))
             if self.shared is not None:

@@ -59,7 +59,7 @@ class PeerArena:
         self.handle = symmetric_memory.rendezvous(self.buffer, group=group.group_name)
         self.base = [int(p) for p in self.handle.buffer_ptrs]
         self.slot_bytes = self.slot_rows * self.width * 2
-        self.stream = torch.cuda.Stream(self.device)
+        self.stream = torch.cuda.Stream(self.device, priority=-1)  # ahead of the GEMMs' CTAs when SMs free up
         self.flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.exchanges = 0
         self.previous = None
