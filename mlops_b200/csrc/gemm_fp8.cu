@@ -18,11 +18,15 @@
 //               the two streams are independent, so while one thread is between K blocks
 //               (commits, two barrier checks: a few hundred cycles) the tensor cores still
 //               have the other thread's instructions queued
-//   warp 2      TMEM allocation / release
+//   warp 2      TMEM allocation / release; in between it brings the scales of every K block (128
+//               row scales, the tile's weight-block scales) from global memory into a ring in
+//               shared memory and counts, with the operands, on the stage's `full` barrier
 //   warp 3      first builds the tile table (group -> first M tile) in shared memory
 //   warps 4-11  epilogue: tcgen05.ld of a K block's partial, scale, accumulate; at the
 //               end of the K loop convert to bf16 and store the rows that belong to the
-//               group (rows past the group's end were multiplied but are not written).
+//               group (rows past the group's end were multiplied but are not written): 32 x 32
+//               blocks through shared memory and TMA stores where all 32 rows belong to the
+//               group, from registers otherwise.
 // Two TMEM accumulator buffers let the tensor cores run K block k+1 while block k is
 // being promoted.  No load is multicast; every wait is bounded.
 #include "common.cuh"
@@ -59,7 +63,9 @@ __device__ int g_tile_counter[kSchedSlots][2];
 //   slot 0 / 1  issuer of the even / odd K blocks: 0 loop top, 1 operands seen, 2 slab 0 free,
 //               3 slab 0 issued, 4 slab 1 free, 5 slab 1 issued
 //   slot 2 / 3  epilogue warp 4 (columns 0-127) / warp 8 (128-255): 0 waiting for the slab,
-//               1 slab complete seen, 2 last TMEM load landed, 3 promoted and handed back
+//               1 slab complete seen, 2 last TMEM load landed, 3 promoted and handed back; at the
+//               first K block of a tile also 4 previous tile's store begins, 5 store issued,
+//               6 next tile's number read, 7 next tile located
 //   slot 4      producer: 0 waiting for the stage, 1 stage free (loads issued next)
 #ifdef B200_GEMM_TRACE
 constexpr int kTraceFirst = 64, kTraceIts = 64, kTraceFields = 8, kTraceSlots = 5;
@@ -77,6 +83,7 @@ constexpr int kTraceFirst = 64, kTraceIts = 64, kTraceFields = 8, kTraceSlots = 
 // without them.  Bit 0: the epilogue hands an accumulator part back without reading it.
 // Bit 1: it reads the part but skips the multiply-adds.  Bit 2: after the first fill of the
 // stages the producer only signals them (no TMA traffic; the MMAs run on stale operands).
+// Bit 3: the scales are taken as 1 instead of being fetched from global memory.
 // -DB200_GEMM_FMA2=0 builds the scalar form of the promotion (one fmaf per element) for comparison.
 #ifndef B200_GEMM_FMA2
 #define B200_GEMM_FMA2 1
@@ -92,6 +99,11 @@ __device__ __forceinline__ void fma2(float& a0, float& a1, uint32_t r0, uint32_t
       : "+f"(a0), "+f"(a1)
       : "r"(r0), "r"(r1), "f"(s));
 }
+// -DB200_GEMM_VARIANT=<bits> builds alternatives of the per-K-block handshake that were measured
+// against the shipped form (0) and lost or tied: bit 0 the issuers read the abort flag every
+// eighth K block only, bit 1 / bit 2 the epilogue / the issuers wait with try_wait (sleeping)
+// instead of polling, bit 3 an accumulator part is handed back before its last multiply-adds,
+// bit 6 the epilogue warps fetch their scales from global memory themselves (no scale ring).
 #ifndef B200_GEMM_VARIANT
 #define B200_GEMM_VARIANT 0
 #endif
@@ -127,6 +139,7 @@ struct GemmFp8Params {
   long long out_rows;  // rows of d (row_map) or of out_f32 (row_token): targets outside are skipped
   int sched_slot;      // slot of g_tile_counter, or -1: tiles by CTA index
   int wide_store;      // d's base and row pitch are multiples of 32 bytes: 32-byte stores per lane
+  int tma_store;       // tmap_d describes d: full groups of 32 rows leave through TMA stores
   int* status;
 #ifdef B200_GEMM_TRACE
   long long* trace;
@@ -154,8 +167,17 @@ struct GemmCfg {
   static constexpr int kTileBytes = kStages * (kABytes + kBBytes);
   static constexpr int kBarBytes = 512;
   static constexpr int kSchedBytes = (2 * (kMaxGroups + 1) * 4 + 15) / 16 * 16;
-  static constexpr int kStoreBytes = 8 * 32 * 80;  // per-warp transpose buffers of the epilogue
-  static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + kStoreBytes + 1024;
+  // per-warp buffers of the epilogue's store: 32 rows x 64 bytes each, 1024-byte aligned (the
+  // source of a TMA store in the 64-byte swizzle mode), plus the slack the alignment may cost
+  // (one buffer per warp, or, where the stages leave room, one per 32-column block of the warp's
+  // part of the tile, so that the blocks' bulk stores need not wait for one another)
+  static constexpr int kFixedBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + 1024 + 8 * 136 * 4;
+  static constexpr int kStoreBuffers = (232448 - kFixedBytes - 1024 >= 8 * 4 * 2048) ? 4 : 1;
+  static constexpr int kStoreBytes = 8 * kStoreBuffers * 32 * 64 + 1024;
+  // ring of the scales of eight K blocks (128 row scales, 4 block scales, padding), filled by warp 2
+  static constexpr int kRingSlots = 8, kRingPitch = 136;
+  static constexpr int kRingBytes = kRingSlots * kRingPitch * 4;
+  static constexpr int kSmemBytes = 1024 + kTileBytes + kBarBytes + kSchedBytes + kStoreBytes + 1024 + kRingBytes;
 };
 
 struct TileCoord {
@@ -197,7 +219,8 @@ __device__ __forceinline__ TileCoord locate_m_tile(int mt, const int* m_tile_sta
 template <int BLOCK_N, bool B_MN_MAJOR, int EPI, bool SPLIT = false, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                        const __grid_constant__ CUtensorMap tmap_b, const GemmFp8Params p) {
+                        const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_d, const GemmFp8Params p) {
   using Cfg = GemmCfg<BLOCK_N, PAIR>;
   constexpr int kStages = Cfg::kStages;
   static_assert(!SPLIT || (BLOCK_N == 256 && EPI != 1), "the split issue is for the plain 256-wide tile");
@@ -225,9 +248,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 22);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* total_m_tiles_s = abort_flag + 1;
-  int* sched_tile = total_m_tiles_s + 1;  // [4]
+  int* sched_tile = total_m_tiles_s + 1;  // [4][4]: tile, its first row, rows that belong to the group, group
   int* m_tile_start = reinterpret_cast<int*>(smem + Cfg::kTileBytes + Cfg::kBarBytes);  // [groups+1]
   int* offs = m_tile_start + (kMaxGroups + 1);                                          // [groups+1]
+  // Single-CTA form: warp 2 brings the two scales of every K block from global memory into a ring
+  // in shared memory, one K block per operand stage, and counts on the stage's `full` barrier.
+  // Fetched by the epilogue warps themselves, the loads held those warps up (a tenth of the
+  // kernel's cycles) although they were issued four K blocks ahead.
+  constexpr bool kScaleRing = !PAIR && (B200_GEMM_VARIANT & 64) == 0;
+  float* scale_ring = reinterpret_cast<float*>(smem + Cfg::kTileBytes + Cfg::kBarBytes + Cfg::kSchedBytes +
+                                               Cfg::kStoreBytes + 1024);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -242,7 +272,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], kScaleRing ? 2 : 1);  // the operands (one arrival with their byte count) and the scales
       mbar_init(&empty[s], 1);
     }
     for (int i = 0; i < 4; ++i) mbar_init(&tfull[i], 1);
@@ -253,7 +283,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(&sched_full[i], 1);
       // the readers of a tile id: eight epilogue warps, the issuer warps (two; none in the
       // pair's second CTA) and, in a pair, the warp that reports landed stages
-      mbar_init(&sched_empty[i], PAIR ? (leader ? 11 : 9) : 10);
+      // (single-CTA form with the scale ring: warp 2 follows the tiles as well)
+      mbar_init(&sched_empty[i], PAIR ? (leader ? 11 : 9) : (kScaleRing ? 11 : 10));
     }
     if constexpr (PAIR) {
       for (int s = 0; s < kStages; ++s) mbar_init(&ready[s], 2);  // one report per CTA
@@ -332,10 +363,22 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // them, one tile ahead, in a four-slot ring in shared memory; -1 ends the sequence.
   // `tile_at(i)`: the i-th tile of this CTA (warp-wide call; lane 0 waits); `done_with(i)`
   // lets the slot be reused.  -2: the wait gave up.
-  auto tile_at = [&](uint32_t i) -> int {
-    int t = -2;
-    if (lane == 0 && mbar_spin(&sched_full[i & 3], (i >> 2) & 1, abort_flag, p.status, 7))
-      t = *reinterpret_cast<volatile int*>(&sched_tile[i & 3]);
+  // The producer locates a tile's rows (a binary search over the groups) once and publishes the
+  // answer with the number, so the other roles do not repeat the search at every tile boundary.
+  auto tile_at = [&](uint32_t i, TileCoord* where = nullptr) -> int {
+    int t = -2, m0 = 0, rows_valid = 0, group = 0;
+    if (lane == 0 && mbar_spin(&sched_full[i & 3], (i >> 2) & 1, abort_flag, p.status, 7)) {
+      const volatile int* e = sched_tile + (i & 3) * 4;
+      t = e[0];
+      m0 = e[1];
+      rows_valid = e[2];
+      group = e[3];
+    }
+    if (where != nullptr) {
+      where->m0 = __shfl_sync(0xffffffffu, m0, 0);
+      where->rows_valid = __shfl_sync(0xffffffffu, rows_valid, 0);
+      where->group = __shfl_sync(0xffffffffu, group, 0);
+    }
     return __shfl_sync(0xffffffffu, t, 0);
   };
   auto done_with = [&](uint32_t i) {
@@ -365,8 +408,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       auto publish = [&](int t) {
         const uint32_t slot = published & 3;
         if (!mbar_wait(&sched_empty[slot], ((published >> 2) & 1) ^ 1, abort_flag, p.status, 8)) return false;
-        sched_tile[slot] = t;
-        mbar_arrive(&sched_full[slot]);  // a release: the id is visible to whoever sees the phase
+        TileCoord where = {0, 0, 0};
+        if (t >= 0) where = locate(t / num_n_tiles);
+        sched_tile[slot * 4 + 0] = t;
+        sched_tile[slot * 4 + 1] = where.m0;
+        sched_tile[slot * 4 + 2] = where.rows_valid;
+        sched_tile[slot * 4 + 3] = where.group;
+        mbar_arrive(&sched_full[slot]);  // a release: the entry is visible to whoever sees the phase
         ++published;
         return true;
       };
@@ -459,6 +507,59 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int s = it % kStages;
         if (!mbar_wait_warp(&full[s], (it / kStages) & 1, abort_flag, p.status, 6)) { ok = false; break; }
         if (lane == 0) mbar_arrive_remote(&ready[s], 0);
+      }
+    }
+  } else if (kScaleRing && warp == 2) {
+    // ------------------------------ scale loader ------------------------------
+    B200_REG_DEC();
+    uint32_t it = 0;
+    bool ok = true;
+    for (uint32_t tile_i = 0; ok; ++tile_i) {
+      TileCoord c;
+      const int t = tile_at(tile_i, &c);
+      if (t == -2) ok = false;
+      else done_with(tile_i);
+      if (t < 0) break;
+      const int n0 = (t % num_n_tiles) * kTileStep;
+      // lane l holds the scales of rows l, l + 32, l + 64, l + 96 of the tile; lanes 0-3 also the
+      // weight-block scales: [0], [1] of the columns of epilogue half 0, 1; [2], [3] of their up
+      // columns (fused SwiGLU form).  Two K blocks per round of loads: this warp lives on 40
+      // registers, and a round's latency is shorter than the operands' own.
+      int row[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) row[i] = min(c.m0 + lane + 32 * i, p.rows_total - 1);
+      const int h = lane & 1;
+      const int col = (lane & 2) ? half_n + n0 + h * 64 : (EPI == 1 ? n0 + h * 64 : n0 + h * (BLOCK_N / 2));
+      const float* b_ptr = p.b_scale + (long long)(c.group % p.weights) * p.bs_group_stride +
+                           (long long)min(col / 128, (p.N - 1) / 128) * p.bs_n_stride;
+      const bool has_b = lane < (EPI == 1 ? 4 : 2);
+      for (int kb0 = 0; kb0 < num_kb && ok; kb0 += 2) {
+        float va[2][4], vb[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int kk = min(kb0 + u, num_kb - 1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            va[u][i] = p.a_scale[(long long)row[i] * p.as_row_stride + (long long)kk * p.as_kb_stride];
+          vb[u] = has_b ? b_ptr[(long long)kk * p.bs_k_stride] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (kb0 + u >= num_kb) break;
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          // The stage's previous K block has been multiplied, so the K block that used this ring
+          // slot (eight back) was promoted long ago: its accumulator had to be handed back before
+          // a later one could be issued.
+          if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag, p.status, 9)) { ok = false; break; }
+          float* slot = scale_ring + (it % Cfg::kRingSlots) * Cfg::kRingPitch;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) slot[lane + 32 * i] = va[u][i];
+          if (has_b) slot[128 + lane] = vb[u];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full[s]);  // a release; the epilogue sees the slot through the issuer's commit
+          ++it;
+        }
       }
     }
   } else if ((warp == 1 || warp == 3) && (!PAIR || leader)) {
@@ -565,8 +666,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     B200_REG_INC();
     constexpr int kCols = BLOCK_N / 2;  // columns owned by one thread
     constexpr int kChunks = kCols / 32;
-    constexpr int kStageRowBytes = 80;  // 64 bytes of data, padded against bank conflicts
+    // A row of a warp's buffer is 64 bytes; its four 16-byte pieces are stored swizzled
+    // (piece ^ ((row >> 1) & 3)): conflict-free for a lane-per-row write and for the 8 rows x 4
+    // pieces read, and the layout a TMA store with the 64-byte swizzle expects.
+    constexpr int kStageRowBytes = 64;
     constexpr int kStageWarpBytes = 32 * kStageRowBytes;
+    auto piece_at = [](int row, int piece) { return row * kStageRowBytes + ((piece ^ ((row >> 1) & 3)) << 4); };
     uint8_t* stage_base = smem + Cfg::kTileBytes + Cfg::kBarBytes + Cfg::kSchedBytes;
     const int q = warp & 3;             // TMEM lane quarter this warp may read
     const int half = (warp - 4) >> 2;   // which half of the tile's columns
@@ -584,11 +689,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const float* bs_ptr;
       const float* bs_ptr_up;
     };
-    auto describe = [&](int t) {
+    auto describe = [&](int t, const TileCoord& c) {
       EpiTile e;
-      const int mt = t / num_n_tiles;
-      const int n0 = (t - mt * num_n_tiles) * kTileStep;
-      const TileCoord c = locate(mt);
+      const int n0 = (t % num_n_tiles) * kTileStep;
       e.rows_valid = c.rows_valid;
       e.grow = c.m0 + row_in_tile;
       e.col0 = EPI == 1 ? n0 + half * 64 : n0 + half * kCols;
@@ -609,6 +712,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      float (&su)[EPI == 1 ? kScaleBatch : 1]) {
 #pragma unroll
       for (int u = 0; u < kScaleBatch; ++u) {
+        if constexpr ((B200_GEMM_ABLATE & 8) != 0) {  // no scale traffic
+          sa[u] = 1.f;
+          sb[u] = 1.f;
+          if constexpr (EPI == 1) su[u] = 1.f;
+          continue;
+        }
         const int kk = min(kb0 + u, num_kb - 1);
         sa[u] = e.as_ptr[(long long)kk * p.as_kb_stride];
         sb[u] = e.bs_ptr[(long long)kk * p.bs_k_stride];
@@ -616,18 +725,22 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     };
     EpiTile cur_tile, nxt_tile;
-    int t_cur = tile_at(0);
+    TileCoord where;
+    int t_cur = tile_at(0, &where);
     if (t_cur == -2) ok = false;
     if (t_cur >= 0) {
-      cur_tile = describe(t_cur);
-      fetch(cur_tile, 0, sa_cur, sb_cur, su_cur);
+      cur_tile = describe(t_cur, where);
+      if constexpr (!kScaleRing) fetch(cur_tile, 0, sa_cur, sb_cur, su_cur);
     }
     for (uint32_t tile_i = 0; t_cur >= 0 && ok; ++tile_i) {
-      const int t_nxt = tile_at(tile_i + 1);  // published together with the current one
+      if (lane == 0 && q == 0) B200_TRACE(2 + half, ab, 5);
+      const int t_nxt = tile_at(tile_i + 1, &where);  // published together with the current one
       if (t_nxt == -2) { ok = false; break; }
+      if (lane == 0 && q == 0) B200_TRACE(2 + half, ab, 6);
       const bool has_next = t_nxt >= 0;
-      if (has_next) nxt_tile = describe(t_nxt);
+      if (has_next) nxt_tile = describe(t_nxt, where);
       done_with(tile_i);
+      if (lane == 0 && q == 0) B200_TRACE(2 + half, ab, 7);
       t_cur = t_nxt;
       const EpiTile c = cur_tile;
       const int grow = c.grow;
@@ -635,13 +748,18 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
       for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kScaleBatch) {
-        if (kb0 + kScaleBatch < num_kb) fetch(c, kb0 + kScaleBatch, sa_nxt, sb_nxt, su_nxt);
-        else if (has_next) fetch(nxt_tile, 0, sa_nxt, sb_nxt, su_nxt);
+        if constexpr (!kScaleRing) {
+          if (kb0 + kScaleBatch < num_kb) fetch(c, kb0 + kScaleBatch, sa_nxt, sb_nxt, su_nxt);
+          else if (has_next) fetch(nxt_tile, 0, sa_nxt, sb_nxt, su_nxt);
+        }
 #pragma unroll
         for (int u = 0; u < kScaleBatch; ++u) {
           if (kb0 + u >= num_kb) break;
-          const float s = sa_cur[u] * sb_cur[u];
-          const float s_up = EPI == 1 ? sa_cur[u] * su_cur[u] : s;
+          float s = 0.f, s_up = 0.f;
+          if constexpr (!kScaleRing) {
+            s = sa_cur[u] * sb_cur[u];
+            s_up = EPI == 1 ? sa_cur[u] * su_cur[u] : s;
+          }
           const int buf = ab & 1;
           const uint32_t aph = (ab >> 1) & 1;
           ++ab;
@@ -653,6 +771,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 1);
+          if constexpr (kScaleRing) {
+            // written before the stage's `full` barrier completed, which the issuer saw before it
+            // issued what this warp has just seen complete
+            const float* slot = scale_ring + ((ab - 1) % Cfg::kRingSlots) * Cfg::kRingPitch;
+            const float sa = slot[row_in_tile];
+            s = sa * slot[128 + half];
+            s_up = EPI == 1 ? sa * slot[130 + half] : s;
+          }
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BLOCK_N +
                                  (EPI == 1 ? half * 64 : half * kCols);
@@ -720,21 +846,31 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (lane == 0 && q == 0) B200_TRACE(2 + half, ab - 1, 3);
           }
         }
+        if constexpr (!kScaleRing) {
 #pragma unroll
-        for (int u = 0; u < kScaleBatch; ++u) {
-          sa_cur[u] = sa_nxt[u];
-          sb_cur[u] = sb_nxt[u];
-          if constexpr (EPI == 1) su_cur[u] = su_nxt[u];
+          for (int u = 0; u < kScaleBatch; ++u) {
+            sa_cur[u] = sa_nxt[u];
+            sb_cur[u] = sb_nxt[u];
+            if constexpr (EPI == 1) su_cur[u] = su_nxt[u];
+          }
         }
       }
       cur_tile = nxt_tile;
       if (!ok) break;
+      if (lane == 0 && q == 0) B200_TRACE(2 + half, ab, 4);
       // Store: the warp holds 32 rows x kCols columns, one row per lane.  Written directly, a
       // store instruction would touch 32 different rows with 16 bytes each; instead each 32-column
       // slab goes through a small per-warp shared-memory buffer and leaves as 8 rows x 64
       // contiguous bytes per instruction (whole 32-byte sectors).
       {
-        uint8_t* stage = stage_base + (warp - 4) * kStageWarpBytes;
+        uint8_t* stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(stage_base) + 1023) & ~uintptr_t(1023)) +
+                         (warp - 4) * (Cfg::kStoreBuffers * kStageWarpBytes);
+        bool drained = false;  // several buffers: one wait per tile covers the previous tile's stores
+        // a bulk store of this warp may still be reading the buffer; lane 0 issued them all
+        auto buffer_free = [&]() {
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+        };
         const int rows_here = c.rows_valid - q * 32;  // rows of this warp that belong to the group
         // where this lane's row goes: in place, or wherever the caller's map sends it (rows
         // that arrived as [source rank][expert] and were multiplied in expert order go back)
@@ -776,7 +912,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
-              __syncwarp();
+              buffer_free();
 #pragma unroll
               for (int j = 0; j < 16; j += 4) {
                 float4 v;
@@ -784,7 +920,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 v.y = wgt * __bfloat162float(__float2bfloat16_rn(acc[cc * 32 + sub * 16 + j + 1]));
                 v.z = wgt * __bfloat162float(__float2bfloat16_rn(acc[cc * 32 + sub * 16 + j + 2]));
                 v.w = wgt * __bfloat162float(__float2bfloat16_rn(acc[cc * 32 + sub * 16 + j + 3]));
-                *reinterpret_cast<float4*>(stage + lane * kStageRowBytes + j * 4) = v;
+                *reinterpret_cast<float4*>(stage + piece_at(lane, j >> 2)) = v;
               }
               __syncwarp();
               const int piece = lane & 3;  // 16-byte piece of the 64-byte row slab
@@ -794,7 +930,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int r = pass * 8 + (lane >> 2);
                 const int tok_r = __shfl_sync(0xffffffffu, tok, r);
                 if (r < rows_here && tok_r >= 0 && col + 4 <= p.N) {
-                  const float4 v = *reinterpret_cast<const float4*>(stage + r * kStageRowBytes + piece * 16);
+                  const float4 v = *reinterpret_cast<const float4*>(stage + piece_at(r, piece));
                   atomicAdd(reinterpret_cast<float4*>(p.out_f32 + (long long)tok_r * p.ldo + col), v);
                 }
               }
@@ -802,6 +938,40 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             continue;
           }
           const int chunk_col0 = EPI == 1 ? ((cc >> 1) ? c.col1 : c.col0) + (cc & 1) * 32 : col0 + cc * 32;
+          if (p.tma_store && rows_here >= 32 && chunk_col0 + 32 <= p.N) {
+            // All 32 rows of the warp belong to the group and lie one after the other in d: the
+            // 32 x 32 block goes to a 2 KB buffer (rows of 64 bytes, 16-byte pieces swizzled as the
+            // tensor map's 64-byte mode expects: conflict-free writes) and leaves as ONE bulk
+            // store.  Written from registers, the tile's 2048 sector-sized stores per CTA kept the
+            // SM's memory pipeline busy for thousands of cycles, in which the issuers' own
+            // instructions (multiplications, barrier checks) queued behind them.  A bulk store
+            // needs some 700 cycles to read its buffer: with one buffer per warp the four blocks
+            // wait for one another, with four they do not.
+            uint8_t* out = stage;
+            if constexpr (Cfg::kStoreBuffers > 1) {
+              out = stage + (cc % Cfg::kStoreBuffers) * kStageWarpBytes;
+              if (!drained) buffer_free();
+              drained = true;
+            } else {
+              buffer_free();  // the previous block has left the buffer
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(acc[cc * 32 + j * 8 + 0], acc[cc * 32 + j * 8 + 1]);
+              v.y = pack_bf16x2(acc[cc * 32 + j * 8 + 2], acc[cc * 32 + j * 8 + 3]);
+              v.z = pack_bf16x2(acc[cc * 32 + j * 8 + 4], acc[cc * 32 + j * 8 + 5]);
+              v.w = pack_bf16x2(acc[cc * 32 + j * 8 + 6], acc[cc * 32 + j * 8 + 7]);
+              *reinterpret_cast<uint4*>(out + piece_at(lane, j)) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_d, out, chunk_col0, c.grow - lane);
+              bulk_commit_group();
+            }
+            continue;
+          }
           if (p.wide_store && chunk_col0 + 32 <= p.N) {
             // 32 bytes per lane and instruction straight from the registers: whole sectors of the
             // lane's own row, no trip through shared memory (the store phase of a tile holds up the
@@ -825,7 +995,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             continue;
           }
-          __syncwarp();
+          buffer_free();
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 v;
@@ -833,7 +1003,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             v.y = pack_bf16x2(acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
             v.z = pack_bf16x2(acc[cc * 32 + j + 4], acc[cc * 32 + j + 5]);
             v.w = pack_bf16x2(acc[cc * 32 + j + 6], acc[cc * 32 + j + 7]);
-            *reinterpret_cast<uint4*>(stage + lane * kStageRowBytes + j * 2) = v;
+            *reinterpret_cast<uint4*>(stage + piece_at(lane, j >> 3)) = v;
           }
           __syncwarp();
           const int piece = lane & 3;          // 16-byte piece of the 64-byte row slab
@@ -844,7 +1014,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int r = pass * 8 + (lane >> 2);
             const int dst_row = __shfl_sync(0xffffffffu, out_row, r);
             if (r < rows_here && dst_row >= 0 && col + 8 <= p.N) {
-              const uint4 v = *reinterpret_cast<const uint4*>(stage + r * kStageRowBytes + piece * 16);
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + piece_at(r, piece));
               *reinterpret_cast<uint4*>(p.d + (long long)dst_row * p.ldd + col) = v;
             }
           }
@@ -895,6 +1065,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    if (lane == 0) bulk_wait_all();  // the buffers' last bulk stores, before shared memory is given up
     if (!ok) {
       // Unwinding: an issuer may be waiting on a hardware barrier for this warp.  (In the pair
       // form the issuer's wait is an mbarrier wait with its own limit.)
@@ -956,8 +1127,8 @@ static int sched_slot_of(cudaStream_t stream) {
 
 // The pair form: clusters of two CTAs, one 256 x 256 tile per pair at a time.
 template <bool B_MN, bool SPLIT>
-static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp8Params& p,
-                            cudaStream_t stream) {
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                            const GemmFp8Params& p, cudaStream_t stream) {
   using Cfg = GemmCfg<256, true>;
   auto kern = grouped_gemm_fp8_kernel<256, B_MN, 0, SPLIT, true>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
@@ -981,13 +1152,13 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, q) != cudaSuccess) return B200MOE_ERR_LAUNCH;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, q) != cudaSuccess) return B200MOE_ERR_LAUNCH;
   return launch_status();
 }
 
 template <int BLOCK_N, bool B_MN, int EPI = 0, bool SPLIT = false>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp8Params& p,
-                       cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                       const GemmFp8Params& p, cudaStream_t stream) {
   using Cfg = GemmCfg<BLOCK_N>;
   auto kern = grouped_gemm_fp8_kernel<BLOCK_N, B_MN, EPI, SPLIT>;
   // Function attributes are per device; setting one is a cheap host-side call.
@@ -1008,7 +1179,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmF
   if (grid < 1) grid = 1;
   GemmFp8Params q = p;
   q.sched_slot = sched_slot_of(stream);
-  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, q);
+  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, td, q);
   return launch_status();
 }
 
@@ -1060,6 +1231,28 @@ extern "C" int b200moe_set_gemm_pair(int mode) {
   return B200MOE_OK;
 }
 
+// The tensor map of the bf16 output for the epilogue's TMA stores (blocks of 32 rows x 32
+// columns, 64-byte swizzle), or a copy of `fallback` when the output cannot leave that way:
+// scattered rows, no plain output, B200MOE_GEMM_TMA_STORE=0.  Returns whether `td` describes d.
+static bool output_tensor_map(CUtensorMap* td, const CUtensorMap& fallback, void* d, long long ldd, int N,
+                              long long rows, bool eligible) {
+  static const bool off = [] {
+    const char* v = getenv("B200MOE_GEMM_TMA_STORE");
+    return v != nullptr && v[0] == '0';
+  }();
+  *td = fallback;
+  if (off || !eligible || d == nullptr || rows <= 0) return false;
+  uint64_t dims[2] = {(uint64_t)N, (uint64_t)rows};
+  uint64_t strides[1] = {(uint64_t)ldd * 2};
+  uint32_t box[2] = {32, 32};
+  CUtensorMap m;
+  if (encode_tensor_map(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B) !=
+      B200MOE_OK)
+    return false;
+  *td = m;
+  return true;
+}
+
 // Shared by the plain product (d != NULL) and the one with the combine fused into its store
 // (out_f32 != NULL).
 static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_scale, long long as_row_stride,
@@ -1107,6 +1300,8 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
     return v != nullptr && v[0] == '0';
   }();
   p.wide_store = (!narrow_store && d != nullptr && ((uintptr_t)d & 31) == 0 && (ldd % 16) == 0) ? 1 : 0;
+  CUtensorMap td;
+  p.tma_store = output_tensor_map(&td, ta, d, ldd, N, rows_total, !fused && row_map == nullptr) ? 1 : 0;
   p.addend = reinterpret_cast<const __nv_bfloat16*>(addend);
   p.ldc = ldc;
   p.offsets = offsets;
@@ -1167,9 +1362,9 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (pair && pair_split)
-    return b_mn_major ? launch_gemm_pair<true, true>(ta, tb, p, s) : launch_gemm_pair<false, true>(ta, tb, p, s);
+    return b_mn_major ? launch_gemm_pair<true, true>(ta, tb, td, p, s) : launch_gemm_pair<false, true>(ta, tb, td, p, s);
   if (pair)
-    return b_mn_major ? launch_gemm_pair<true, false>(ta, tb, p, s) : launch_gemm_pair<false, false>(ta, tb, p, s);
+    return b_mn_major ? launch_gemm_pair<true, false>(ta, tb, td, p, s) : launch_gemm_pair<false, false>(ta, tb, td, p, s);
   // the 256-wide tile issues each K block in two halves (B200MOE_GEMM_SPLIT=0: in one piece)
   static const bool split = [] {
     const char* v = getenv("B200MOE_GEMM_SPLIT");
@@ -1177,15 +1372,15 @@ static int grouped_gemm_fp8_impl(const void* a, long long lda, const float* a_sc
   }();
   if (fused) {
     if (split)
-      return b_mn_major ? launch_gemm<256, true, 2, true>(ta, tb, p, s) : launch_gemm<256, false, 2, true>(ta, tb, p, s);
-    return b_mn_major ? launch_gemm<256, true, 2>(ta, tb, p, s) : launch_gemm<256, false, 2>(ta, tb, p, s);
+      return b_mn_major ? launch_gemm<256, true, 2, true>(ta, tb, td, p, s) : launch_gemm<256, false, 2, true>(ta, tb, td, p, s);
+    return b_mn_major ? launch_gemm<256, true, 2>(ta, tb, td, p, s) : launch_gemm<256, false, 2>(ta, tb, td, p, s);
   }
   if (block_n == 128) {
-    return b_mn_major ? launch_gemm<128, true>(ta, tb, p, s) : launch_gemm<128, false>(ta, tb, p, s);
+    return b_mn_major ? launch_gemm<128, true>(ta, tb, td, p, s) : launch_gemm<128, false>(ta, tb, td, p, s);
   }
   if (split)
-    return b_mn_major ? launch_gemm<256, true, 0, true>(ta, tb, p, s) : launch_gemm<256, false, 0, true>(ta, tb, p, s);
-  return b_mn_major ? launch_gemm<256, true>(ta, tb, p, s) : launch_gemm<256, false>(ta, tb, p, s);
+    return b_mn_major ? launch_gemm<256, true, 0, true>(ta, tb, td, p, s) : launch_gemm<256, false, 0, true>(ta, tb, td, p, s);
+  return b_mn_major ? launch_gemm<256, true>(ta, tb, td, p, s) : launch_gemm<256, false>(ta, tb, td, p, s);
 }
 
 extern "C" int b200moe_grouped_gemm_fp8(const void* a, long long lda, const float* a_scale,
@@ -1282,6 +1477,8 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.d = reinterpret_cast<__nv_bfloat16*>(h13);
   p.ldd = ldh;
   p.wide_store = (((uintptr_t)h13 & 31) == 0 && (ldh % 16) == 0) ? 1 : 0;
+  CUtensorMap td;
+  p.tma_store = output_tensor_map(&td, ta, h13, ldh, N, rows_total, true) ? 1 : 0;
   p.addend = nullptr;
   p.ldc = 0;
   p.offsets = offsets;
@@ -1306,7 +1503,7 @@ extern "C" int b200moe_grouped_gemm_fp8_swiglu(const void* a, long long lda, con
   p.status = status;
   B200_SET_TRACE(p);
   B200_SET_WITHHOLD(p);
-  return launch_gemm<256, false, 1>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
+  return launch_gemm<256, false, 1>(ta, tb, td, p, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200moe_set_cta_limit(int ctas) {

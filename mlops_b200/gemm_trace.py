@@ -92,8 +92,33 @@ def report(table, first):
     return "\n".join(lines)
 
 
+ISSUER_FIELDS = ("loop top", "operands landed", "slab 0 free", "slab 0 issued", "slab 1 free", "slab 1 issued")
+EPILOGUE_FIELDS = ("wait begins", "slab complete", "loads done", "slab released", "tile boundary: store begins",
+                   "tile boundary: store issued", "tile boundary: next tile's number read", "tile boundary: next tile located")
+
+
+def timeline(table, first, start, count):
+    """The stamps of K blocks `start .. start + count - 1` (relative to the window) of all roles,
+    merged and ordered by time; times relative to the earliest of them."""
+    events = []
+    for i in range(start, start + count):
+        for f, name in enumerate(ISSUER_FIELDS):
+            events.append((float(table[i % 2, i, f]), f"issuer {i % 2}", first + i, name))
+        for half, slot in ((0, 2), (1, 3)):
+            for f, name in enumerate(EPILOGUE_FIELDS):
+                events.append((float(table[slot, i, f]), f"epilogue {half}", first + i, name))
+        for f, name in enumerate(("wait begins", "stage free")):
+            events.append((float(table[4, i, f]), "producer", first + i, name))
+    events = [e for e in events if e[0] > 0]
+    events.sort()
+    base = events[0][0]
+    return "\n".join(f"{t - base:8.0f}  {role:<11} K block {kb:<4} {name}" for t, role, kb, name in events)
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--timeline", type=int, default=0, help="also print the ordered stamps of this many K blocks")
+    parser.add_argument("--timeline-start", type=int, default=24, help="... from this K block of the window on")
     parser.add_argument("--rows", type=int, default=32768)
     parser.add_argument("--experts", type=int, default=32)
     parser.add_argument("--n", type=int, default=4096)
@@ -104,6 +129,8 @@ def main():
     table, first = trace(args.rows, args.experts, args.n, args.k, b_mn_major=args.mn_major, pair=args.pair)
     print(f"rows {args.rows} experts {args.experts} N {args.n} K {args.k} mn_major {args.mn_major} pair {args.pair}")
     print(report(table, first))
+    if args.timeline:
+        print(timeline(table, first, args.timeline_start, args.timeline))
 
 
 if __name__ == "__main__":
