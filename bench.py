@@ -78,7 +78,7 @@ SKEWED_BIAS_STD = 0.1
 # --no-cpu --no-extras` (forward up, forward down, input gradient of down, input gradient of
 # up). Traffic is operands once + output once, so the full-size layer (8x the rows and
 # experts) scales by 8.
-GEMM_DRAM_BYTES_C4P = (1.480e9 + 0.282e9, 0.539e9 + 0.440e9, 0.753e9 + 0.131e9, 1.095e9 + 0.462e9)
+GEMM_DRAM_BYTES_C4P = (1.271e9 + 0.278e9, 0.540e9 + 0.439e9, 0.742e9 + 0.130e9, 1.097e9 + 0.460e9)
 
 
 def measured_peaks():
