@@ -56,3 +56,13 @@ def test_ops_refuse_cpu_tensors():
         ops.route_topk(torch.zeros(4, 8), 2, "softmax_then_topk")
     with pytest.raises(NativeError):
         ops.quantize_rows(torch.zeros(4, 128, dtype=torch.bfloat16))
+
+
+def test_device_probes_compile_for_sm_100a():
+    """The stand-alone probes beside the kernels build with nvcc (nothing runs without a GPU)."""
+    from mlops_b200 import probes
+
+    names = sorted(p.stem for p in probes.PROBES.glob("*.cu"))
+    assert "handshake" in names
+    for name in names:
+        assert probes.build(name).exists()
