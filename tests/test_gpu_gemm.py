@@ -565,3 +565,50 @@ def test_pair_form_integer_operands_scatter_and_addend(pair_form, mn_major):
     expected = torch.empty_like(ref)
     expected[row_map.long()] = ref + addend.double()
     assert torch.equal(scattered.cpu(), expected.float().bfloat16())
+
+
+_STORE_FORMS_SNIPPET = """
+import hashlib, sys, torch
+sys.path.insert(0, {root!r})
+from mlops_b200 import ops
+g = torch.Generator(device="cuda").manual_seed(5)
+counts = [0, 130, 1, 255, 64, 33, 300, 97]   # warps with all 32 rows in the group, with fewer, with none
+rows, n, k = sum(counts), 544, 384            # 544 = 2 x 256 + 32: the last tile is one 32-column block wide
+a = torch.randn(rows, k, device="cuda", generator=g).bfloat16()
+w = torch.randn(len(counts), n, k, device="cuda", generator=g).bfloat16()
+a_q, a_s = ops.quantize_rows(a)
+w_q, w_s = ops.quantize_blocks(w)
+offs = torch.tensor([0] + counts, dtype=torch.int32).cumsum(0).to(torch.int32).cuda()
+out = ops.grouped_gemm_fp8(a_q, a_s, w_q, w_s, offs)
+# the fused SwiGLU form stores h13 the same way
+w13 = torch.randn(len(counts), 512, k, device="cuda", generator=g).bfloat16()
+w13_q, w13_s = ops.quantize_blocks(w13)
+fused = ops.grouped_gemm_fp8_swiglu(a_q, a_s, w13_q, w13_s, offs)
+ops.check_status(torch.device("cuda"))
+torch.cuda.synchronize()
+digest = hashlib.sha256(out.view(torch.int16).cpu().numpy().tobytes())
+digest.update(fused[0].view(torch.int16).cpu().numpy().tobytes())
+print("DIGEST", digest.hexdigest(), float(out.float().abs().sum()))
+"""
+
+
+def test_tma_store_and_register_store_write_the_same_bytes():
+    """The output of the FP8 GEMM leaves through TMA stores where a warp's 32 rows all belong
+    to the group and from registers elsewhere; with B200MOE_GEMM_TMA_STORE=0 (read once per
+    process, hence the child processes) everything leaves from registers. Same bytes."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = str(Path(__file__).resolve().parent.parent)
+    digests = []
+    for switch in ("1", "0"):
+        env = dict(os.environ, B200MOE_GEMM_TMA_STORE=switch)
+        done = subprocess.run([sys.executable, "-c", _STORE_FORMS_SNIPPET.format(root=root)], env=env,
+                              capture_output=True, text=True, timeout=300)
+        assert done.returncode == 0, done.stderr[-2000:]
+        line = [l for l in done.stdout.splitlines() if l.startswith("DIGEST")][-1].split()
+        assert float(line[2]) > 0
+        digests.append(line[1])
+    assert digests[0] == digests[1]
